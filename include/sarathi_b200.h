@@ -1,0 +1,226 @@
+/* C ABI of libsarathi_b200.so -- the B200 (sm_100a) implementation of the
+ * tensor-parallel decoder-layer path of Sarathi-Serve.
+ *
+ * Conventions
+ *   - Every entry point returns 0 (SB200_OK) or a positive status code;
+ *     sb200_last_error() returns a human-readable message for the calling
+ *     thread's last failure.
+ *   - All pointers are DEVICE pointers unless named host_*; the caller owns
+ *     every buffer; no entry point allocates device memory unless it says so.
+ *   - `stream` is a cudaStream_t passed as void* (0 = the legacy default
+ *     stream).  Kernels are launched on it and nothing is synchronised.
+ *   - The current CUDA device of the calling thread must be the device that
+ *     owns the buffers (the reference's ops install no device guard either).
+ *   - dtype ids: SB200_F32 / SB200_F16 / SB200_BF16.
+ *   - "reference" citations are paths inside the microsoft/sarathi-serve tree.
+ */
+#ifndef SARATHI_B200_H_
+#define SARATHI_B200_H_
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef void* sb200_stream_t;
+
+enum sb200_dtype { SB200_F32 = 0, SB200_F16 = 1, SB200_BF16 = 2 };
+enum sb200_itype { SB200_I32 = 0, SB200_I64 = 1, SB200_I16 = 2, SB200_I8 = 3, SB200_U8 = 4 };
+
+enum sb200_status {
+  SB200_OK = 0,
+  SB200_ERR_INVALID_ARGUMENT = 1, /* bad pointer / shape / stride / alignment */
+  SB200_ERR_UNSUPPORTED = 2,      /* dtype or shape outside what the kernels cover */
+  SB200_ERR_CUDA = 3,             /* a CUDA runtime / driver call failed */
+  SB200_ERR_PEER_TIMEOUT = 4,     /* a bounded device-side wait on a peer or barrier ran out */
+  SB200_ERR_NOT_INITIALISED = 5
+};
+
+/* Message for the last non-zero status returned to this thread. */
+const char* sb200_last_error(void);
+/* Library version string. */
+const char* sb200_version(void);
+
+/* ------------------------------------------------------------------ norms */
+
+/* out[t,:] = ((T)(x[t,:] * rsqrt(mean(x[t,:]^2) + eps))) * w      (statistics in fp32).
+ * Replaces: layernorm_ops.rms_norm -- csrc/layernorm.cpp:3-13,
+ * csrc/layernorm_kernels.cu:10-62 (called from
+ * sarathi/model_executor/layers/layernorm.py:31-40).
+ * x, out: [T, H] contiguous rows; w: [H]. */
+int sb200_rms_norm(void* out, const void* x, const void* w, float eps,
+                   int64_t T, int64_t H, int dtype, sb200_stream_t stream);
+
+/* z = (T)(x + residual); residual_out = z; out = rms_norm(z, w, eps).
+ * Replaces the pair "hidden = residual + hidden" + RMSNorm of the decoder layer:
+ * sarathi/model_executor/models/llama.py:248-252,254 (torch add, then
+ * csrc/layernorm_kernels.cu:10-35).  residual_out may alias residual or x. */
+int sb200_fused_add_rms_norm(void* out, void* residual_out, const void* x, const void* residual,
+                             const void* w, float eps, int64_t T, int64_t H, int dtype,
+                             sb200_stream_t stream);
+
+/* ------------------------------------------------------------ activations */
+
+/* out[t,i] = ((T) silu(in[t,i])) * in[t,d+i]; in: [T, 2d], out: [T, d].
+ * Replaces: activation_ops.silu_and_mul -- csrc/activation.cpp:3-5,
+ * csrc/activation_kernels.cu:8-48. */
+int sb200_silu_and_mul(void* out, const void* in, int64_t T, int64_t d, int dtype,
+                       sb200_stream_t stream);
+/* Element-wise tanh-approximated GELUs on [T, d].
+ * Replace: activation_ops.gelu_new / gelu_fast -- csrc/activation_kernels.cu:53-112. */
+int sb200_gelu_new(void* out, const void* in, int64_t T, int64_t d, int dtype, sb200_stream_t stream);
+int sb200_gelu_fast(void* out, const void* in, int64_t T, int64_t d, int dtype, sb200_stream_t stream);
+
+/* ------------------------------------------------------------------ rotary */
+
+/* In-place rotary embedding of query [T, nq*head_size] and key [T, nkv*head_size]
+ * whose rows are q_stride / k_stride ELEMENTS apart (views into a fused qkv
+ * buffer are fine).  cos_sin_cache: [max_pos, rot_dim] = cos(rot_dim/2) | sin(rot_dim/2)
+ * in the same dtype; positions: int64 [T].  is_neox != 0 pairs (i, i+rot_dim/2),
+ * otherwise (2i, 2i+1).
+ * Replaces: pos_encoding_ops.rotary_embedding -- csrc/pos_encoding.cpp:3-15,
+ * csrc/pos_encoding_kernels.cu:8-127. */
+int sb200_rotary_embedding(const int64_t* positions, void* query, void* key, int64_t T,
+                           int num_heads, int num_kv_heads, int head_size, int rot_dim,
+                           int64_t q_stride, int64_t k_stride, const void* cos_sin_cache,
+                           int is_neox, int dtype, sb200_stream_t stream);
+
+/* -------------------------------------------------------------- MoE routing */
+
+/* Softmax over E experts in fp32, then k rounds of arg-max (ties -> lowest
+ * index).  gating: [T, E] in gating_dtype (fp32 reproduces the reference op;
+ * fp16/bf16 fold in the reference's `.float()` cast, fused_moe.py:367).
+ * topk_weights: fp32 [T,k]; topk_ids, token_expert_indices: int32 [T,k]
+ * (token_expert_indices[t,j] = j*T + t; may be NULL).  renormalize != 0 divides
+ * each row of weights by its sum (fused_moe.py:371-372).  Any E is accepted
+ * (powers of two <= 256 take the warp-level path); no workspace is needed.
+ * Replaces: moe_ops.topk_softmax -- csrc/moe.cpp:3-8,
+ * csrc/moe_topk_softmax_kernels.cu:50-166,182-380,421-503. */
+int sb200_topk_softmax(float* topk_weights, int32_t* topk_ids, int32_t* token_expert_indices,
+                       const void* gating, int gating_dtype, int64_t T, int E, int k,
+                       int renormalize, sb200_stream_t stream);
+
+/* Stable counting sort of the flat (token, k) slots by expert, each expert's
+ * segment padded to a multiple of block_size.  sorted_token_ids (capacity
+ * sorted_capacity >= numel + min(E,numel)*(block_size-1)) is fully written: slot
+ * indices in the defined prefix, `numel` as the pad value everywhere else (the
+ * reference pre-fills it in Python, fused_moe.py:191-195).  expert_ids[b] is
+ * written for b < num_tokens_post_pad/block_size.  Ids outside [0, E) are
+ * skipped.  `scratch` (device, sb200_moe_align_scratch_bytes() bytes) is
+ * optional: with it, inputs above 8192 slots are spread over many CTAs;
+ * without it one CTA does the whole sort in shared memory.
+ * Replaces: moe_ops.moe_align_block_size -- csrc/moe.cpp:10-17,
+ * csrc/moe_align_block_size_kernels.cu:23-135. */
+int sb200_moe_align_block_size(const void* topk_ids, int ids_itype, int64_t numel, int num_experts,
+                               int block_size, int32_t* sorted_token_ids, int64_t sorted_capacity,
+                               int32_t* expert_ids, int64_t expert_ids_capacity,
+                               int32_t* num_tokens_post_pad, void* scratch, int64_t scratch_bytes,
+                               sb200_stream_t stream);
+/* Bytes of scratch the multi-CTA path of sb200_moe_align_block_size wants. */
+int64_t sb200_moe_align_scratch_bytes(int64_t numel, int num_experts);
+
+/* ------------------------------------------------- column-parallel projections */
+
+enum sb200_epilogue {
+  SB200_EPI_NONE = 0,     /* out = x * w^T (+ bias) */
+  SB200_EPI_ROTARY = 1,   /* qkv projection with the rotary embedding of q and k applied in the epilogue */
+  SB200_EPI_SILU_MUL = 2  /* gate_up projection with silu(gate) * up applied in the epilogue */
+};
+
+typedef struct sb200_rotary_args {
+  const int64_t* positions;   /* int64 [T] */
+  const void* cos_sin_cache;  /* [max_pos, rot_dim], output dtype */
+  int head_size;              /* 64, 128 or 256 */
+  int rot_dim;                /* must equal head_size for the fused epilogue */
+  int rot_cols;               /* output columns [0, rot_cols) are q and k heads; the rest (v) pass through */
+  int is_neox;
+} sb200_rotary_args;
+
+/* out[T, N] = x[T, K] * w[N, K]^T: the local matmul of a ColumnParallelLinear /
+ * ReplicatedLinear shard (w is the nn.Linear weight [out_features/tp, in_features],
+ * row-major, used as is).  ldx / ldw / ldo are row strides in elements.
+ * bf16 / fp16 run on tcgen05 tensor cores with fp32 accumulation; fp32 runs a plain
+ * FFMA kernel and supports SB200_EPI_NONE only.
+ *   SB200_EPI_ROTARY   : additionally applies rotary_embedding to the q / k heads
+ *                        (out is the fused qkv buffer [T, N]).
+ *   SB200_EPI_SILU_MUL : w holds the gate shard in rows [0, N/2) and the up shard in
+ *                        rows [N/2, N); out is [T, N/2].
+ * status: optional device word that receives a non-zero code if a bounded
+ * pipeline wait inside the kernel ran out.  tile_n: 0 = choose, or 64/128/256.
+ * Replaces: ColumnParallelLinear.apply_weights / ReplicatedLinear.apply_weights
+ * (F.linear -> cuBLAS), sarathi/model_executor/parallel_utils/tensor_parallel/layers.py:278-284,516-518,
+ * and, with the fused epilogues, the rotary_embedding call of models/llama.py:176-177
+ * and the SiluAndMul call of models/llama.py:101-104. */
+int sb200_gemm_colpar(void* out, int64_t ldo, const void* x, int64_t ldx, const void* w, int64_t ldw,
+                      const void* bias, int64_t T, int64_t N, int64_t K, int dtype, int epilogue,
+                      const sb200_rotary_args* rot, uint32_t* status, int tile_n, sb200_stream_t stream);
+
+/* ------------------------------------------- tensor-parallel communication */
+
+/* One context per (process, GPU, TP group).  It owns a "symmetric heap" on the
+ * current device; after the handle exchange every rank's kernels can store
+ * into every other rank's heap over NVLink.  All ranks must issue the same
+ * sequence of sb200_all_reduce / sb200_gemm_rowpar calls with the same shapes.
+ * Replaces the NCCL communicator behind get_tensor_model_parallel_group()
+ * (sarathi/model_executor/parallel_utils/parallel_state.py:147-158,235-240) for
+ * the all-reduce of tensor_parallel/mappings.py:16-26. */
+typedef struct sb200_comm sb200_comm;
+#define SB200_IPC_HANDLE_BYTES 64
+
+/* Bytes of device memory a context with the given region size allocates. */
+int64_t sb200_comm_heap_bytes(int64_t region_bytes);
+/* Allocates (cudaMalloc) and zeroes the heap on the current device.  region_bytes
+ * must hold the largest [T, H] batch: T * H * sizeof(dtype), T rounded up to a
+ * multiple of `world`. */
+int sb200_comm_create(sb200_comm** out, int rank, int world, int64_t region_bytes);
+/* Same, over heaps the caller allocated, zeroed and peer-mapped itself
+ * (heaps[i] = address of rank i's heap in this process, sb200_comm_heap_bytes() each). */
+int sb200_comm_create_external(sb200_comm** out, int rank, int world, int64_t region_bytes, void* const* heaps);
+/* CUDA IPC handle (SB200_IPC_HANDLE_BYTES bytes, host memory) of this rank's heap. */
+int sb200_comm_ipc_handle(sb200_comm* comm, void* host_handle_out);
+/* host_handles: world * SB200_IPC_HANDLE_BYTES bytes, rank-major.  Maps every peer heap.
+ * The caller must run a host barrier across the ranks before the first collective. */
+int sb200_comm_open_peers(sb200_comm* comm, const void* host_handles);
+int sb200_comm_destroy(sb200_comm* comm);
+void* sb200_comm_local_heap(sb200_comm* comm);
+void* sb200_comm_scratch(sb200_comm* comm);
+int64_t sb200_comm_region_bytes(sb200_comm* comm);
+/* Limit of every device-side wait on a peer, in SM clock cycles (default ~2 s). */
+int sb200_comm_set_wait_limit(sb200_comm* comm, int64_t cycles);
+/* Synchronises `stream`, reads the context's device status word into *host_status and returns
+ * SB200_ERR_PEER_TIMEOUT if a bounded wait ran out since the last clear. */
+int sb200_comm_status(sb200_comm* comm, sb200_stream_t stream, uint32_t* host_status);
+int sb200_comm_clear_status(sb200_comm* comm, sb200_stream_t stream);
+
+/* Sum `in` [T, H] over the ranks; then, on the summed rows,
+ *   z = sum (+ bias) (+ residual);   y = norm_w ? rms_norm(z, norm_w, eps) : z.
+ * The primary result (y) lands in a context-owned buffer on EVERY rank
+ * (*out_ptr, valid until the second-next collective on this context) and, if
+ * out_copy != NULL, in that tensor.  With norm_w, z is also produced: in
+ * *resid_ptr / resid_copy (all rows if write_resid_all, else only this rank's rows
+ * [rank*ceil(T/world), ...)).  bias / residual / norm_w may be NULL.
+ * Replaces: reduce_from_tensor_model_parallel_region ->
+ * torch.distributed.all_reduce, tensor_parallel/mappings.py:16-26,270-271, plus the
+ * bias add of tensor_parallel/layers.py:448-453, the residual add of
+ * models/llama.py:248,254 and rms_norm (csrc/layernorm_kernels.cu:10-35). */
+int sb200_all_reduce(sb200_comm* comm, const void* in, int64_t T, int64_t H, int dtype, const void* bias,
+                     const void* residual, const void* norm_w, float eps, int write_resid_all,
+                     void* out_copy, void* resid_copy, sb200_stream_t stream, void** out_ptr, void** resid_ptr);
+
+/* Row-parallel projection fused with its all-reduce and the element-wise tail:
+ *   partial = x[T, K/tp] * w[N, K/tp]^T  (tcgen05, partial rows stored straight
+ *   into the owner rank's heap by the GEMM epilogue), then the reduce /
+ *   bias / residual / RMSNorm / broadcast phases of sb200_all_reduce in the same kernel.
+ * Arguments and results as sb200_all_reduce (H = N).
+ * Replaces: RowParallelLinear.forward (F.linear -> cuBLAS, then NCCL all-reduce),
+ * tensor_parallel/layers.py:421-454, with the same element-wise tail. */
+int sb200_gemm_rowpar(sb200_comm* comm, const void* x, int64_t ldx, const void* w, int64_t ldw, int64_t T,
+                      int64_t N, int64_t K, int dtype, const void* bias, const void* residual,
+                      const void* norm_w, float eps, int write_resid_all, void* out_copy, void* resid_copy,
+                      int tile_n, sb200_stream_t stream, void** out_ptr, void** resid_ptr);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* SARATHI_B200_H_ */

@@ -1,0 +1,155 @@
+"""Tensor-parallel communication context: symmetric device heaps mapped between
+the ranks of one node, and the collectives built on them (all-reduce and the
+row-parallel projection fused with its all-reduce, residual add and RMSNorm).
+
+torch.distributed is used only as plumbing: to exchange the 64-byte CUDA IPC
+handles once at construction and for the host barrier that follows.  The data
+path is this library's own kernels storing into peer memory over NVLink; NCCL
+is not called on it."""
+from __future__ import annotations
+
+import ctypes
+from typing import Optional, Tuple
+
+import torch
+
+from . import _native as N
+
+_STATUS_TEXT = {1: "GEMM pipeline barrier", 2: "partial rows from a peer never arrived",
+                3: "finished rows from a peer never arrived"}
+
+
+class _DeviceMemory:
+    """Exposes a raw device range through __cuda_array_interface__ so torch can view it."""
+
+    def __init__(self, ptr: int, nbytes: int):
+        self.__cuda_array_interface__ = {"shape": (nbytes,), "typestr": "|u1", "data": (ptr, False),
+                                         "version": 3, "strides": None}
+
+
+class TPComm:
+    """One per (process, GPU, tensor-parallel group).
+
+    ``region_bytes`` bounds the largest [T, H] batch a collective may carry
+    (T rounded up to a multiple of the group size)."""
+
+    def __init__(self, rank: int, world: int, region_bytes: int, group=None, device: Optional[torch.device] = None):
+        if not torch.cuda.is_available():
+            raise RuntimeError("TPComm needs a CUDA device (there is no CPU fallback)")
+        self.rank, self.world, self.group = rank, world, group
+        self.device = torch.device("cuda", torch.cuda.current_device()) if device is None else device
+        self._h = ctypes.c_void_p()
+        lib = N.lib()
+        with torch.cuda.device(self.device):
+            N.check(lib.sb200_comm_create(ctypes.byref(self._h), rank, world, int(region_bytes)), "comm_create")
+            if world > 1:
+                import torch.distributed as dist
+                mine = (ctypes.c_ubyte * 64)()
+                N.check(lib.sb200_comm_ipc_handle(self._h, mine), "comm_ipc_handle")
+                handles = [None] * world
+                dist.all_gather_object(handles, bytes(mine), group=group)
+                blob = b"".join(handles)
+                N.check(lib.sb200_comm_open_peers(self._h, blob), "comm_open_peers")
+                dist.barrier(group=group)
+        self.region_bytes = int(lib.sb200_comm_region_bytes(self._h))
+        heap_ptr = lib.sb200_comm_local_heap(self._h)
+        heap_bytes = int(lib.sb200_comm_heap_bytes(self.region_bytes))
+        self._heap = torch.as_tensor(_DeviceMemory(heap_ptr, heap_bytes), device=self.device)
+        self._heap_ptr = heap_ptr
+
+    # ------------------------------------------------------------------ utils
+    def close(self) -> None:
+        if self._h:
+            torch.cuda.synchronize(self.device)
+            N.lib().sb200_comm_destroy(self._h)
+            self._h = ctypes.c_void_p()
+            self._heap = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+    def set_wait_limit_cycles(self, cycles: int) -> None:
+        N.check(N.lib().sb200_comm_set_wait_limit(self._h, int(cycles)), "comm_set_wait_limit")
+
+    def check_status(self) -> None:
+        """Synchronises the current stream; raises if a device-side wait on a peer ran out."""
+        st = ctypes.c_uint32(0)
+        rc = N.lib().sb200_comm_status(self._h, N.stream_ptr(), ctypes.byref(st))
+        if rc != 0:
+            N.lib().sb200_comm_clear_status(self._h, N.stream_ptr())
+            N.check(rc, "tensor-parallel collective")
+
+    def status_code(self) -> int:
+        st = ctypes.c_uint32(0)
+        N.lib().sb200_comm_status(self._h, N.stream_ptr(), ctypes.byref(st))
+        return int(st.value)
+
+    def clear_status(self) -> None:
+        N.check(N.lib().sb200_comm_clear_status(self._h, N.stream_ptr()), "comm_clear_status")
+
+    def _view(self, ptr: Optional[int], T: int, H: int, dtype: torch.dtype) -> Optional[torch.Tensor]:
+        if not ptr:
+            return None
+        off = ptr - self._heap_ptr
+        nbytes = T * H * torch.empty((), dtype=dtype).element_size()
+        return self._heap[off:off + nbytes].view(dtype).view(T, H)
+
+    # ------------------------------------------------------------ collectives
+    def _tail_args(self, T, H, x_dtype, bias, residual, norm_weight, out, resid_out):
+        for name, t in (("bias", bias), ("norm_weight", norm_weight)):
+            if t is not None and (t.dtype != x_dtype or t.numel() != H or not t.is_contiguous()):
+                raise RuntimeError(f"{name} must be a contiguous [{H}] tensor of the activation dtype")
+        for name, t in (("residual", residual), ("out", out), ("resid_out", resid_out)):
+            if t is not None and (t.dtype != x_dtype or tuple(t.shape) != (T, H) or not t.is_contiguous()):
+                raise RuntimeError(f"{name} must be a contiguous [{T}, {H}] tensor of the activation dtype")
+
+    def all_reduce(self, x: torch.Tensor, *, bias=None, residual=None, norm_weight=None, eps: float = 0.0,
+                   resid_everywhere: bool = True, out=None, resid_out=None) -> Tuple[torch.Tensor, Optional[torch.Tensor]]:
+        """Sum x [T, H] over the group, then (+bias) (+residual) and an optional RMSNorm.
+
+        Returns (y, z): y = the primary result on every rank, z = the pre-norm sum
+        (only when norm_weight is given).  Without ``out`` / ``resid_out`` the results
+        are views into the context's heap, valid until the second-next collective."""
+        N.require_cuda(x, bias, residual, norm_weight, out, resid_out)
+        if x.dim() != 2 or not x.is_contiguous():
+            raise RuntimeError("all_reduce: input must be a contiguous [T, H] tensor")
+        T, H = x.shape
+        if T == 0:
+            return (x if out is None else out), None
+        self._tail_args(T, H, x.dtype, bias, residual, norm_weight, out, resid_out)
+        op, rp = ctypes.c_void_p(), ctypes.c_void_p()
+        N.check(N.lib().sb200_all_reduce(self._h, N.ptr(x), T, H, N.dtype_id(x), N.ptr(bias), N.ptr(residual),
+                                         N.ptr(norm_weight), float(eps), 1 if resid_everywhere else 0, N.ptr(out),
+                                         N.ptr(resid_out), N.stream_ptr(), ctypes.byref(op), ctypes.byref(rp)),
+                "all_reduce")
+        y = out if out is not None else self._view(op.value, T, H, x.dtype)
+        z = resid_out if resid_out is not None else self._view(rp.value, T, H, x.dtype)
+        return y, (z if norm_weight is not None else None)
+
+    def rowpar_linear(self, x: torch.Tensor, weight: torch.Tensor, *, bias=None, residual=None, norm_weight=None,
+                      eps: float = 0.0, resid_everywhere: bool = True, out=None, resid_out=None,
+                      tile_n: int = 0) -> Tuple[torch.Tensor, Optional[torch.Tensor]]:
+        """(x[T, K/tp] @ weight[N, K/tp]^T) summed over the group, with the same tail
+        and result conventions as ``all_reduce`` -- one kernel for bf16/fp16."""
+        N.require_cuda(x, weight, bias, residual, norm_weight, out, resid_out)
+        if x.dim() != 2 or x.stride(1) != 1 or weight.dim() != 2 or weight.stride(1) != 1:
+            raise RuntimeError("rowpar_linear: x and weight must be 2-D with unit inner stride")
+        if weight.shape[1] != x.shape[1] or weight.dtype != x.dtype:
+            raise RuntimeError("rowpar_linear: weight does not match the input")
+        T, K = x.shape
+        H = weight.shape[0]
+        if T == 0:
+            return torch.empty(0, H, dtype=x.dtype, device=x.device), None
+        self._tail_args(T, H, x.dtype, bias, residual, norm_weight, out, resid_out)
+        op, rp = ctypes.c_void_p(), ctypes.c_void_p()
+        N.check(N.lib().sb200_gemm_rowpar(self._h, N.ptr(x), x.stride(0), N.ptr(weight), weight.stride(0), T, H, K,
+                                          N.dtype_id(x), N.ptr(bias), N.ptr(residual), N.ptr(norm_weight),
+                                          float(eps), 1 if resid_everywhere else 0, N.ptr(out), N.ptr(resid_out),
+                                          tile_n, N.stream_ptr(), ctypes.byref(op), ctypes.byref(rp)),
+                "gemm_rowpar")
+        y = out if out is not None else self._view(op.value, T, H, x.dtype)
+        z = resid_out if resid_out is not None else self._view(rp.value, T, H, x.dtype)
+        return y, (z if norm_weight is not None else None)

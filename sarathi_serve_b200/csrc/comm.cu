@@ -1,0 +1,322 @@
+// Tensor-parallel communication context (symmetric heaps mapped between the
+// ranks of one node), the standalone all-reduce built on the push / reduce /
+// finish phases of comm.cuh, and the row-parallel projection entry point that
+// runs the same phases inside the GEMM kernel.
+//
+// Replaces the all-reduce call site of the reference,
+// tensor_parallel/mappings.py:16-26 (torch.distributed.all_reduce over NCCL),
+// and the sequence RowParallelLinear.forward -> all_reduce -> (+bias) ->
+// residual add -> RMSNorm (tensor_parallel/layers.py:425-454,
+// models/llama.py:248-254, csrc/layernorm_kernels.cu:10-35).
+#include "gemm_host.cuh"
+
+#include <new>
+#include <string.h>
+
+struct sb200_comm {
+  int rank, world, device;
+  size_t region_bytes, heap_bytes;
+  void* heap[sb200::kMaxRanks];
+  bool own_heap;
+  bool ipc_opened[sb200::kMaxRanks];
+  uint32_t push_total[2], done_total[2];
+  uint64_t seq;
+  long long wait_cycles;
+};
+
+namespace sb200 {
+
+constexpr size_t kCounterBytes = 4096;
+constexpr int kRegions = 7;  // partial[2], out[2], resid[2], scratch
+
+static size_t round_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
+
+static CommView make_view(const sb200_comm* c) {
+  CommView v = {};
+  v.rank = c->rank;
+  v.world = c->world;
+  for (int i = 0; i < c->world; ++i) v.heap[i] = (char*)c->heap[i];
+  size_t off = kCounterBytes;
+  v.partial_off[0] = off; off += c->region_bytes;
+  v.partial_off[1] = off; off += c->region_bytes;
+  v.out_off[0] = off; off += c->region_bytes;
+  v.out_off[1] = off; off += c->region_bytes;
+  v.resid_off[0] = off; off += c->region_bytes;
+  v.resid_off[1] = off; off += c->region_bytes;
+  v.region_bytes = c->region_bytes;
+  return v;
+}
+static size_t scratch_off(const sb200_comm* c) { return kCounterBytes + 6 * c->region_bytes; }
+
+// Standalone all-reduce: push rows of a local tensor, then the shared phases.
+template <typename T>
+__global__ void __launch_bounds__(256)
+all_reduce_kernel(const CommView c, const ReduceArgs a, const T* __restrict__ in) {
+  constexpr int N = Vec16<T>::N;
+  const int nvec = a.H / N;
+  const size_t total = (size_t)a.T * nvec;
+  const size_t stride = (size_t)gridDim.x * blockDim.x;
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += stride) {
+    const int t = (int)(i / nvec), v = (int)(i - (size_t)t * nvec);
+    const int owner = t / a.rows_per_rank, lr = t - owner * a.rows_per_rank;
+    T* dst = (T*)(c.heap[owner] + c.partial_off[a.set]) + ((size_t)c.rank * a.rows_per_rank + lr) * a.H + (size_t)v * N;
+    st16(dst, ld16(in + i * N));
+  }
+  __threadfence_system();
+  __syncthreads();
+  if (threadIdx.x < c.world) red_release_sys_add(comm_counter(c, threadIdx.x, CC_PUSH0 + a.set), 1u);
+  const int warps = blockDim.x / 32;
+  reduce_phase<T>(c, a, blockIdx.x * warps + (threadIdx.x >> 5), gridDim.x * warps);
+  if (a.out_copy || a.resid_copy || blockIdx.x == 0) {
+    if (finish_phase(c, a) && (a.out_copy || a.resid_copy))
+      copy_out_phase<T>(c, a, blockIdx.x * blockDim.x + threadIdx.x, gridDim.x * blockDim.x);
+  }
+}
+
+static int all_reduce_grid(int64_t T_, int64_t H, int dtype, int rows_per_rank) {
+  const int64_t nvec = H / (16 / (int64_t)dtype_size(dtype));
+  int64_t g = (T_ * nvec + 1023) / 1024;
+  const int64_t by_rows = (rows_per_rank + 7) / 8;
+  if (g < by_rows) g = by_rows;
+  if (g > sm_count()) g = sm_count();
+  if (g < 1) g = 1;
+  return (int)g;
+}
+
+struct CallPlan {
+  ReduceArgs ra;
+  CommView cv;
+};
+
+// Common argument checks + per-call bookkeeping.  `pushes_to_me` is what every
+// rank adds to this rank's push counter during the call.
+static int plan_call(sb200_comm* c, int64_t T_, int64_t H, int dtype, const void* bias, const void* residual,
+                     const void* norm_w, float eps, int write_resid_all, void* out_copy, void* resid_copy,
+                     CallPlan* p) {
+  SB_CHECK_ARG(c != nullptr, "null communication context");
+  const size_t es = dtype_size(dtype);
+  SB_CHECK_ARG(T_ > 0 && H > 0 && T_ <= INT32_MAX && H <= INT32_MAX, "bad shape T=%lld H=%lld", (long long)T_, (long long)H);
+  SB_CHECK_ARG((H * es) % 16 == 0, "row length %lld is not a multiple of 16 bytes", (long long)H);
+  const int rpr = (int)((T_ + c->world - 1) / c->world);
+  SB_CHECK_ARG((size_t)T_ * H * es <= c->region_bytes && (size_t)rpr * c->world * H * es <= c->region_bytes,
+               "batch of %lld x %lld elements exceeds the context's region size (%zu bytes)", (long long)T_,
+               (long long)H, c->region_bytes);
+  SB_CHECK_ARG((!bias || aligned16(bias)) && (!residual || aligned16(residual)) && (!norm_w || aligned16(norm_w)) &&
+                   (!out_copy || aligned16(out_copy)) && (!resid_copy || aligned16(resid_copy)),
+               "bias / residual / norm weight / output tensors must be 16-byte aligned");
+  int dev = -1;
+  SB_CUDA(cudaGetDevice(&dev));
+  SB_CHECK_ARG(dev == c->device, "current device %d is not the context's device %d", dev, c->device);
+  ReduceArgs& a = p->ra;
+  a = ReduceArgs{};
+  a.T = (int)T_; a.H = (int)H; a.rows_per_rank = rpr;
+  a.set = (int)(c->seq & 1);
+  a.bias = bias; a.residual = residual; a.norm_w = norm_w; a.eps = eps;
+  a.write_resid_all = write_resid_all;
+  a.out_copy = out_copy; a.resid_copy = resid_copy;
+  a.wait_cycles = c->wait_cycles;
+  p->cv = make_view(c);
+  return SB200_OK;
+}
+
+static void commit_call(sb200_comm* c, CallPlan* p, uint32_t pushes_to_me, void** out_ptr, void** resid_ptr) {
+  const int set = p->ra.set;
+  c->push_total[set] += pushes_to_me;
+  c->done_total[set] += (uint32_t)p->ra.T;
+  p->ra.push_target = c->push_total[set];
+  p->ra.done_target = c->done_total[set];
+  if (out_ptr) *out_ptr = (char*)c->heap[c->rank] + p->cv.out_off[set];
+  if (resid_ptr) *resid_ptr = p->ra.norm_w ? (void*)((char*)c->heap[c->rank] + p->cv.resid_off[set]) : nullptr;
+  c->seq++;
+}
+
+template <typename T>
+static int launch_all_reduce(const CallPlan& p, const void* in, int grid, cudaStream_t s) {
+  all_reduce_kernel<T><<<grid, 256, 0, s>>>(p.cv, p.ra, (const T*)in);
+  SB_CHECK_LAUNCH("all_reduce_kernel");
+  return SB200_OK;
+}
+
+static int do_all_reduce(sb200_comm* c, const void* in, int64_t T_, int64_t H, int dtype, const void* bias,
+                         const void* residual, const void* norm_w, float eps, int write_resid_all, void* out_copy,
+                         void* resid_copy, cudaStream_t s, void** out_ptr, void** resid_ptr) {
+  CallPlan p;
+  int rc = plan_call(c, T_, H, dtype, bias, residual, norm_w, eps, write_resid_all, out_copy, resid_copy, &p);
+  if (rc) return rc;
+  SB_CHECK_ARG(in && aligned16(in), "all_reduce: input must be a 16-byte aligned device pointer");
+  const int grid = all_reduce_grid(T_, H, dtype, p.ra.rows_per_rank);
+  commit_call(c, &p, (uint32_t)(c->world * grid), out_ptr, resid_ptr);
+  SB_DISPATCH_FLOAT(dtype, return (launch_all_reduce<scalar_t>(p, in, grid, s)));
+  return SB200_OK;
+}
+
+}  // namespace sb200
+
+using namespace sb200;
+
+extern "C" int64_t sb200_comm_heap_bytes(int64_t region_bytes) {
+  return (int64_t)(kCounterBytes + kRegions * round_up((size_t)region_bytes, 1024));
+}
+
+static int comm_new(sb200_comm** out, int rank, int world, int64_t region_bytes) {
+  SB_CHECK_ARG(out != nullptr, "comm_create: null output");
+  SB_CHECK_ARG(world >= 1 && world <= kMaxRanks && rank >= 0 && rank < world, "comm_create: bad rank %d / world %d (max %d ranks)",
+               rank, world, kMaxRanks);
+  SB_CHECK_ARG(region_bytes > 0, "comm_create: region_bytes must be positive");
+  sb200_comm* c = new (std::nothrow) sb200_comm();
+  SB_CHECK_ARG(c != nullptr, "comm_create: out of host memory");
+  memset(c, 0, sizeof(*c));
+  c->rank = rank; c->world = world;
+  c->region_bytes = round_up((size_t)region_bytes, 1024);
+  c->heap_bytes = kCounterBytes + kRegions * c->region_bytes;
+  c->wait_cycles = ptx::kWaitLimitCycles;
+  if (cudaGetDevice(&c->device) != cudaSuccess) { delete c; set_error("comm_create: no current CUDA device"); return SB200_ERR_CUDA; }
+  *out = c;
+  return SB200_OK;
+}
+
+extern "C" int sb200_comm_create(sb200_comm** out, int rank, int world, int64_t region_bytes) {
+  int rc = comm_new(out, rank, world, region_bytes);
+  if (rc) return rc;
+  sb200_comm* c = *out;
+  void* p = nullptr;
+  cudaError_t e = cudaMalloc(&p, c->heap_bytes);
+  if (e == cudaSuccess) e = cudaMemset(p, 0, c->heap_bytes);
+  if (e == cudaSuccess) e = cudaDeviceSynchronize();
+  if (e != cudaSuccess) {
+    if (p) cudaFree(p);
+    delete c; *out = nullptr;
+    return cuda_fail(e, "comm_create: allocating the symmetric heap");
+  }
+  c->heap[rank] = p;
+  c->own_heap = true;
+  return SB200_OK;
+}
+
+extern "C" int sb200_comm_create_external(sb200_comm** out, int rank, int world, int64_t region_bytes,
+                                          void* const* heaps) {
+  SB_CHECK_ARG(heaps != nullptr, "comm_create_external: null heap table");
+  int rc = comm_new(out, rank, world, region_bytes);
+  if (rc) return rc;
+  sb200_comm* c = *out;
+  for (int i = 0; i < world; ++i) {
+    if (!heaps[i] || !aligned16(heaps[i])) { delete c; *out = nullptr; set_error("comm_create_external: heap %d is null or misaligned", i); return SB200_ERR_INVALID_ARGUMENT; }
+    c->heap[i] = heaps[i];
+  }
+  c->own_heap = false;
+  return SB200_OK;
+}
+
+extern "C" int sb200_comm_ipc_handle(sb200_comm* c, void* handle_out) {
+  SB_CHECK_ARG(c && handle_out && c->own_heap, "comm_ipc_handle: context does not own its heap");
+  static_assert(sizeof(cudaIpcMemHandle_t) == SB200_IPC_HANDLE_BYTES, "IPC handle size");
+  cudaIpcMemHandle_t h;
+  SB_CUDA(cudaIpcGetMemHandle(&h, c->heap[c->rank]));
+  memcpy(handle_out, &h, sizeof(h));
+  return SB200_OK;
+}
+
+extern "C" int sb200_comm_open_peers(sb200_comm* c, const void* handles) {
+  SB_CHECK_ARG(c && handles && c->own_heap, "comm_open_peers: bad arguments");
+  for (int i = 0; i < c->world; ++i) {
+    if (i == c->rank || c->heap[i]) continue;
+    cudaIpcMemHandle_t h;
+    memcpy(&h, (const char*)handles + (size_t)i * sizeof(h), sizeof(h));
+    void* p = nullptr;
+    SB_CUDA(cudaIpcOpenMemHandle(&p, h, cudaIpcMemLazyEnablePeerAccess));
+    c->heap[i] = p;
+    c->ipc_opened[i] = true;
+  }
+  return SB200_OK;
+}
+
+extern "C" int sb200_comm_destroy(sb200_comm* c) {
+  if (!c) return SB200_OK;
+  for (int i = 0; i < c->world; ++i)
+    if (c->ipc_opened[i] && c->heap[i]) cudaIpcCloseMemHandle(c->heap[i]);
+  if (c->own_heap && c->heap[c->rank]) cudaFree(c->heap[c->rank]);
+  delete c;
+  return SB200_OK;
+}
+
+extern "C" void* sb200_comm_local_heap(sb200_comm* c) { return c ? c->heap[c->rank] : nullptr; }
+extern "C" void* sb200_comm_scratch(sb200_comm* c) { return c ? (char*)c->heap[c->rank] + scratch_off(c) : nullptr; }
+extern "C" int64_t sb200_comm_region_bytes(sb200_comm* c) { return c ? (int64_t)c->region_bytes : 0; }
+
+extern "C" int sb200_comm_set_wait_limit(sb200_comm* c, int64_t cycles) {
+  SB_CHECK_ARG(c && cycles > 0, "comm_set_wait_limit: bad arguments");
+  c->wait_cycles = cycles;
+  return SB200_OK;
+}
+
+extern "C" int sb200_comm_status(sb200_comm* c, sb200_stream_t stream, uint32_t* host_status) {
+  SB_CHECK_ARG(c && host_status, "comm_status: bad arguments");
+  uint32_t* w = reinterpret_cast<uint32_t*>(c->heap[c->rank]) + CC_STATUS;
+  SB_CUDA(cudaMemcpyAsync(host_status, w, sizeof(uint32_t), cudaMemcpyDeviceToHost, (cudaStream_t)stream));
+  SB_CUDA(cudaStreamSynchronize((cudaStream_t)stream));
+  if (*host_status != 0) {
+    set_error("device-side wait timed out (code %u: %s)", *host_status,
+              *host_status == CS_TIMEOUT_MBARRIER ? "GEMM pipeline barrier"
+              : *host_status == CS_TIMEOUT_PUSH   ? "partial rows from a peer did not arrive"
+                                                  : "finished rows from a peer did not arrive");
+    return SB200_ERR_PEER_TIMEOUT;
+  }
+  return SB200_OK;
+}
+
+extern "C" int sb200_comm_clear_status(sb200_comm* c, sb200_stream_t stream) {
+  SB_CHECK_ARG(c, "comm_clear_status: null context");
+  uint32_t* w = reinterpret_cast<uint32_t*>(c->heap[c->rank]) + CC_STATUS;
+  SB_CUDA(cudaMemsetAsync(w, 0, sizeof(uint32_t), (cudaStream_t)stream));
+  return SB200_OK;
+}
+
+extern "C" int sb200_all_reduce(sb200_comm* comm, const void* in, int64_t T, int64_t H, int dtype, const void* bias,
+                                const void* residual, const void* norm_w, float eps, int write_resid_all,
+                                void* out_copy, void* resid_copy, sb200_stream_t stream, void** out_ptr,
+                                void** resid_ptr) {
+  return do_all_reduce(comm, in, T, H, dtype, bias, residual, norm_w, eps, write_resid_all, out_copy, resid_copy,
+                       (cudaStream_t)stream, out_ptr, resid_ptr);
+}
+
+extern "C" int sb200_gemm_rowpar(sb200_comm* comm, const void* x, int64_t ldx, const void* w, int64_t ldw, int64_t T,
+                                 int64_t N, int64_t K, int dtype, const void* bias, const void* residual,
+                                 const void* norm_w, float eps, int write_resid_all, void* out_copy, void* resid_copy,
+                                 int tile_n, sb200_stream_t stream, void** out_ptr, void** resid_ptr) {
+  SB_CHECK_ARG(comm && x && w, "gemm_rowpar: null pointer");
+  SB_CHECK_ARG(T > 0 && N > 0 && K > 0 && K <= INT32_MAX, "gemm_rowpar: bad shape T=%lld N=%lld K=%lld", (long long)T,
+               (long long)N, (long long)K);
+  cudaStream_t s = (cudaStream_t)stream;
+  if (dtype == SB200_F32) {
+    // fp32: FFMA GEMM into the context's scratch region, then the standalone all-reduce phases.
+    SB_CHECK_ARG((size_t)T * N * 4 <= comm->region_bytes, "gemm_rowpar: batch exceeds the context's region size");
+    float* tmp = (float*)sb200_comm_scratch(comm);
+    int rc = run_gemm_f32(tmp, N, (const float*)x, ldx, (const float*)w, ldw, nullptr, (int)T, (int)N, (int)K, s);
+    if (rc) return rc;
+    return do_all_reduce(comm, tmp, T, N, dtype, bias, residual, norm_w, eps, write_resid_all, out_copy, resid_copy,
+                         s, out_ptr, resid_ptr);
+  }
+  CallPlan p;
+  int rc = plan_call(comm, T, N, dtype, bias, residual, norm_w, eps, write_resid_all, out_copy, resid_copy, &p);
+  if (rc) return rc;
+  SB_CHECK_ARG(N % 8 == 0, "gemm_rowpar: output width must be a multiple of 8");
+  const int bn = choose_bn(EPI_PUSH, T, N, 0, tile_n);
+  SB_CHECK_ARG(bn != 0, "gemm_rowpar: bad tile width %d", tile_n);
+  const int n_tiles = (int)((N + bn - 1) / bn);
+  // pushes into this rank per call: every rank, every column tile, every (32-row group, me) overlap
+  const int rpr = p.ra.rows_per_rank;
+  const int64_t lo = (int64_t)comm->rank * rpr, hi = (lo + rpr < T ? lo + rpr : T);  // my rows [lo, hi)
+  uint32_t groups = 0;
+  if (hi > lo) groups = (uint32_t)((hi - 1) / 32 - lo / 32 + 1);
+  GemmArgs g = {};
+  g.M = (int)T; g.N = (int)N; g.K = (int)K;
+  g.head_size = 128;
+  // validate the operands before touching the epoch bookkeeping (a failed call must not desynchronise ranks)
+  CUtensorMap probe;
+  rc = make_tmap_2d(&probe, dtype, x, T, K, ldx, kBM, kBK);
+  if (rc) return rc;
+  rc = make_tmap_2d(&probe, dtype, w, N, K, ldw, bn, kBK);
+  if (rc) return rc;
+  commit_call(comm, &p, (uint32_t)comm->world * (uint32_t)n_tiles * groups, out_ptr, resid_ptr);
+  return run_gemm_sm100(dtype, EPI_PUSH, bn, x, ldx, w, ldw, g, p.cv, p.ra, s);
+}

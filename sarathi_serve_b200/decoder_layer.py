@@ -1,0 +1,144 @@
+"""The callers of the hot path: Llama-style attention / MLP / decoder-layer
+modules with the reference's constructor and forward signatures and parameter
+names (sarathi/model_executor/models/llama.py:60-106,109-188,191-255), built on
+this package's layers.
+
+``LlamaDecoderLayer.forward`` keeps the reference's contract
+(positions, hidden_states, layer_cache_idx, attention_backend_wrapper) ->
+hidden_states, and runs five kernels besides attention:
+    rms_norm | qkv GEMM + rotary | o_proj GEMM + all-reduce + residual + RMSNorm |
+    gate_up GEMM + SiLU*mul | down GEMM + all-reduce + residual.
+``forward_carry`` is the variant for a stack of layers: it takes the already
+normalised hidden states and the residual, and its last kernel also applies the
+NEXT layer's input RMSNorm, so a layer costs four kernels."""
+from __future__ import annotations
+
+from typing import Any, Dict, Optional, Tuple
+
+import torch
+import torch.nn as nn
+
+from . import parallel_state as ps
+from .nn_layers import RMSNorm, SiluAndMul, get_rope
+from .tp_layers import ColumnParallelLinear, RowParallelLinear
+
+
+class LlamaMLP(nn.Module):
+    def __init__(self, hidden_size: int, intermediate_size: int, hidden_act: str,
+                 layer_id: Optional[int] = None) -> None:
+        super().__init__()
+        self.gate_up_proj = ColumnParallelLinear(hidden_size, 2 * intermediate_size, bias=False, gather_output=False,
+                                                 perform_initialization=False, layer_id=layer_id)
+        self.down_proj = RowParallelLinear(intermediate_size, hidden_size, bias=False, input_is_parallel=True,
+                                           perform_initialization=False, layer_id=layer_id)
+        if hidden_act != "silu":
+            raise ValueError(f"Unsupported activation: {hidden_act}. Only silu is supported for now.")
+        self.act_fn = SiluAndMul()
+
+    def forward(self, x):
+        """Module-by-module path (three kernels + the all-reduce inside down_proj)."""
+        gate_up, _ = self.gate_up_proj(x)
+        x = self.act_fn(gate_up)
+        x, _ = self.down_proj(x)
+        return x
+
+
+class LlamaAttention(nn.Module):
+    def __init__(self, hidden_size: int, num_heads: int, num_kv_heads: int, rope_theta: float = 10000,
+                 rope_scaling: Optional[Dict[str, Any]] = None, max_position_embeddings: int = 8192,
+                 layer_id: Optional[int] = None) -> None:
+        super().__init__()
+        self.hidden_size = hidden_size
+        tp_size = ps.get_tensor_model_parallel_world_size()
+        self.total_num_heads = num_heads
+        assert self.total_num_heads % tp_size == 0
+        self.num_heads = self.total_num_heads // tp_size
+        self.total_num_kv_heads = num_kv_heads
+        assert self.total_num_kv_heads % tp_size == 0
+        self.num_kv_heads = self.total_num_kv_heads // tp_size
+        self.head_dim = hidden_size // self.total_num_heads
+        self.q_size = self.num_heads * self.head_dim
+        self.kv_size = self.num_kv_heads * self.head_dim
+        self.scaling = self.head_dim ** -0.5
+        self.rope_theta = rope_theta
+        self.max_position_embeddings = max_position_embeddings
+        self.layer_id = layer_id
+        self.qkv_proj = ColumnParallelLinear(hidden_size,
+                                             (self.total_num_heads + 2 * self.total_num_kv_heads) * self.head_dim,
+                                             bias=False, gather_output=False, perform_initialization=False,
+                                             layer_id=layer_id)
+        self.o_proj = RowParallelLinear(self.total_num_heads * self.head_dim, hidden_size, bias=False,
+                                        input_is_parallel=True, perform_initialization=False, layer_id=layer_id)
+        self.rotary_emb = get_rope(head_size=self.head_dim, rotary_dim=self.head_dim,
+                                   max_position=self.max_position_embeddings, base=self.rope_theta,
+                                   is_neox_style=True, rope_scaling=rope_scaling)
+
+    def qkv_rotary(self, positions: torch.Tensor, hidden_states: torch.Tensor):
+        """qkv projection with the rotary embedding fused into the GEMM epilogue; returns q, k, v views."""
+        qkv = self.qkv_proj.forward_rotary(hidden_states, positions, self.rotary_emb, self.q_size + self.kv_size)
+        return qkv.split([self.q_size, self.kv_size, self.kv_size], dim=-1)
+
+    def forward(self, positions: torch.Tensor, hidden_states: torch.Tensor, layer_cache_idx: int,
+                attention_backend_wrapper) -> torch.Tensor:
+        """Module-by-module path, as in the reference (llama.py:168-188)."""
+        qkv, _ = self.qkv_proj(hidden_states)
+        q, k, v = qkv.split([self.q_size, self.kv_size, self.kv_size], dim=-1)
+        q, k = self.rotary_emb(positions, q, k)
+        attn_output = attention_backend_wrapper.forward(q, k, v, layer_cache_idx, self.scaling, self.layer_id)
+        output, _ = self.o_proj(attn_output)
+        return output
+
+
+class LlamaDecoderLayer(nn.Module):
+    def __init__(self, config, layer_id: Optional[int] = None) -> None:
+        super().__init__()
+        self.hidden_size = config.hidden_size
+        rope_theta = getattr(config, "rope_theta", 10000)
+        rope_scaling = getattr(config, "rope_scaling", None)
+        max_position_embeddings = getattr(config, "max_position_embeddings", 8192)
+        self.self_attn = LlamaAttention(hidden_size=self.hidden_size, num_heads=config.num_attention_heads,
+                                        num_kv_heads=config.num_key_value_heads, rope_theta=rope_theta,
+                                        rope_scaling=rope_scaling, max_position_embeddings=max_position_embeddings,
+                                        layer_id=layer_id)
+        self.mlp = LlamaMLP(hidden_size=self.hidden_size, intermediate_size=config.intermediate_size,
+                            hidden_act=config.hidden_act, layer_id=layer_id)
+        self.input_layernorm = RMSNorm(config.hidden_size, eps=config.rms_norm_eps, layer_id=layer_id)
+        self.post_attention_layernorm = RMSNorm(config.hidden_size, eps=config.rms_norm_eps, layer_id=layer_id)
+
+    # ------------------------------------------------------------- unfused
+    def forward_unfused(self, positions, hidden_states, layer_cache_idx, attention_backend_wrapper) -> torch.Tensor:
+        """Op-for-op the reference's sequence (llama.py:232-255): every module called on its own."""
+        residual = hidden_states
+        hidden_states = self.input_layernorm(hidden_states)
+        hidden_states = self.self_attn(positions=positions, hidden_states=hidden_states,
+                                       layer_cache_idx=layer_cache_idx,
+                                       attention_backend_wrapper=attention_backend_wrapper)
+        hidden_states, residual = self.post_attention_layernorm.forward_add(hidden_states, residual)
+        hidden_states = self.mlp(hidden_states)
+        return residual + hidden_states
+
+    # --------------------------------------------------------------- fused
+    def _attn_mlp(self, positions, normed, residual, layer_cache_idx, attn, next_norm_weight, next_eps, out=None):
+        sa = self.self_attn
+        q, k, v = sa.qkv_rotary(positions, normed)
+        attn_out = attn.forward(q, k, v, layer_cache_idx, sa.scaling, sa.layer_id)
+        h, resid = sa.o_proj.forward_fused(attn_out, residual, self.post_attention_layernorm.weight.data,
+                                           self.post_attention_layernorm.variance_epsilon)
+        act = self.mlp.gate_up_proj.forward_silu_mul(h)
+        return self.mlp.down_proj.forward_fused(act, resid, next_norm_weight, next_eps, out=out)
+
+    def forward(self, positions: torch.Tensor, hidden_states: torch.Tensor, layer_cache_idx: int,
+                attention_backend_wrapper) -> torch.Tensor:
+        normed = self.input_layernorm(hidden_states)
+        out = torch.empty_like(hidden_states)  # caller-owned result, like the reference's
+        self._attn_mlp(positions, normed, hidden_states, layer_cache_idx, attention_backend_wrapper, None, 0.0,
+                       out=out)
+        return out
+
+    def forward_carry(self, positions: torch.Tensor, normed: torch.Tensor, residual: torch.Tensor,
+                      layer_cache_idx: int, attention_backend_wrapper, next_norm: RMSNorm
+                      ) -> Tuple[torch.Tensor, torch.Tensor]:
+        """(normed_l, residual_l) -> (normed_{l+1}, residual_{l+1}); ``next_norm`` is the following
+        layer's input_layernorm (or the model's final norm)."""
+        return self._attn_mlp(positions, normed, residual, layer_cache_idx, attention_backend_wrapper,
+                              next_norm.weight.data, next_norm.variance_epsilon)

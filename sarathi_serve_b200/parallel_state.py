@@ -1,0 +1,110 @@
+"""Tensor-parallel group bookkeeping with the accessor names the reference's
+layers read (sarathi/model_executor/parallel_utils/parallel_state.py:49-215,
+235-330,512-537).  Only the tensor-parallel group exists here: pipeline, data
+and embedding groups are outside this package's path."""
+from __future__ import annotations
+
+from typing import Optional
+
+import torch
+
+_TP_GROUP = None
+_TP_RANKS = None
+_TP_WORLD_SIZE_OVERRIDE: Optional[int] = None
+_TP_RANK_OVERRIDE: Optional[int] = None
+_TP_COMM = None
+_INITIALISED = False
+
+# Largest [T, H] batch (bytes) a collective of the shared context may carry.
+DEFAULT_COMM_REGION_BYTES = 64 << 20
+
+
+def initialize_model_parallel(tensor_model_parallel_size: int = 1, pipeline_model_parallel_size: int = 1,
+                              virtual_pipeline_model_parallel_size=None,
+                              pipeline_model_parallel_split_rank=None) -> None:
+    """Create the tensor-parallel group(s): consecutive blocks of ``tensor_model_parallel_size`` ranks
+    (reference: parallel_state.py:147-158).  Works without torch.distributed when the size is 1."""
+    global _TP_GROUP, _TP_RANKS, _INITIALISED
+    if pipeline_model_parallel_size != 1:
+        raise NotImplementedError("pipeline parallelism is outside the tensor-parallel decoder-layer path")
+    import torch.distributed as dist
+    if not dist.is_available() or not dist.is_initialized():
+        if tensor_model_parallel_size != 1:
+            raise RuntimeError("torch.distributed must be initialised for tensor_model_parallel_size > 1")
+        _TP_GROUP, _TP_RANKS, _INITIALISED = None, [0], True
+        return
+    world = dist.get_world_size()
+    if world % tensor_model_parallel_size != 0:
+        raise RuntimeError(f"world size {world} is not divisible by tensor parallel size {tensor_model_parallel_size}")
+    assert _TP_GROUP is None or not _INITIALISED, "tensor model parallel group is already initialized"
+    rank = dist.get_rank()
+    for i in range(world // tensor_model_parallel_size):
+        ranks = list(range(i * tensor_model_parallel_size, (i + 1) * tensor_model_parallel_size))
+        group = dist.new_group(ranks)
+        if rank in ranks:
+            _TP_GROUP, _TP_RANKS = group, ranks
+    _INITIALISED = True
+
+
+def model_parallel_is_initialized() -> bool:
+    return _INITIALISED
+
+
+def get_tensor_model_parallel_group():
+    assert _INITIALISED, "tensor model parallel group is not initialized"
+    return _TP_GROUP
+
+
+def set_tensor_model_parallel_world_size(world_size: Optional[int]) -> None:
+    global _TP_WORLD_SIZE_OVERRIDE
+    _TP_WORLD_SIZE_OVERRIDE = world_size
+
+
+def set_tensor_model_parallel_rank(rank: Optional[int]) -> None:
+    global _TP_RANK_OVERRIDE
+    _TP_RANK_OVERRIDE = rank
+
+
+def get_tensor_model_parallel_world_size() -> int:
+    if _TP_WORLD_SIZE_OVERRIDE is not None:
+        return _TP_WORLD_SIZE_OVERRIDE
+    if not _INITIALISED or _TP_GROUP is None:
+        return 1 if _TP_RANKS is None else len(_TP_RANKS)
+    import torch.distributed as dist
+    return dist.get_world_size(group=_TP_GROUP)
+
+
+def get_tensor_model_parallel_rank() -> int:
+    if _TP_RANK_OVERRIDE is not None:
+        return _TP_RANK_OVERRIDE
+    if not _INITIALISED or _TP_GROUP is None:
+        return 0
+    import torch.distributed as dist
+    return dist.get_rank(group=_TP_GROUP)
+
+
+def get_tensor_model_parallel_src_rank() -> int:
+    return 0 if _TP_RANKS is None else _TP_RANKS[0]
+
+
+def get_tensor_model_parallel_comm(region_bytes: Optional[int] = None):
+    """The process-wide communication context of the tensor-parallel group
+    (created on first use; every rank must reach this call together)."""
+    global _TP_COMM
+    if _TP_COMM is None:
+        from .comm import TPComm
+        _TP_COMM = TPComm(get_tensor_model_parallel_rank(), get_tensor_model_parallel_world_size(),
+                          region_bytes or DEFAULT_COMM_REGION_BYTES, group=_TP_GROUP)
+    elif region_bytes is not None and region_bytes > _TP_COMM.region_bytes:
+        raise RuntimeError(f"the tensor-parallel context was created with {_TP_COMM.region_bytes} byte regions; "
+                           f"{region_bytes} requested -- create it first with the larger size")
+    return _TP_COMM
+
+
+def destroy_model_parallel() -> None:
+    global _TP_GROUP, _TP_RANKS, _TP_COMM, _INITIALISED, _TP_WORLD_SIZE_OVERRIDE, _TP_RANK_OVERRIDE
+    if _TP_COMM is not None:
+        _TP_COMM.close()
+    _TP_GROUP = _TP_RANKS = _TP_COMM = None
+    _TP_WORLD_SIZE_OVERRIDE = _TP_RANK_OVERRIDE = None
+    _INITIALISED = False

@@ -1,0 +1,168 @@
+"""Generate golden fixtures by running the REFERENCE's own Python modules on CPU/gloo.
+
+    python tests/golden/make_golden.py [--reference /root/reference]
+
+The unmodified reference package is imported from its checkout (never copied).
+What it needs to run without a GPU is shimmed here:
+  * stub modules for plotting / sketch packages its metrics code imports;
+  * its four CUDA extension modules (`sarathi.layernorm_ops`, `activation_ops`,
+    `pos_encoding_ops`, `moe_ops`) are replaced by the CPU restatements in
+    oracle/tp_layer_oracle.py (those restatements are pinned separately, on the
+    GPU, against the reference's compiled kernels);
+  * `torch.cuda.current_device` -> "cpu" and `device="cuda"` -> "cpu" in
+    torch.arange, because the reference allocates on the current CUDA device;
+  * a disabled MetricsStore, a plain-namespace model config, and an attention
+    stand-in (attn_out = q after rotary; attention is outside the path).
+Everything else -- ColumnParallelLinear, RowParallelLinear, the all-reduce in
+mappings._reduce over a gloo group, RMSNorm, RotaryEmbedding (incl. its cos/sin
+cache), SiluAndMul, LlamaAttention, LlamaMLP, LlamaDecoderLayer -- is the
+reference's code.  Inputs come from sarathi_serve_b200.synthetic (seeded).
+
+Outputs: tests/golden/<case>_tp<world>.npz with rank 0's intermediates (16-bit
+tensors as raw int16 bit patterns).  Larger cases store a strided subset of rows
+plus float64 checksums (sum, sum |.|, sum of squares) of the full tensors.
+"""
+from __future__ import annotations
+
+import argparse
+import os
+import sys
+import types
+
+import numpy as np
+import torch
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+ROOT = os.path.dirname(os.path.dirname(HERE))
+sys.path.insert(0, ROOT)
+
+RUNS = [("mini_f32", 1), ("mini_f32", 2), ("mini_bf16", 1), ("mini_bf16", 2), ("mini_f16", 1), ("mini_f16", 2),
+        ("config1", 2)]
+ROW_SUBSET = {"config1": 18, "mini_f16": 4}  # keep every n-th row of the larger cases
+
+
+def _install_shims(reference: str) -> None:
+    sys.path.insert(0, reference)
+    from oracle import tp_layer_oracle as O
+
+    def stub(name, **attrs):
+        m = types.ModuleType(name)
+        m.__dict__.update(attrs)
+        sys.modules[name] = m
+        return m
+
+    stub("plotly"); stub("plotly.express"); stub("plotly_express")
+    stub("ddsketch"); stub("ddsketch.ddsketch", DDSketch=object)
+
+    def silu_and_mul(out, x): out.copy_(O.silu_and_mul(x))
+    def gelu_new(out, x): out.copy_(O.gelu_new(x))
+    def gelu_fast(out, x): out.copy_(O.gelu_fast(x))
+    def rms_norm(out, x, w, eps): out.copy_(O.rms_norm(x, w, eps))
+    def rotary_embedding(positions, q, k, head_size, cache, is_neox):
+        O.rotary_embedding(positions, q, k, head_size, cache, is_neox)
+
+    stub("sarathi.activation_ops", silu_and_mul=silu_and_mul, gelu_new=gelu_new, gelu_fast=gelu_fast)
+    stub("sarathi.layernorm_ops", rms_norm=rms_norm)
+    stub("sarathi.pos_encoding_ops", rotary_embedding=rotary_embedding)
+    stub("sarathi.moe_ops")
+    torch.cuda.current_device = lambda: "cpu"
+    _arange = torch.arange
+
+    def arange(*a, **k):
+        if k.get("device") == "cuda":
+            k["device"] = "cpu"
+        return _arange(*a, **k)
+
+    torch.arange = arange
+
+
+def _worker(rank: int, world: int, case_name: str, port: int, reference: str, out_path: str) -> None:
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    torch.set_num_threads(max(1, (os.cpu_count() or 2) // world))
+    import torch.distributed as dist
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    _install_shims(reference)
+    from sarathi_serve_b200 import synthetic as S
+    from sarathi.config import MetricsConfig
+    from sarathi.metrics.metrics_store import MetricsStore
+    MetricsStore.get_or_create_instance(None, None, MetricsConfig(write_metrics=False))
+    from sarathi.model_executor.parallel_utils import parallel_state as ps
+    ps.initialize_model_parallel(world, 1)
+    from sarathi.model_executor.attention.base_attention_wrapper import BaseAttentionWrapper
+    from sarathi.model_executor.models.llama import LlamaDecoderLayer
+
+    case = S.CASES[case_name]
+    torch.set_default_dtype(case.dtype)
+    layer = LlamaDecoderLayer(case.hf_config(), layer_id=0)
+    tensors = S.generate(case)
+    S.load_layer(layer, S.shard(tensors, rank, world))
+
+    captured = {}
+
+    def keep(name):
+        def hook(_m, _inp, outp):
+            t = outp[0] if isinstance(outp, tuple) else outp
+            captured[name] = t.detach().clone()
+        return hook
+
+    layer.input_layernorm.register_forward_hook(keep("input_norm"))
+    layer.self_attn.qkv_proj.register_forward_hook(keep("qkv_pre_rotary"))
+    layer.self_attn.o_proj.register_forward_hook(keep("o_proj"))
+    layer.post_attention_layernorm.register_forward_hook(keep("post_attn_norm"))
+    layer.mlp.gate_up_proj.register_forward_hook(keep("gate_up"))
+    layer.mlp.act_fn.register_forward_hook(keep("act"))
+    layer.mlp.down_proj.register_forward_hook(keep("down_proj"))
+
+    class Attn(BaseAttentionWrapper):
+        def __init__(self): pass
+        def init_gpu_cache(self, n): pass
+        def get_cache_block(self, n, **k): pass
+        def begin_forward(self, l): pass
+        def end_forward(self): pass
+        def forward(self, q, k, v, idx, softmax_scale=1.0, layer_id=None):
+            captured["q_rot"] = q.detach().clone()
+            captured["k_rot"] = k.detach().clone()
+            captured["v"] = v.detach().clone()
+            return q.contiguous()
+
+    with torch.inference_mode():
+        out = layer(tensors.positions, tensors.x.to(case.dtype).clone(), 0, Attn())
+    captured["out"] = out.clone()
+    captured["cos_sin_cache"] = layer.self_attn.rotary_emb.cos_sin_cache.clone()
+    if rank == 0:
+        step = ROW_SUBSET.get(case_name, 1)
+        arrays = {}
+        for name, t in captured.items():
+            if name == "cos_sin_cache":
+                t = torch.cat([t[:24], t[-8:]])  # a few table rows are enough to pin the cache builder
+            else:
+                tf = t.double()
+                arrays[f"{name}__sum"] = np.array([tf.sum().item(), tf.abs().sum().item(), tf.pow(2).sum().item()])
+                t = t[::step]
+            # 16-bit dtypes are stored as their raw bit patterns (exact, half the size of fp32)
+            arrays[name] = t.contiguous().view(torch.int16).numpy() if t.element_size() == 2 else t.numpy()
+        arrays["__row_step"] = np.array([step])
+        arrays["__dtype"] = np.array([str(case.dtype)])
+        np.savez_compressed(out_path, **arrays)
+        print(f"wrote {out_path} ({os.path.getsize(out_path) / 1024:.0f} KiB)")
+    dist.destroy_process_group()
+
+
+def main() -> None:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--reference", default="/root/reference")
+    ap.add_argument("--only", default=None)
+    a = ap.parse_args()
+    import torch.multiprocessing as mp
+    port = 29610
+    for case_name, world in RUNS:
+        if a.only and a.only != case_name:
+            continue
+        out_path = os.path.join(HERE, f"{case_name}_tp{world}.npz")
+        mp.spawn(_worker, args=(world, case_name, port, a.reference, out_path), nprocs=world)
+        port += 1
+
+
+if __name__ == "__main__":
+    main()

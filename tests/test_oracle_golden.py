@@ -1,0 +1,59 @@
+"""The CPU oracle against fixtures produced by the reference's own Python layer
+code (tests/golden/make_golden.py).  Pins oracle/tp_layer_oracle.decoder_layer."""
+import pytest
+import torch
+
+from helpers import TOL, load_golden, rel_err
+from oracle import tp_layer_oracle as O
+from sarathi_serve_b200 import synthetic as S
+
+RUNS = [("mini_f32", 1), ("mini_f32", 2), ("mini_bf16", 1), ("mini_bf16", 2), ("mini_f16", 1), ("mini_f16", 2),
+        ("config1", 2)]
+NAMES = ["input_norm", "qkv_pre_rotary", "o_proj", "post_attn_norm", "gate_up", "act", "down_proj", "out"]
+
+
+def run_oracle(case_name, world):
+    case = S.CASES[case_name]
+    t = S.generate(case)
+    params = [S.shard(t, r, world) for r in range(world)]
+    cache = O.cos_sin_cache(case.head_dim, case.head_dim, case.max_position, case.rope_theta, case.dtype)
+    out = O.decoder_layer(params, t.x.to(case.dtype), t.positions, num_heads=case.num_heads,
+                          num_kv_heads=case.num_kv_heads, head_dim=case.head_dim, eps=case.rms_norm_eps, cache=cache)
+    return case, out, cache
+
+
+@pytest.mark.parametrize("case_name,world", RUNS)
+def test_oracle_matches_reference_layer(case_name, world):
+    gold, sums, step, dtype = load_golden(case_name, world)
+    case, out, cache = run_oracle(case_name, world)
+    nq = case.num_heads // world * case.head_dim
+    nkv = case.num_kv_heads // world * case.head_dim
+    out["q_rot"], out["k_rot"], out["v"] = out["qkv"].split([nq, nkv, nkv], dim=-1)
+    # The oracle repeats the reference's op sequence with the same CPU kernels: the only
+    # freedom is the GEMM blocking of differently shaped calls, so allow a few ulps.
+    tol = {torch.float32: 2e-6, torch.bfloat16: 1e-2, torch.float16: 2e-3}[dtype]
+    for name in NAMES + ["q_rot", "k_rot", "v"]:
+        got = out[name]
+        assert rel_err(got[::step], gold[name]) <= tol, name
+        s = got.double()
+        ref = sums[name]
+        assert abs(s.sum().item() - ref[0]) <= 1e-3 * max(1.0, ref[1]) * (tol * 50), name
+        assert abs(s.pow(2).sum().item() - ref[2]) <= ref[2] * tol * 50 + 1e-9, name
+
+
+@pytest.mark.parametrize("case_name", ["mini_f32", "mini_bf16", "mini_f16", "config1"])
+def test_cos_sin_cache_matches_reference(case_name):
+    world = 2 if case_name == "config1" else 1
+    gold, _, _, dtype = load_golden(case_name, world)
+    case = S.CASES[case_name]
+    cache = O.cos_sin_cache(case.head_dim, case.head_dim, case.max_position, case.rope_theta, case.dtype)
+    got = torch.cat([cache[:24], cache[-8:]])
+    assert torch.equal(got.view(torch.int16) if got.element_size() == 2 else got,
+                       gold["cos_sin_cache"].view(torch.int16) if got.element_size() == 2 else gold["cos_sin_cache"])
+
+
+def test_tp_invariance():
+    """TP=1 and TP=2 of the oracle agree (fp32: summation order only)."""
+    _, o1, _ = run_oracle("mini_f32", 1)
+    _, o2, _ = run_oracle("mini_f32", 2)
+    assert rel_err(o2["out"], o1["out"]) < 1e-5
