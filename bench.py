@@ -1,0 +1,340 @@
+#!/usr/bin/env python
+"""Benchmark of the tensor-parallel decoder-layer path.
+
+    python bench.py --gpus N --steps K --warmup W            # this library, TP = N
+    python bench.py --impl reference --gpus N --steps K ...  # CPU arm (oracle port of the reference path)
+
+A step = one Llama-3-8B-shaped decoder layer (BASELINE config 2: hidden 4096,
+32 q / 8 kv heads, head_dim 128, intermediate 14336, bf16) over one Sarathi
+mixed chunk of 512 tokens (448 prefill + 64 decode), tensor-parallel over N
+GPUs, attention replaced by the stand-in attn_out = q (attention is outside
+the path).  Inputs are seeded synthetic tensors (sarathi_serve_b200.synthetic).
+
+`value`   : tokens/s of the device-resident layer (4 kernels per step: qkv GEMM+rotary,
+            o_proj GEMM+all-reduce+residual+RMSNorm, gate_up GEMM+SiLU*mul,
+            down GEMM+all-reduce+residual+next RMSNorm), CUDA-event timed, max over ranks.
+`e2e`     : tokens/s through the public layer API with HOST buffers: pinned H2D of the
+            hidden states and positions, LlamaDecoderLayer.forward, D2H of the result, every step.
+`roofline`: the dominant kernel (gate_up GEMM + SiLU*mul), timed alone with CUDA events.
+Weights of several distinct layers are cycled so that each step's operands exceed the L2.
+One JSON line is printed by rank 0.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+METRIC = "tp_decoder_layer_tokens_per_s"
+UNIT = "tokens/s"
+L2_BYTES = 126 << 20
+
+
+def parse():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=200)
+    ap.add_argument("--warmup", type=int, default=20)
+    ap.add_argument("--impl", default="native", choices=["native", "reference"])
+    ap.add_argument("--workload", default="config2")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--cpu-baseline-seconds", type=float, default=15.0)
+    return ap.parse_args()
+
+
+def peaks():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        with open(p) as fh:
+            d = json.load(fh)
+        return d.get("bf16_tflops", 1590.0), d.get("hbm_gbs", 6650.0), "measured"
+    return 1590.0, 6650.0, "fallback"
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+         "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index, self.rows, self.proc = index, [], None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
+                                          "-i", str(self.index), "-lms", "100"], stdout=subprocess.PIPE,
+                                         stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([c.strip() for c in line.split(",")])
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.15)
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=2)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        sm, mx, reasons = [], [], set()
+        for r in self.rows:
+            try:
+                sm.append(float(r[1])); mx.append(float(r[2]))
+            except (ValueError, IndexError):
+                continue
+            for name, col in (("hw_slowdown", 5), ("hw_thermal_slowdown", 6), ("sw_thermal_slowdown", 7),
+                              ("sw_power_cap", 8)):
+                if len(r) > col and r[col].lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "samples": len(sm), "reasons": sorted(reasons)}
+
+
+# ------------------------------------------------------------------ CPU arm
+def cpu_layer_runner(case, threads: int):
+    """Returns (fn, tokens): fn() runs the oracle port of the reference layer path once on the CPU."""
+    import torch
+    from oracle import tp_layer_oracle as O
+    from sarathi_serve_b200 import synthetic as S
+    torch.set_num_threads(threads)
+    t = S.generate(case)
+    params = [S.shard(t, 0, 1)]
+    cache = O.cos_sin_cache(case.head_dim, case.head_dim, case.max_position, case.rope_theta, case.dtype)
+    x = t.x.to(case.dtype)
+
+    def fn():
+        with torch.inference_mode():
+            return O.decoder_layer(params, x, t.positions, num_heads=case.num_heads, num_kv_heads=case.num_kv_heads,
+                                   head_dim=case.head_dim, eps=case.rms_norm_eps, cache=cache)["out"]
+    return fn, case.num_tokens
+
+
+def time_cpu(case, budget_s: float, warmup: int = 1, max_iters: int = 50, min_iters: int = 2):
+    threads = os.cpu_count() or 1
+    fn, tokens = cpu_layer_runner(case, threads)
+    for _ in range(warmup):
+        fn()
+    times = []
+    t_end = time.perf_counter() + budget_s
+    while len(times) < max_iters and (len(times) < min_iters or time.perf_counter() < t_end):
+        t0 = time.perf_counter()
+        fn()
+        times.append(time.perf_counter() - t0)
+    med = statistics.median(times)
+    return tokens / med, threads, len(times), med
+
+
+def run_reference_arm(a):
+    """The reference's path on the host cores: the oracle port (torch CPU kernels, bf16, all host
+    threads) of LlamaDecoderLayer over the same workload; rank 0 only."""
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    from sarathi_serve_b200 import synthetic as S
+    case = S.CASES[a.workload]
+    threads = os.cpu_count() or 1
+    fn, tokens = cpu_layer_runner(case, threads)
+    steps = max(1, min(a.steps, 20))
+    warm = max(1, min(a.warmup, 3))
+    for _ in range(warm):
+        fn()
+    t0 = time.perf_counter()
+    for _ in range(steps):
+        fn()
+    dt = (time.perf_counter() - t0) / steps
+    v = tokens / dt
+    line = {"metric": METRIC, "value": v, "unit": UNIT, "n_gpus": a.gpus, "steps": steps, "warmup": warm,
+            "ms_per_step": dt * 1e3, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+            "dtype": "bf16", "data": "synthetic", "impl": "reference",
+            "config": {"workload": f"{a.workload}: Llama-3-8B-shaped decoder layer, 512-token mixed chunk "
+                                   "(448 prefill + 64 decode), oracle port of the reference layer path on CPU, TP=1",
+                       "tokens_per_step": tokens},
+            "cpu_baseline": {"value": v, "unit": UNIT, "cores": threads, "kind": "port",
+                             "sample": f"{steps} full layer passes of the workload (steps capped at 20)"},
+            "e2e": {"value": v, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+            "gpu_launches": 0}
+    print(json.dumps(line), flush=True)
+
+
+# --------------------------------------------------------------- native arm
+class QAttention:
+    def forward(self, q, k, v, layer_cache_idx, softmax_scale=1.0, layer_id=None):
+        return q
+
+
+def run_native(a):
+    import torch
+    import torch.distributed as dist
+    from sarathi_serve_b200 import dense_ops, parallel_state as ps, synthetic as S
+    from sarathi_serve_b200.decoder_layer import LlamaDecoderLayer
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if world != a.gpus:
+        if world == 1 and a.gpus > 1:
+            raise SystemExit("launch with torchrun --nproc-per-node N for --gpus N > 1")
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("cpu:gloo,cuda:nccl", rank=rank, world_size=world, device_id=dev)
+    ps.initialize_model_parallel(world)
+
+    case = S.CASES[a.workload]
+    T, H = case.num_tokens, case.hidden_size
+    es = 2
+    comm = ps.get_tensor_model_parallel_comm(max(64 << 20, -(-T // world) * world * H * es))
+
+    torch.set_default_dtype(case.dtype)
+    t = S.generate(case)
+    params = S.shard(t, rank, world)
+    per_layer_bytes = sum(v.numel() for k, v in params.items() if "proj" in k) * es
+    n_layers = max(1, -(-2 * L2_BYTES // per_layer_bytes))
+    layers = []
+    for i in range(n_layers):
+        layer = LlamaDecoderLayer(case.hf_config(), layer_id=i)
+        S.load_layer(layer, params)  # same values, distinct device buffers: what matters is distinct addresses
+        layers.append(layer)
+    attn = QAttention()
+    x_dev = t.x.to(case.dtype).to(dev)
+    pos_dev = t.positions.to(dev)
+    with torch.inference_mode():
+        normed0 = layers[0].input_layernorm(x_dev)
+
+    def step_resident(i):
+        layer = layers[i % n_layers]
+        nxt = layers[(i + 1) % n_layers].input_layernorm
+        return layer.forward_carry(pos_dev, normed0, x_dev, 0, attn, nxt)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def max_over_ranks(v: float) -> float:
+        if world == 1:
+            return v
+        tt = torch.tensor([v], dtype=torch.float64, device=dev)
+        dist.all_reduce(tt, op=dist.ReduceOp.MAX)
+        return float(tt.item())
+
+    with torch.inference_mode():
+        # ---- device-resident value
+        for i in range(a.warmup):
+            step_resident(i)
+        barrier()
+        sampler = ClockSampler(local)
+        if rank == 0:
+            sampler.start()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for i in range(a.steps):
+            step_resident(i)
+        e1.record()
+        barrier()
+        ms_resident = max_over_ranks(e0.elapsed_time(e1) / a.steps)
+        clocks = sampler.stop() if rank == 0 else None
+        comm.check_status()
+        dense_ops.check_status(dev)
+
+        # ---- end to end through the layer API with host buffers
+        x_host = t.x.to(case.dtype).pin_memory()
+        pos_host = t.positions.pin_memory()
+        out_host = torch.empty(T, H, dtype=case.dtype).pin_memory()
+        x_in = torch.empty_like(x_dev)
+        pos_in = torch.empty_like(pos_dev)
+
+        def step_e2e(i):
+            x_in.copy_(x_host, non_blocking=True)
+            pos_in.copy_(pos_host, non_blocking=True)
+            out = layers[i % n_layers](pos_in, x_in, 0, attn)
+            out_host.copy_(out, non_blocking=True)
+            torch.cuda.current_stream().synchronize()
+
+        e2e_steps = max(10, a.steps // 4)
+        for i in range(max(3, a.warmup // 4)):
+            step_e2e(i)
+        barrier()
+        t0 = time.perf_counter()
+        for i in range(e2e_steps):
+            step_e2e(i)
+        barrier()
+        ms_e2e = max_over_ranks((time.perf_counter() - t0) * 1e3 / e2e_steps)
+        comm.check_status()
+
+        # ---- dominant kernel alone: gate_up GEMM + SiLU*mul
+        gu = [l.mlp.gate_up_proj for l in layers]
+        h_in = normed0
+        for i in range(5):
+            gu[i % n_layers].forward_silu_mul(h_in)
+        torch.cuda.synchronize()
+        reps = max(20, a.steps // 2)
+        k0, k1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        k0.record()
+        for i in range(reps):
+            gu[i % n_layers].forward_silu_mul(h_in)
+        k1.record()
+        torch.cuda.synchronize()
+        ms_kernel = k0.elapsed_time(k1) / reps
+
+    peak_tf, peak_hbm, peak_src = peaks()
+    d = case.intermediate_size // world
+    flops = 2.0 * T * H * 2 * d
+    achieved = flops / (ms_kernel * 1e-3) / 1e12
+    line = None
+    if rank == 0:
+        value = T / (ms_resident * 1e-3)
+        line = {"metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": a.steps, "warmup": a.warmup,
+                "ms_per_step": ms_resident, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+                "dtype": "bf16", "data": "synthetic",
+                "config": {"workload": f"{a.workload}: Llama-3-8B-shaped decoder layer (hidden 4096, 32q/8kv heads, "
+                                       f"head_dim 128, intermediate 14336), 512-token mixed chunk (448 prefill + 64 "
+                                       f"decode), TP={world}, attention stand-in attn_out=q",
+                           "tokens_per_step": T, "parallelism": f"tp{world}",
+                           "l2": f"{n_layers} distinct weight sets ({n_layers * per_layer_bytes >> 20} MiB/GPU) cycled: "
+                                 "operands of consecutive steps exceed the 126 MB L2"},
+                "clocks": clocks,
+                "e2e": {"value": T / (ms_e2e * 1e-3), "unit": UNIT, "ms_per_step": ms_e2e,
+                        "h2d_bytes_per_step": T * H * es + T * 8, "d2h_bytes_per_step": T * H * es},
+                "gpu_launches": 4 * a.steps,
+                "roofline": {"bound": "tensor", "kernel": "gemm_sm100_kernel<bf16, EPI_SILU_MUL> (gate_up + SiLU*mul)",
+                             "achieved": achieved, "peak": peak_tf, "unit": "TFLOP/s", "frac": achieved / peak_tf,
+                             "peak_source": f"{peak_src} (burst bf16)", "ms_per_launch": ms_kernel, "traffic": None}}
+        if not a.no_cpu_baseline and world == 1:
+            v, cores, iters, med = time_cpu(case, a.cpu_baseline_seconds)
+            line["cpu_baseline"] = {"value": v, "unit": UNIT, "cores": cores, "kind": "port",
+                                    "sample": f"{iters} full layer passes of the same workload "
+                                              f"(median {med * 1e3:.0f} ms each), oracle port, torch CPU bf16"}
+        print(json.dumps(line), flush=True)
+    barrier()
+    ps.destroy_model_parallel()
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def main():
+    a = parse()
+    if a.impl == "reference":
+        run_reference_arm(a)
+    else:
+        run_native(a)
+
+
+if __name__ == "__main__":
+    main()

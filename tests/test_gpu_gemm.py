@@ -1,0 +1,110 @@
+"""GPU parity of the dense projections (tcgen05 GEMM for bf16/fp16, FFMA for
+fp32) through the C ABI, against a plain fp32 torch matmul of the same operands
+and against the CPU oracle for the fused epilogues."""
+import pytest
+import torch
+
+from helpers import rel_err
+from oracle import tp_layer_oracle as O
+
+pytestmark = pytest.mark.gpu
+
+GEMM_TOL = {torch.float32: 2e-5, torch.bfloat16: 1e-2, torch.float16: 2e-3}
+
+
+def _rand(shape, dtype, seed, scale=1.0):
+    g = torch.Generator().manual_seed(seed)
+    return (torch.randn(*shape, generator=g) * scale).to(dtype)
+
+
+def _check_status():
+    from sarathi_serve_b200 import dense_ops
+    dense_ops.check_status(torch.device("cuda", torch.cuda.current_device()))
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16, torch.float32])
+@pytest.mark.parametrize("tile_n", [0, 64, 128, 256])
+@pytest.mark.parametrize("T,N,K", [(128, 128, 64), (128, 256, 128), (512, 768, 4096), (288, 768, 1024), (1, 256, 512),
+                                   (65, 200, 264), (300, 1000, 1000), (512, 6144, 512), (1024, 8, 4096)])
+def test_linear(dtype, tile_n, T, N, K):
+    from sarathi_serve_b200 import dense_ops
+    if dtype == torch.float32 and tile_n not in (0,):
+        pytest.skip("tile width applies to the tensor-core path only")
+    x, w = _rand((T, K), dtype, T + N + K), _rand((N, K), dtype, 7 * N + K, 0.05)
+    b = _rand((N,), dtype, 3)
+    ref = x.float().cuda() @ w.float().cuda().t()
+    out = dense_ops.linear(x.cuda(), w.cuda(), tile_n=tile_n)
+    _check_status()
+    assert rel_err(out.float(), ref) <= GEMM_TOL[dtype]
+    outb = dense_ops.linear(x.cuda(), w.cuda(), b.cuda(), tile_n=tile_n)
+    assert rel_err(outb.float(), ref + b.float().cuda()) <= GEMM_TOL[dtype]
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+def test_linear_strided_operands(dtype):
+    """A and the output may be row-strided views (q view of the fused qkv buffer feeding o_proj)."""
+    from sarathi_serve_b200 import dense_ops
+    big = _rand((130, 1536), dtype, 1).cuda()
+    x = big[:, 256:256 + 512]  # row stride 1536, 16-byte aligned start
+    w = _rand((384, 512), dtype, 2, 0.05).cuda()
+    outbuf = torch.zeros(130, 1024, dtype=dtype, device="cuda")
+    out = outbuf[:, 128:128 + 384]
+    dense_ops.linear(x, w, out=out)
+    _check_status()
+    assert rel_err(out.float(), x.float() @ w.float().t()) <= GEMM_TOL[dtype]
+    assert torch.all(outbuf[:, :128] == 0) and torch.all(outbuf[:, 512:] == 0)
+
+
+def test_linear_rejects_misaligned_stride():
+    from sarathi_serve_b200 import dense_ops
+    x = torch.randn(16, 100, dtype=torch.bfloat16, device="cuda")[:, :68]  # 68*2 bytes rows of a 100-wide buffer
+    w = torch.randn(32, 68, dtype=torch.bfloat16, device="cuda")
+    with pytest.raises(RuntimeError):
+        dense_ops.linear(x[:, 1:65], w[:, :64].contiguous())
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("neox", [True, False])
+@pytest.mark.parametrize("T,nq,nkv,hd,K", [(512, 4, 1, 128, 4096), (288, 8, 2, 64, 1024), (65, 2, 2, 128, 512),
+                                           (7, 1, 1, 256, 256)])
+def test_linear_rotary(dtype, neox, T, nq, nkv, hd, K):
+    from sarathi_serve_b200 import dense_ops
+    N = (nq + 2 * nkv) * hd
+    x, w = _rand((T, K), dtype, T + K), _rand((N, K), dtype, N, 0.03)
+    g = torch.Generator().manual_seed(5)
+    pos = torch.randint(0, 2048, (T,), generator=g, dtype=torch.int64)
+    cache = O.cos_sin_cache(hd, hd, 2048, 10000.0, dtype)
+    out = dense_ops.linear_rotary(x.cuda(), w.cuda(), pos.cuda(), cache.cuda(), hd, (nq + nkv) * hd, neox)
+    _check_status()
+    # oracle: GEMM rounded to the dtype (GPU fp32 matmul of the same operands), then the rotary restatement
+    ref = (x.float().cuda() @ w.float().cuda().t()).to(dtype).cpu()
+    q, k, _ = ref.split([nq * hd, nkv * hd, nkv * hd], dim=-1)
+    O.rotary_embedding(pos, q, k, hd, cache, neox)
+    assert rel_err(out, ref) <= GEMM_TOL[dtype]
+    # v columns are a plain GEMM
+    assert rel_err(out[:, (nq + nkv) * hd:], ref[:, (nq + nkv) * hd:]) <= GEMM_TOL[dtype]
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("tile_n", [0, 64, 128, 256])
+@pytest.mark.parametrize("T,d,K", [(512, 1792, 4096), (288, 1408, 1024), (65, 96, 512), (1, 64, 64)])
+def test_linear_silu_mul(dtype, tile_n, T, d, K):
+    from sarathi_serve_b200 import dense_ops
+    x, w = _rand((T, K), dtype, T + K), _rand((2 * d, K), dtype, d, 0.05)
+    out = dense_ops.linear_silu_mul(x.cuda(), w.cuda(), tile_n=tile_n)
+    _check_status()
+    gate_up = (x.float().cuda() @ w.float().cuda().t()).to(dtype).cpu()
+    ref = O.silu_and_mul(gate_up)
+    assert out.shape == (T, d)
+    assert rel_err(out, ref) <= 2e-2
+
+
+def test_gemm_linearity_full_size():
+    """Size-independent property at the headline shapes: (a*x) W^T == a * (x W^T) for a power of two."""
+    from sarathi_serve_b200 import dense_ops
+    x = _rand((512, 4096), torch.bfloat16, 1).cuda()
+    w = _rand((3584 * 2, 4096), torch.bfloat16, 2, 0.02).cuda()
+    y1 = dense_ops.linear(x, w)
+    y2 = dense_ops.linear(x * 4, w)
+    _check_status()
+    assert torch.equal(y1 * 4, y2)

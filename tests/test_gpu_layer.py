@@ -1,0 +1,102 @@
+"""GPU parity of the decoder layer built from this package's modules (tensor
+parallel size 1: one GPU, the row-parallel kernel runs its reduce / residual /
+norm phases locally) against the CPU oracle and the reference fixtures."""
+import pytest
+import torch
+
+from helpers import TOL, load_golden, rel_err
+from oracle import tp_layer_oracle as O
+from sarathi_serve_b200 import synthetic as S
+
+pytestmark = pytest.mark.gpu
+
+
+class QAttention:
+    """Attention stand-in shared with the oracle and the fixtures: attn_out = q (after rotary)."""
+
+    def __init__(self):
+        self.seen = {}
+
+    def forward(self, q, k, v, layer_cache_idx, softmax_scale=1.0, layer_id=None):
+        self.seen = {"q_rot": q.clone(), "k_rot": k.clone(), "v": v.clone()}
+        return q  # a strided view: the o_proj GEMM reads it in place
+
+
+@pytest.fixture(scope="module")
+def tp1():
+    from sarathi_serve_b200 import parallel_state as ps
+    ps.destroy_model_parallel()
+    ps.initialize_model_parallel(1)
+    yield ps
+    ps.destroy_model_parallel()
+
+
+def build_layer(case, rank=0, world=1):
+    from sarathi_serve_b200.decoder_layer import LlamaDecoderLayer
+    old = torch.get_default_dtype()
+    torch.set_default_dtype(case.dtype)
+    try:
+        layer = LlamaDecoderLayer(case.hf_config(), layer_id=0)
+    finally:
+        torch.set_default_dtype(old)
+    t = S.generate(case)
+    S.load_layer(layer, S.shard(t, rank, world))
+    return layer, t
+
+
+def oracle_out(case, t, next_norm=None):
+    cache = O.cos_sin_cache(case.head_dim, case.head_dim, case.max_position, case.rope_theta, case.dtype)
+    return O.decoder_layer([S.shard(t, 0, 1)], t.x.to(case.dtype), t.positions, num_heads=case.num_heads,
+                           num_kv_heads=case.num_kv_heads, head_dim=case.head_dim, eps=case.rms_norm_eps,
+                           cache=cache, next_norm_weight=next_norm)
+
+
+@pytest.mark.parametrize("case_name", ["mini_f32", "mini_bf16", "mini_f16", "config1"])
+@pytest.mark.parametrize("path", ["fused", "unfused"])
+def test_layer_matches_oracle_and_fixture(tp1, case_name, path):
+    case = S.CASES[case_name]
+    layer, t = build_layer(case)
+    attn = QAttention()
+    x = t.x.to(case.dtype).cuda()
+    pos = t.positions.cuda()
+    with torch.inference_mode():
+        fn = layer.forward if path == "fused" else layer.forward_unfused
+        out = fn(pos, x.clone(), 0, attn)
+    tp1.get_tensor_model_parallel_comm().check_status()
+    ref = oracle_out(case, t)
+    tol = TOL[case.dtype]
+    assert rel_err(out, ref["out"]) <= tol
+    nq = case.num_heads * case.head_dim
+    assert rel_err(attn.seen["q_rot"], ref["qkv"][:, :nq]) <= tol
+    assert rel_err(attn.seen["k_rot"], ref["qkv"][:, nq:nq + case.num_kv_heads * case.head_dim]) <= tol
+    world = 2 if case_name == "config1" else 1
+    gold, _, step, _ = load_golden(case_name, world)
+    assert rel_err(out[::step], gold["out"]) <= tol  # the reference's own layer output (TP-invariant)
+
+
+def test_layer_carry_path(tp1):
+    """(normed, residual) -> (normed', residual') equals the oracle's layer followed by the next norm."""
+    from sarathi_serve_b200.nn_layers import RMSNorm
+    case = S.CASES["mini_bf16"]
+    layer, t = build_layer(case)
+    x = t.x.to(case.dtype).cuda()
+    next_norm = RMSNorm(case.hidden_size, eps=case.rms_norm_eps)
+    next_norm.weight.data = t.ln2.to(case.dtype).cuda()
+    with torch.inference_mode():
+        normed = layer.input_layernorm(x)
+        y, z = layer.forward_carry(t.positions.cuda(), normed, x, 0, QAttention(), next_norm)
+    tp1.get_tensor_model_parallel_comm().check_status()
+    ref = oracle_out(case, t, next_norm=t.ln2.to(case.dtype))
+    assert rel_err(z, ref["out"]) <= TOL[case.dtype]
+    assert rel_err(y, ref["out_normed"]) <= TOL[case.dtype]
+
+
+def test_layer_config2_full_size(tp1):
+    """Headline shapes (Llama-3-8B layer, 512-token mixed chunk), TP=1, against the CPU oracle."""
+    case = S.CASES["config2"]
+    layer, t = build_layer(case)
+    with torch.inference_mode():
+        out = layer(t.positions.cuda(), t.x.to(case.dtype).cuda(), 0, QAttention())
+    tp1.get_tensor_model_parallel_comm().check_status()
+    ref = oracle_out(case, t)
+    assert rel_err(out, ref["out"]) <= TOL[case.dtype]

@@ -1,0 +1,198 @@
+"""Host-side logic that needs no GPU: sharding, layer construction (API surface,
+parameter names and shapes), tensor-parallel group bookkeeping over gloo with
+two processes, the distributed oracle, and a threaded model of the device-side
+push / reduce / finish counter protocol including a rank that never arrives."""
+import os
+import threading
+import time
+
+import pytest
+import torch
+import torch.multiprocessing as mp
+
+from oracle import tp_layer_oracle as O
+from sarathi_serve_b200 import synthetic as S
+
+
+def test_divide_and_shard_shapes():
+    from sarathi_serve_b200.mappings import divide
+    assert divide(12, 4) == 3
+    with pytest.raises(AssertionError):
+        divide(10, 4)
+    t = S.generate(S.CASES["mini_bf16"])
+    for world in (1, 2):
+        p = S.shard(t, world - 1, world)
+        assert p["self_attn.qkv_proj.weight"].shape == ((4 + 2 * 2) * 128 // world, 512)
+        assert p["self_attn.o_proj.weight"].shape == (512, 4 * 128 // world)
+        assert p["mlp.gate_up_proj.weight"].shape == (2 * 1024 // world, 512)
+        assert p["mlp.down_proj.weight"].shape == (512, 1024 // world)
+    # shards tile the full matrices
+    p0, p1 = S.shard(t, 0, 2, torch.float32), S.shard(t, 1, 2, torch.float32)
+    assert torch.equal(torch.cat([p0["self_attn.o_proj.weight"], p1["self_attn.o_proj.weight"]], 1), t.wo)
+    assert torch.equal(torch.cat([p0["mlp.gate_up_proj.weight"][:512], p1["mlp.gate_up_proj.weight"][:512]]), t.wgate)
+
+
+def test_generator_is_deterministic_and_dtype_independent():
+    a = S.generate(S.CASES["mini_f32"])
+    old = torch.get_default_dtype()
+    torch.set_default_dtype(torch.bfloat16)
+    try:
+        b = S.generate(S.CASES["mini_f32"])
+    finally:
+        torch.set_default_dtype(old)
+    assert torch.equal(a.x, b.x) and torch.equal(a.wdown, b.wdown) and torch.equal(a.positions, b.positions)
+    c = S.CASES["config2"]
+    assert c.num_tokens == 512 and c.prefill_tokens == 448 and c.decode_tokens == 64
+
+
+def test_layer_api_surface_on_cpu():
+    """Constructor keywords, attributes and state-dict names/shapes of the reference's layers."""
+    from sarathi_serve_b200 import parallel_state as ps
+    from sarathi_serve_b200.decoder_layer import LlamaDecoderLayer
+    from sarathi_serve_b200.tp_layers import ColumnParallelLinear, ReplicatedLinear, RowParallelLinear
+    ps.destroy_model_parallel()
+    ps.initialize_model_parallel(1)
+    ps.set_tensor_model_parallel_world_size(4)
+    ps.set_tensor_model_parallel_rank(1)
+    try:
+        col = ColumnParallelLinear(64, 256, bias=True, gather_output=False, skip_bias_add=True,
+                                   params_dtype=torch.bfloat16, linear_metric_name="x",
+                                   communication_metric_name="y", layer_id=3)
+        assert col.weight.shape == (64, 64) and col.bias.shape == (64,) and col.output_size_per_partition == 64
+        assert col.weight.dtype == torch.bfloat16 and col.world_size == 4
+        row = RowParallelLinear(256, 64, bias=False, input_is_parallel=True, reduce_results=True, layer_id=0)
+        assert row.weight.shape == (64, 64) and row.bias is None and row.input_size_per_partition == 64
+        rep = ReplicatedLinear(64, 8, bias=False, params_dtype=torch.float16, metric_name="g")
+        assert rep.weight.shape == (8, 64)
+        with pytest.raises(AssertionError):
+            ColumnParallelLinear(64, 30)  # 30 not divisible by 4
+        with pytest.raises(AssertionError):
+            RowParallelLinear(64, 64, perform_initialization=True)
+        case = S.CASES["config1"]
+        layer = LlamaDecoderLayer(case.hf_config(), layer_id=0)
+        sd = layer.state_dict()
+        assert sd["self_attn.qkv_proj.weight"].shape == ((16 + 8) * 64 // 4, 1024)
+        assert sd["self_attn.o_proj.weight"].shape == (1024, 1024 // 4)
+        assert sd["mlp.gate_up_proj.weight"].shape == (2 * 2816 // 4, 1024)
+        assert sd["mlp.down_proj.weight"].shape == (1024, 2816 // 4)
+        assert set(sd) == {"self_attn.qkv_proj.weight", "self_attn.o_proj.weight", "mlp.gate_up_proj.weight",
+                           "mlp.down_proj.weight", "input_layernorm.weight", "post_attention_layernorm.weight"}
+        with pytest.raises(RuntimeError):  # no CPU fallback: a CPU tensor is refused
+            col(torch.randn(4, 64, dtype=torch.bfloat16))
+    finally:
+        ps.destroy_model_parallel()
+
+
+def test_rope_variants_build_tables():
+    from sarathi_serve_b200.nn_layers import get_rope
+    base = get_rope(64, 64, 128, 10000, True, None)
+    assert base.cos_sin_cache.shape == (128, 64)
+    assert torch.allclose(base.cos_sin_cache.float().cpu(), O.cos_sin_cache(64, 64, 128, 10000.0, torch.float32))
+    lin = get_rope(64, 64, 128, 10000, True, {"type": "linear", "factor": 2.0})
+    assert lin.cos_sin_cache.shape == (256, 64)
+    assert torch.allclose(lin.cos_sin_cache[2].float(), base.cos_sin_cache[1].float())
+    dyn = get_rope(64, 64, 128, 10000, True, {"type": "dynamic", "factor": 2.0})
+    assert dyn.cos_sin_cache.shape == (256, 64)
+    yarn = get_rope(64, 64, 256, 10000, True, {"type": "yarn", "factor": 2.0, "original_max_position_embeddings": 128})
+    assert yarn.cos_sin_cache.shape == (256, 64)
+    with pytest.raises(ValueError):
+        get_rope(64, 64, 128, 10000, True, {"type": "nope", "factor": 2.0})
+
+
+# ---------------------------------------------------------------- gloo, 2 ranks
+def _gloo_worker(rank, world, port, ret):
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    import torch.distributed as dist
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    torch.set_num_threads(2)
+    from sarathi_serve_b200 import parallel_state as ps
+    from sarathi_serve_b200.mappings import gather_from_tensor_model_parallel_region, scatter_to_tensor_model_parallel_region
+    ps.initialize_model_parallel(world)
+    assert ps.get_tensor_model_parallel_world_size() == world
+    assert ps.get_tensor_model_parallel_rank() == rank
+    x = torch.arange(12.0).view(3, 4)
+    mine = scatter_to_tensor_model_parallel_region(x)
+    assert torch.equal(mine, x[:, rank * 2:(rank + 1) * 2])
+    assert torch.equal(gather_from_tensor_model_parallel_region(mine), x)
+    # distributed oracle == single-process simulated-rank oracle
+    case = S.CASES["mini_f32"]
+    t = S.generate(case)
+    cache = O.cos_sin_cache(case.head_dim, case.head_dim, case.max_position, case.rope_theta, case.dtype)
+    kw = dict(num_heads=case.num_heads, num_kv_heads=case.num_kv_heads, head_dim=case.head_dim,
+              eps=case.rms_norm_eps, cache=cache)
+    out = O.decoder_layer_distributed(S.shard(t, rank, world), t.x, t.positions, world=world,
+                                      group=ps.get_tensor_model_parallel_group(), **kw)
+    sim = O.decoder_layer([S.shard(t, r, world) for r in range(world)], t.x, t.positions, **kw)["out"]
+    assert O.rel_err(out, sim) < 1e-6
+    ps.destroy_model_parallel()
+    dist.destroy_process_group()
+
+
+def test_two_rank_gloo_groups_and_distributed_oracle():
+    mp.spawn(_gloo_worker, args=(2, 29731, None), nprocs=2)
+
+
+# ------------------------------------------- host model of the counter protocol
+class _Rank:
+    """Counters of one rank's heap (monotonic, compared against per-call targets)."""
+
+    def __init__(self):
+        self.push = [0, 0]
+        self.done = [0, 0]
+        self.lock = threading.Lock()
+
+
+def _wait(get, target, limit_s):
+    t0 = time.perf_counter()
+    while get() < target:
+        if time.perf_counter() - t0 > limit_s:
+            return False
+        time.sleep(0.0005)
+    return True
+
+
+def _run_protocol(world, calls, absent=None, limit_s=0.3):
+    """Each thread = one rank running `calls` collectives: push to every owner, wait for
+    its own pushes, 'reduce', signal done to everyone, wait for all rows.  Returns statuses."""
+    ranks = [_Rank() for _ in range(world)]
+    status = [0] * world
+    T = 16
+    rows = T // world
+
+    def body(r):
+        push_total, done_total = [0, 0], [0, 0]
+        for c in range(calls):
+            s = c & 1
+            if absent == (r, c):
+                return  # this rank never launches call c
+            for o in range(world):  # push phase
+                with ranks[o].lock:
+                    ranks[o].push[s] += 1
+            push_total[s] += world
+            done_total[s] += T
+            if not _wait(lambda: ranks[r].push[s], push_total[s], limit_s):
+                status[r] = 2
+                return
+            for o in range(world):  # reduce + broadcast: one count per owned row on every rank
+                with ranks[o].lock:
+                    ranks[o].done[s] += rows
+            if not _wait(lambda: ranks[r].done[s], done_total[s], limit_s):
+                status[r] = 3
+                return
+
+    th = [threading.Thread(target=body, args=(r,)) for r in range(world)]
+    [t.start() for t in th]
+    [t.join() for t in th]
+    return status
+
+
+def test_counter_protocol_completes_with_skewed_ranks():
+    assert _run_protocol(4, 25) == [0, 0, 0, 0]
+    assert _run_protocol(2, 40) == [0, 0]
+
+
+def test_counter_protocol_reports_a_lost_rank_instead_of_hanging():
+    st = _run_protocol(4, 6, absent=(2, 3))
+    assert st[2] == 0  # the absent rank just stops
+    assert all(s in (2, 3) for i, s in enumerate(st) if i != 2), st
