@@ -120,6 +120,25 @@ int sb200_moe_align_block_size(const void* topk_ids, int ids_itype, int64_t nume
 /* Bytes of scratch the multi-CTA path of sb200_moe_align_block_size wants. */
 int64_t sb200_moe_align_scratch_bytes(int64_t numel, int num_experts);
 
+/* Same sort and same outputs as sb200_moe_align_block_size, for callers that can neither
+ * pass a scratch buffer nor allocate one (a worker whose GPU memory is already committed
+ * to its KV cache, code that must not trigger the device-wide synchronisation of
+ * cudaMalloc / cudaFree, a plugin boundary that forwards only inputs and outputs).  It calls
+ * no allocator: its per-segment counters live in a fixed array inside the library image
+ * (about 258 KiB held by every GPU that loads the library, until the process exits).
+ * Limits: numel <= SB200_ALIGN_NOALLOC_MAX_SLOTS and num_experts <=
+ * SB200_ALIGN_NOALLOC_MAX_EXPERTS, otherwise SB200_ERR_UNSUPPORTED.  All calls on a device
+ * share that array: calls that overlap on the GPU race, so keep them on one stream or
+ * order them.  The first call on each device resolves the array's device address; make it
+ * outside any stream capture.
+ * This entry point has no counterpart in the reference. */
+#define SB200_ALIGN_NOALLOC_MAX_SLOTS 65536
+#define SB200_ALIGN_NOALLOC_MAX_EXPERTS 256
+int sb200_moe_align_block_size_noalloc(const void* topk_ids, int ids_itype, int64_t numel, int num_experts,
+                                       int block_size, int32_t* sorted_token_ids, int64_t sorted_capacity,
+                                       int32_t* expert_ids, int64_t expert_ids_capacity,
+                                       int32_t* num_tokens_post_pad, sb200_stream_t stream);
+
 /* ------------------------------------------------- column-parallel projections */
 
 enum sb200_epilogue {

@@ -70,6 +70,7 @@ def _declare(lib):
         "sb200_topk_softmax": (I, [P, P, P, P, I, L, I, I, I, P]),
         "sb200_moe_align_block_size": (I, [P, I, L, I, I, P, L, P, L, P, P, L, P]),
         "sb200_moe_align_scratch_bytes": (L, [L, I]),
+        "sb200_moe_align_block_size_noalloc": (I, [P, I, L, I, I, P, L, P, L, P, P]),
     }
     optional = {}
     optional.update(_GEMM_SIGS)

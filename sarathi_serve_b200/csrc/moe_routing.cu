@@ -21,6 +21,7 @@
 
 #include <cub/block/block_reduce.cuh>
 #include <float.h>
+#include <mutex>
 
 namespace sb200 {
 
@@ -435,5 +436,98 @@ extern "C" int sb200_moe_align_block_size(const void* topk_ids, int ids_itype, i
   moe_align_scatter_kernel<<<ctas, 256, 0, s>>>(topk_ids, ids_itype, numel, E, p.seg_len, p.nseg, scr,
                                                 sorted_token_ids);
   SB_CHECK_LAUNCH("moe_align_scatter_kernel");
+  return SB200_OK;
+}
+
+// ------------------------------------------------------------------------------------------
+// sb200_moe_align_block_size_noalloc: the multi-CTA sort above, for callers that must not
+// allocate.  Some hosts of this library cannot hand it a scratch buffer and cannot call
+// cudaMalloc at the point where they route tokens: a serving worker that has already given
+// every free byte of the GPU to its KV cache, code that runs between other streams' kernels
+// where the device-wide synchronisation inside cudaMalloc / cudaFree would stall them, or a
+// plugin boundary that only passes inputs and outputs through.  For them the per-segment
+// counters live in a fixed array that is part of the library image: every GPU that loads
+// the library holds these 258 KiB until the process exits.
+//
+// Limits: numel <= SB200_ALIGN_NOALLOC_MAX_SLOTS and num_experts <= SB200_ALIGN_NOALLOC_MAX_EXPERTS;
+// larger inputs are refused with SB200_ERR_UNSUPPORTED.
+//
+// The array is shared by every call on a device and keeps the previous call's contents.
+// Nothing in it needs clearing between calls: the count kernel zeroes each segment's
+// counters before counting and the scan kernel rewrites every prefix entry it later reads.
+// Two calls that overlap on the GPU (different streams, or different threads without
+// ordering) would race on it; issue them on one stream or order them with events.
+//
+// The first call on each device looks up the array's device address (with that device
+// current); make that first call outside any stream capture.
+constexpr int kNoAllocMaxSegments = SB200_ALIGN_NOALLOC_MAX_SLOTS / 256;
+constexpr int kNoAllocScratchInts = kNoAllocMaxSegments * SB200_ALIGN_NOALLOC_MAX_EXPERTS + SB200_ALIGN_NOALLOC_MAX_EXPERTS + 1 + 63;
+static __device__ __align__(256) int g_align_noalloc_scratch[kNoAllocScratchInts];
+
+namespace sb200 {
+constexpr int kMaxDevices = 64;
+static int* g_noalloc_ptr[kMaxDevices];  // device address of the array, per device ordinal
+static std::mutex g_noalloc_mutex;
+
+// In host code the array's name is only a handle for the runtime, not a device address:
+// the address a kernel can use comes from cudaGetSymbolAddress, once per device.
+static int noalloc_scratch(int** out) {
+  int dev = -1;
+  SB_CUDA(cudaGetDevice(&dev));
+  SB_CHECK_ARG(dev >= 0 && dev < kMaxDevices, "moe_align_block_size_noalloc: device ordinal %d out of range", dev);
+  std::lock_guard<std::mutex> lock(g_noalloc_mutex);
+  if (!g_noalloc_ptr[dev]) {
+    void* p = nullptr;
+    const cudaError_t e = cudaGetSymbolAddress(&p, g_align_noalloc_scratch);
+    if (e != cudaSuccess) return cuda_fail(e, "cudaGetSymbolAddress(g_align_noalloc_scratch)");
+    g_noalloc_ptr[dev] = static_cast<int*>(p);
+  }
+  *out = g_noalloc_ptr[dev];
+  return SB200_OK;
+}
+}  // namespace sb200
+
+extern "C" int sb200_moe_align_block_size_noalloc(const void* topk_ids, int ids_itype, int64_t numel, int num_experts,
+                                                  int block_size, int32_t* sorted_token_ids, int64_t sorted_capacity,
+                                                  int32_t* expert_ids, int64_t expert_ids_capacity,
+                                                  int32_t* num_tokens_post_pad, sb200_stream_t stream) {
+  const int E = num_experts;
+  SB_CHECK_ARG(numel >= 0 && E > 0 && block_size > 0, "moe_align_block_size_noalloc: bad shape numel=%lld E=%d block=%d",
+               (long long)numel, E, block_size);
+  if (numel > SB200_ALIGN_NOALLOC_MAX_SLOTS || E > SB200_ALIGN_NOALLOC_MAX_EXPERTS) {
+    set_error("moe_align_block_size_noalloc: numel=%lld / num_experts=%d exceed the built-in scratch (at most %d slots, "
+              "%d experts); use sb200_moe_align_block_size with a caller-provided scratch buffer",
+              (long long)numel, E, SB200_ALIGN_NOALLOC_MAX_SLOTS, SB200_ALIGN_NOALLOC_MAX_EXPERTS);
+    return SB200_ERR_UNSUPPORTED;
+  }
+  SB_CHECK_ARG(ids_itype >= SB200_I32 && ids_itype <= SB200_U8, "moe_align_block_size_noalloc: bad index type %d", ids_itype);
+  SB_CHECK_ARG(numel + (int64_t)E * block_size <= INT32_MAX, "moe_align_block_size_noalloc: sizes overflow int32");
+  SB_CHECK_ARG(sorted_token_ids && expert_ids && num_tokens_post_pad && (topk_ids || numel == 0),
+               "moe_align_block_size_noalloc: null pointer");
+  const int64_t worst = numel + (int64_t)(E < numel ? E : numel) * (block_size - 1);
+  SB_CHECK_ARG(sorted_capacity >= worst, "moe_align_block_size_noalloc: sorted_token_ids holds %lld < %lld entries",
+               (long long)sorted_capacity, (long long)worst);
+  SB_CHECK_ARG(expert_ids_capacity >= (worst + block_size - 1) / block_size,
+               "moe_align_block_size_noalloc: expert_ids holds %lld entries, %lld needed", (long long)expert_ids_capacity,
+               (long long)((worst + block_size - 1) / block_size));
+  int* scr = nullptr;
+  const int rc = noalloc_scratch(&scr);
+  if (rc) return rc;
+  cudaStream_t s = (cudaStream_t)stream;
+  AlignPlan p = align_plan(numel);
+  if (p.nseg > kNoAllocMaxSegments) {  // cannot happen below the slot limit; kept as a guard on the array bound
+    set_error("moe_align_block_size_noalloc: internal segment count %d exceeds %d", p.nseg, kNoAllocMaxSegments);
+    return SB200_ERR_UNSUPPORTED;
+  }
+  const int ctas = (p.nseg + 7) / 8;
+  moe_align_count_kernel<<<ctas, 256, 0, s>>>(topk_ids, ids_itype, numel, E, p.seg_len, p.nseg, scr, sorted_token_ids,
+                                              sorted_capacity);
+  SB_CHECK_LAUNCH("moe_align_count_kernel (noalloc)");
+  moe_align_scan_kernel<<<1, 1024, 0, s>>>(E, block_size, p.nseg, scr, expert_ids, expert_ids_capacity,
+                                           num_tokens_post_pad);
+  SB_CHECK_LAUNCH("moe_align_scan_kernel (noalloc)");
+  moe_align_scatter_kernel<<<ctas, 256, 0, s>>>(topk_ids, ids_itype, numel, E, p.seg_len, p.nseg, scr,
+                                                sorted_token_ids);
+  SB_CHECK_LAUNCH("moe_align_scatter_kernel (noalloc)");
   return SB200_OK;
 }

@@ -51,3 +51,31 @@ def moe_align_block_size(topk_ids: torch.Tensor, num_experts: int, block_size: i
 
 def moe_align_scratch_bytes(numel: int, num_experts: int) -> int:
     return int(N.lib().sb200_moe_align_scratch_bytes(int(numel), int(num_experts)))
+
+
+NOALLOC_MAX_SLOTS = 65536
+NOALLOC_MAX_EXPERTS = 256
+
+
+def moe_align_block_size_noalloc(topk_ids: torch.Tensor, num_experts: int, block_size: int,
+                                 sorted_token_ids: torch.Tensor, experts_ids: torch.Tensor,
+                                 num_tokens_post_pad: torch.Tensor) -> None:
+    """``moe_align_block_size`` for callers that cannot allocate device memory or pass scratch.
+
+    Same outputs; the kernels' working counters live in a fixed array inside the library
+    instead of a caller buffer, so the call itself allocates nothing (no cudaMalloc, no torch
+    allocation).  Meant for hosts whose GPU memory is fully committed (a serving worker after
+    its KV cache is sized) or that must avoid the device-wide stall of an allocation.  At most
+    ``NOALLOC_MAX_SLOTS`` slots and ``NOALLOC_MAX_EXPERTS`` experts; larger inputs raise.  All
+    calls on a device share the array, so keep them on one stream; make the first call on a
+    device outside any stream capture."""
+    N.require_cuda(topk_ids, sorted_token_ids, experts_ids, num_tokens_post_pad)
+    if sorted_token_ids.dtype != torch.int32 or experts_ids.dtype != torch.int32 or num_tokens_post_pad.dtype != torch.int32:
+        raise RuntimeError("moe_align_block_size_noalloc: outputs must be int32")
+    if not (topk_ids.is_contiguous() and sorted_token_ids.is_contiguous() and experts_ids.is_contiguous()):
+        raise RuntimeError("moe_align_block_size_noalloc: tensors must be contiguous")
+    N.check(N.lib().sb200_moe_align_block_size_noalloc(N.ptr(topk_ids), N.itype_id(topk_ids), topk_ids.numel(),
+                                                       int(num_experts), int(block_size), N.ptr(sorted_token_ids),
+                                                       sorted_token_ids.numel(), N.ptr(experts_ids),
+                                                       experts_ids.numel(), N.ptr(num_tokens_post_pad),
+                                                       N.stream_ptr()), "moe_align_block_size_noalloc")
