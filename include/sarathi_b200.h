@@ -166,14 +166,31 @@ typedef struct sb200_rotary_args {
  *   SB200_EPI_SILU_MUL : w holds the gate shard in rows [0, N/2) and the up shard in
  *                        rows [N/2, N); out is [T, N/2].
  * status: optional device word that receives a non-zero code if a bounded
- * pipeline wait inside the kernel ran out.  tile_n: 0 = choose, or 64/128/256.
+ * pipeline wait inside the kernel ran out.
+ * tile_cfg: 0 = let the library choose the tile shape, else
+ *   BN + 1000*MODE + 100000*S  (BN = tile columns 32..256 step 32; MODE = 1|2: one CTA
+ *   with 1|2 accumulators of 128 rows; MODE = 3|4: CTA pairs (tcgen05 cta_group::2) with
+ *   1|2 accumulators of 256 rows; S >= 2 cuts tiles along K so that about S units share
+ *   one; a bare BN means MODE = 1, whole tiles per CTA).
+ * workspace: optional device buffer (zero-filled once by the caller, at least 64 KiB +
+ *   room for the fp32 partial tiles) that allows tiles to be cut along K ("stream-K");
+ *   the library leaves its first 64 KiB zero again after every launch.  NULL / 0: whole
+ *   tiles per CTA only.
  * Replaces: ColumnParallelLinear.apply_weights / ReplicatedLinear.apply_weights
  * (F.linear -> cuBLAS), sarathi/model_executor/parallel_utils/tensor_parallel/layers.py:278-284,516-518,
  * and, with the fused epilogues, the rotary_embedding call of models/llama.py:176-177
  * and the SiluAndMul call of models/llama.py:101-104. */
 int sb200_gemm_colpar(void* out, int64_t ldo, const void* x, int64_t ldx, const void* w, int64_t ldw,
                       const void* bias, int64_t T, int64_t N, int64_t K, int dtype, int epilogue,
-                      const sb200_rotary_args* rot, uint32_t* status, int tile_n, sb200_stream_t stream);
+                      const sb200_rotary_args* rot, uint32_t* status, int tile_cfg, void* workspace,
+                      int64_t workspace_bytes, sb200_stream_t stream);
+
+/* The tile shape and schedule the two GEMM entry points would pick (epilogue 3 = the
+ * row-parallel kernel): out[0..10] = cta_pairs, accumulators, BN, scheduling units,
+ * tiles handed out whole, K-parts of the remaining tiles, k-blocks per part, pipeline
+ * stages, M tiles, N tiles, k-blocks.  Host-only; no counterpart in the reference. */
+int sb200_gemm_plan(int epilogue, int64_t T, int64_t N, int64_t K, int head_size, int tile_cfg,
+                    int64_t workspace_bytes, int* out);
 
 /* ------------------------------------------- tensor-parallel communication */
 
@@ -237,7 +254,7 @@ int sb200_all_reduce(sb200_comm* comm, const void* in, int64_t T, int64_t H, int
 int sb200_gemm_rowpar(sb200_comm* comm, const void* x, int64_t ldx, const void* w, int64_t ldw, int64_t T,
                       int64_t N, int64_t K, int dtype, const void* bias, const void* residual,
                       const void* norm_w, float eps, int write_resid_all, void* out_copy, void* resid_copy,
-                      int tile_n, sb200_stream_t stream, void** out_ptr, void** resid_ptr);
+                      int tile_cfg, sb200_stream_t stream, void** out_ptr, void** resid_ptr);
 
 #ifdef __cplusplus
 }

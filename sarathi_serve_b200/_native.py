@@ -38,7 +38,9 @@ class RotaryArgs(ctypes.Structure):
 
 _PP = ctypes.POINTER(c_void_p)
 _GEMM_SIGS: dict = {
-    "sb200_gemm_colpar": (_I, [_P, _L, _P, _L, _P, _L, _P, _L, _L, _L, _I, _I, ctypes.POINTER(RotaryArgs), _P, _I, _P]),
+    "sb200_gemm_colpar": (_I, [_P, _L, _P, _L, _P, _L, _P, _L, _L, _L, _I, _I, ctypes.POINTER(RotaryArgs), _P, _I, _P,
+                               _L, _P]),
+    "sb200_gemm_plan": (_I, [_I, _L, _L, _L, _I, _I, _L, ctypes.POINTER(c_int)]),
     "sb200_comm_heap_bytes": (_L, [_L]),
     "sb200_comm_create": (_I, [_PP, _I, _I, _L]),
     "sb200_comm_create_external": (_I, [_PP, _I, _I, _L, _PP]),

@@ -19,7 +19,6 @@ struct sb200_comm {
   void* heap[sb200::kMaxRanks];
   bool own_heap;
   bool ipc_opened[sb200::kMaxRanks];
-  uint32_t push_total[2], done_total[2];
   uint64_t seq;
   long long wait_cycles;
 };
@@ -71,6 +70,7 @@ all_reduce_kernel(const CommView c, const ReduceArgs a, const T* __restrict__ in
     if (finish_phase(c, a) && (a.out_copy || a.resid_copy))
       copy_out_phase<T>(c, a, blockIdx.x * blockDim.x + threadIdx.x, gridDim.x * blockDim.x);
   }
+  advance_targets(c, a);
 }
 
 static int all_reduce_grid(int64_t T_, int64_t H, int dtype, int rows_per_rank) {
@@ -121,10 +121,8 @@ static int plan_call(sb200_comm* c, int64_t T_, int64_t H, int dtype, const void
 
 static void commit_call(sb200_comm* c, CallPlan* p, uint32_t pushes_to_me, void** out_ptr, void** resid_ptr) {
   const int set = p->ra.set;
-  c->push_total[set] += pushes_to_me;
-  c->done_total[set] += (uint32_t)p->ra.T;
-  p->ra.push_target = c->push_total[set];
-  p->ra.done_target = c->done_total[set];
+  p->ra.push_per_call = pushes_to_me;
+  p->ra.done_per_call = (uint32_t)p->ra.T;
   if (out_ptr) *out_ptr = (char*)c->heap[c->rank] + p->cv.out_off[set];
   if (resid_ptr) *resid_ptr = p->ra.norm_w ? (void*)((char*)c->heap[c->rank] + p->cv.resid_off[set]) : nullptr;
   c->seq++;
@@ -282,15 +280,17 @@ extern "C" int sb200_all_reduce(sb200_comm* comm, const void* in, int64_t T, int
 extern "C" int sb200_gemm_rowpar(sb200_comm* comm, const void* x, int64_t ldx, const void* w, int64_t ldw, int64_t T,
                                  int64_t N, int64_t K, int dtype, const void* bias, const void* residual,
                                  const void* norm_w, float eps, int write_resid_all, void* out_copy, void* resid_copy,
-                                 int tile_n, sb200_stream_t stream, void** out_ptr, void** resid_ptr) {
+                                 int tile_cfg, sb200_stream_t stream, void** out_ptr, void** resid_ptr) {
   SB_CHECK_ARG(comm && x && w, "gemm_rowpar: null pointer");
   SB_CHECK_ARG(T > 0 && N > 0 && K > 0 && K <= INT32_MAX, "gemm_rowpar: bad shape T=%lld N=%lld K=%lld", (long long)T,
                (long long)N, (long long)K);
   cudaStream_t s = (cudaStream_t)stream;
   if (dtype == SB200_F32) {
     // fp32: FFMA GEMM into the context's scratch region, then the standalone all-reduce phases.
-    SB_CHECK_ARG((size_t)T * N * 4 <= comm->region_bytes, "gemm_rowpar: batch exceeds the context's region size");
-    float* tmp = (float*)sb200_comm_scratch(comm);
+    // (the first kWsCounterBytes of the scratch region are the split-K counters of the tensor-core path)
+    SB_CHECK_ARG((size_t)T * N * 4 + kWsCounterBytes <= comm->region_bytes,
+                 "gemm_rowpar: batch exceeds the context's region size");
+    float* tmp = (float*)((char*)sb200_comm_scratch(comm) + kWsCounterBytes);
     int rc = run_gemm_f32(tmp, N, (const float*)x, ldx, (const float*)w, ldw, nullptr, (int)T, (int)N, (int)K, s);
     if (rc) return rc;
     return do_all_reduce(comm, tmp, T, N, dtype, bias, residual, norm_w, eps, write_resid_all, out_copy, resid_copy,
@@ -300,23 +300,23 @@ extern "C" int sb200_gemm_rowpar(sb200_comm* comm, const void* x, int64_t ldx, c
   int rc = plan_call(comm, T, N, dtype, bias, residual, norm_w, eps, write_resid_all, out_copy, resid_copy, &p);
   if (rc) return rc;
   SB_CHECK_ARG(N % 8 == 0, "gemm_rowpar: output width must be a multiple of 8");
-  const int bn = choose_bn(EPI_PUSH, T, N, 0, tile_n);
-  SB_CHECK_ARG(bn != 0, "gemm_rowpar: bad tile width %d", tile_n);
-  const int n_tiles = (int)((N + bn - 1) / bn);
-  // pushes into this rank per call: every rank, every column tile, every (32-row group, me) overlap
+  // split-K partial tiles live in the context's scratch region (its counters stay zero between launches)
+  void* ws = sb200_comm_scratch(comm);
+  const GemmPlan plan = plan_gemm(EPI_PUSH, T, N, K, 0, tile_cfg, comm->region_bytes);
+  SB_CHECK_ARG(plan.bn != 0, "gemm_rowpar: bad tile configuration %d", tile_cfg);
+  // pushes into this rank per call: what one rank's kernel reports for my rows, times the ranks
   const int rpr = p.ra.rows_per_rank;
   const int64_t lo = (int64_t)comm->rank * rpr, hi = (lo + rpr < T ? lo + rpr : T);  // my rows [lo, hi)
-  uint32_t groups = 0;
-  if (hi > lo) groups = (uint32_t)((hi - 1) / 32 - lo / 32 + 1);
+  const uint32_t per_rank = gemm_push_increments(plan, T, lo, hi);
   GemmArgs g = {};
   g.M = (int)T; g.N = (int)N; g.K = (int)K;
   g.head_size = 128;
   // validate the operands before touching the epoch bookkeeping (a failed call must not desynchronise ranks)
   CUtensorMap probe;
-  rc = make_tmap_2d(&probe, dtype, x, T, K, ldx, kBM, kBK);
+  rc = make_tmap_2d(&probe, dtype, x, T, K, ldx, 128, kBK);
   if (rc) return rc;
-  rc = make_tmap_2d(&probe, dtype, w, N, K, ldw, bn, kBK);
+  rc = make_tmap_2d(&probe, dtype, w, N, K, ldw, plan.cta2 ? plan.bn / 2 : plan.bn, kBK);
   if (rc) return rc;
-  commit_call(comm, &p, (uint32_t)comm->world * (uint32_t)n_tiles * groups, out_ptr, resid_ptr);
-  return run_gemm_sm100(dtype, EPI_PUSH, bn, x, ldx, w, ldw, g, p.cv, p.ra, s);
+  commit_call(comm, &p, (uint32_t)comm->world * per_rank, out_ptr, resid_ptr);
+  return run_gemm_sm100(dtype, EPI_PUSH, plan, x, ldx, w, ldw, g, ws, p.cv, p.ra, s);
 }

@@ -12,7 +12,9 @@
 //   finish  : each rank waits until all rows have landed in its own buffers.
 // Row t is owned by rank t / rows_per_rank.  Buffers and counters are double
 // buffered by call parity (`set`); counters only ever grow and are compared
-// against per-call targets kept by the host, so nothing is reset on the device.
+// against cumulative targets that live next to them and are advanced on the
+// device at the end of each call, so nothing is reset and no per-call value
+// comes from the host (a captured CUDA graph of collectives can be replayed).
 // Two ranks can be at most one call apart because every call ends with the
 // finish wait, which needs every rank's reduce of the same call.
 // All waits are bounded; a wait that runs out sets the status word and the
@@ -32,7 +34,12 @@ enum CommCounter {
   CC_DONE0 = 2,   // finished rows received, set 0 / 1
   CC_DONE1 = 3,
   CC_STATUS = 4,  // first error recorded by a kernel on this rank (0 = none)
-  CC_BARRIER = 8, // [kMaxRanks] generic barrier slots
+  CC_PUSH_TGT0 = 8,   // cumulative number of pushes this rank has been promised, set 0 / 1
+  CC_PUSH_TGT1 = 9,   //   (advanced on the device by the last CTA of each collective kernel, so a
+  CC_DONE_TGT0 = 10,  //    captured CUDA graph can be replayed: no per-call host value is baked in)
+  CC_DONE_TGT1 = 11,
+  CC_EXIT_TICKET = 12,  // CTAs of the running collective kernel that have finished
+  CC_BARRIER = 16,      // [kMaxRanks] generic barrier slots
   CC_COUNT = 64
 };
 
@@ -62,6 +69,11 @@ __device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t* p) {
   asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
   return v;
 }
+__device__ __forceinline__ uint32_t ld_acquire_gpu(const uint32_t* p) {
+  uint32_t v;
+  asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
 __device__ __forceinline__ void red_release_sys_add(uint32_t* p, uint32_t v) {
   asm volatile("red.release.sys.global.add.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
 }
@@ -85,8 +97,8 @@ struct ReduceArgs {
   int T, H;               // rows of the whole batch, row length
   int rows_per_rank;      // ownership granule: owner(t) = t / rows_per_rank
   int set;                // call parity
-  uint32_t push_target;   // value CC_PUSH[set] must reach before this rank may reduce
-  uint32_t done_target;   // value CC_DONE[set] reaches when all T rows have landed
+  uint32_t push_per_call; // increments this rank's CC_PUSH[set] receives during this call
+  uint32_t done_per_call; // increments this rank's CC_DONE[set] receives during this call (= T)
   const void* bias;       // [H] or null, added after the sum (reference: layers.py:448-453)
   const void* residual;   // [T, H] local tensor or null: z = sum + residual
   const void* norm_w;     // [H] or null: also produce rms_norm(z) * norm_w
@@ -110,7 +122,10 @@ __device__ void reduce_phase(const CommView& c, const ReduceArgs& a, int warp_gl
   const int nrows = max(0, min(a.rows_per_rank, a.T - row0));
   if (nrows > 0) {
     bool ok = true;
-    if (lane == 0) ok = wait_counter(comm_counter(c, c.rank, CC_PUSH0 + a.set), a.push_target, a.wait_cycles);
+    if (lane == 0) {
+      const uint32_t target = *(volatile uint32_t*)comm_counter(c, c.rank, CC_PUSH_TGT0 + a.set) + a.push_per_call;
+      ok = wait_counter(comm_counter(c, c.rank, CC_PUSH0 + a.set), target, a.wait_cycles);
+    }
     ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
     if (!ok) {
       if (lane == 0) record_status(c, CS_TIMEOUT_PUSH);
@@ -199,12 +214,31 @@ __device__ void reduce_phase(const CommView& c, const ReduceArgs& a, int warp_gl
 __device__ __forceinline__ bool finish_phase(const CommView& c, const ReduceArgs& a) {
   __shared__ int s_ok;
   if (threadIdx.x == 0) {
-    const bool ok = wait_counter(comm_counter(c, c.rank, CC_DONE0 + a.set), a.done_target, a.wait_cycles);
+    const uint32_t target = *(volatile uint32_t*)comm_counter(c, c.rank, CC_DONE_TGT0 + a.set) + a.done_per_call;
+    const bool ok = wait_counter(comm_counter(c, c.rank, CC_DONE0 + a.set), target, a.wait_cycles);
     if (!ok) record_status(c, CS_TIMEOUT_DONE);
     s_ok = ok ? 1 : 0;
   }
   __syncthreads();
   return s_ok != 0;
+}
+
+// Last step of every collective kernel, called by all threads of every CTA after their phases:
+// the last CTA to get here advances the cumulative targets of this call's set.  Every CTA has
+// read the old targets by then (it reads them before it can finish), and the next collective on
+// this set is a later kernel on the same stream.
+__device__ __forceinline__ void advance_targets(const CommView& c, const ReduceArgs& a) {
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    __threadfence();
+    uint32_t* ticket = comm_counter(c, c.rank, CC_EXIT_TICKET);
+    if (atomicAdd(ticket, 1u) == gridDim.x - 1) {
+      *(volatile uint32_t*)comm_counter(c, c.rank, CC_PUSH_TGT0 + a.set) += a.push_per_call;
+      *(volatile uint32_t*)comm_counter(c, c.rank, CC_DONE_TGT0 + a.set) += a.done_per_call;
+      *(volatile uint32_t*)ticket = 0;
+      __threadfence();
+    }
+  }
 }
 
 // Copy rows owned by OTHER ranks from the local heap regions into the caller's tensors.

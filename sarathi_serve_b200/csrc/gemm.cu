@@ -4,6 +4,7 @@
 #include "gemm_host.cuh"
 
 #include <mutex>
+#include <stdlib.h>
 
 namespace sb200 {
 
@@ -57,89 +58,211 @@ int make_tmap_2d(CUtensorMap* map, int dtype, const void* ptr, int64_t rows, int
 }
 
 // ------------------------------------------------------------ tile selection
-int choose_bn(int epi, int64_t M, int64_t N, int head_size, int tile_n) {
-  const int64_t m_tiles = (M + kBM - 1) / kBM;
+// Analytical choice of (CTA pairing, MI, BN, scheduling): estimated SM clocks of the slowest unit.
+//   main loop per k-block = max(tensor time, shared-memory traffic of the stage at 128 B/clk
+//   (TMA writes + operand reads of the MMAs), L2 -> shared-memory time of the stage);
+//   data-parallel: whole tiles per unit (no fix-up, but units may get unequal tile counts);
+//   stream-K: every unit gets the same number of k-blocks and tiles cut along K are summed
+//   through the workspace by the last unit to arrive.
+GemmPlan plan_gemm(int epi, int64_t M, int64_t N, int64_t K, int head_size, int tile_cfg, size_t ws_bytes) {
+  GemmPlan best = {};
   const int sms = sm_count();
-  auto allowed = [&](int bn) {
-    if (epi == EPI_ROTARY) return bn % head_size == 0;
-    return true;
-  };
-  if (tile_n == 64 || tile_n == 128 || tile_n == 256) return allowed(tile_n) ? tile_n : 0;
-  // Largest tile that still gives every SM a tile; otherwise the smallest allowed tile.
-  const int cands[3] = {256, 128, 64};
-  int smallest = 0;
-  for (int bn : cands) {
-    if (!allowed(bn)) continue;
-    smallest = bn;
-    const int64_t cols_per_tile = (epi == EPI_SILU_MUL) ? bn / 2 : bn;
-    const int64_t out_cols = (epi == EPI_SILU_MUL) ? N / 2 : N;
-    const int64_t tiles = m_tiles * ((out_cols + cols_per_tile - 1) / cols_per_tile);
-    if (tiles >= sms) return bn;
+  const int k_blocks = (int)((K + kBK - 1) / kBK);
+  const int64_t out_cols = (epi == EPI_SILU_MUL) ? N / 2 : N;
+  // explicit configuration: BN + 1000*MODE + 100000*S.  MODE = 1|2: accumulators of one CTA;
+  // 3|4: CTA pairs with 1|2 accumulators.  S = 0|1: whole tiles per unit; S >= 2: cut along K so
+  // that about S units share a tile.
+  int f_bn = 0, f_mode = 0, f_s = 0;
+  if (tile_cfg > 0) {
+    f_s = tile_cfg / 100000;
+    f_mode = (tile_cfg / 1000) % 100;
+    f_bn = tile_cfg % 1000;
+    if (f_mode == 0) f_mode = 1;
+    if (f_s == 0) f_s = 1;
   }
-  return smallest;
+  double best_cost = 1e30;
+  for (int mode = 1; mode <= 4; ++mode) {
+    if (f_mode && mode != f_mode) continue;
+    const int cta2 = mode >= 3 ? 1 : 0;
+    const int mi = cta2 ? mode - 2 : mode;
+    for (int bn = 32; bn <= 256; bn += 32) {
+      if (f_bn && bn != f_bn) continue;
+      if (epi == EPI_ROTARY && bn % head_size != 0) continue;
+      if (epi == EPI_SILU_MUL && bn % 64 != 0) continue;
+      if (cta2 && bn % 64 != 0) continue;  // each CTA of a pair keeps bn/2 rows of B: whole 32-column chunks
+      if (!f_bn && bn < 64) continue;
+      const int stages = gemm_max_stages(mi, bn, cta2);
+      if (stages < 2) continue;
+      const int bm = (cta2 ? 256 : 128) * mi;
+      const int m_tiles = (int)((M + bm - 1) / bm);
+      const int cols_per_tile = (epi == EPI_SILU_MUL) ? bn / 2 : bn;
+      const int n_tiles = (int)((out_cols + cols_per_tile - 1) / cols_per_tile);
+      const int64_t tiles = (int64_t)m_tiles * n_tiles;
+      if (!f_mode && bm > 128 && M <= bm / 2) continue;  // half of the tile would be empty
+      const int units_max = cta2 ? sms / 2 : sms;     // CTAs or CTA pairs that run at once
+      const int64_t total = tiles * k_blocks;
+      // per-k-block clocks of one SM
+      const double stage = gemm_stage_bytes(mi, bn, cta2);
+      const double mma = 2.0 * mi * bn;                                        // tensor pipe
+      const double b_rows = cta2 ? bn / 2.0 : bn;
+      const double smem_rd = mi * (128 + b_rows) * kBK * 2;                    // operands the MMAs read
+      double per_kb = mma;
+      if ((stage + smem_rd) / 128.0 > per_kb) per_kb = (stage + smem_rd) / 128.0;
+      if (stage / 44.0 > per_kb) per_kb = stage / 44.0;  // L2 -> SM at ~44 B/clk/SM when every SM pulls
+      const double epi_units = (mi == 2 ? bn / 32.0 : bn / 64.0);
+      const double epi_c = epi_units * 450.0 + 400.0;
+      const bool dbuf = mi * bn * 2 <= 512;
+      const int64_t G = tiles < units_max ? tiles : units_max;
+      const int64_t tiles_full = (tiles / G) * G, rem = tiles - tiles_full;
+      const double full_item = dbuf ? (k_blocks * per_kb > epi_c ? k_blocks * per_kb : epi_c) : k_blocks * per_kb + epi_c;
+      for (int sp = 1; sp <= 8; ++sp) {  // parts the tiles of the last partial round are cut into
+        if (f_s && sp != f_s) continue;
+        int64_t units = G;
+        int kbp = k_blocks;
+        double cost = 2500.0 + (dbuf ? epi_c : 0.0);
+        if (tiles >= units_max || sp == 1) cost += (tiles_full / G) * full_item;
+        if (sp == 1) {
+          if (rem) cost += full_item;
+        } else {
+          // cutting only pays (and is only allowed) when the parts fit into one extra round
+          const int64_t rem_t = rem ? rem : 0;
+          if (rem_t == 0 && tiles >= units_max) continue;
+          const int64_t cut_tiles = rem_t ? rem_t : tiles;  // fewer tiles than units: all of them are "the last round"
+          if (sp > k_blocks / 2) break;
+          if (tiles < units_max) units = (cut_tiles * sp < units_max) ? cut_tiles * sp : units_max;
+          const size_t need = kWsCounterBytes + (size_t)cut_tiles * sp * bm * bn * sizeof(float);
+          if (need > ws_bytes || (size_t)cut_tiles * 32 * sizeof(uint32_t) > kWsCounterBytes) continue;
+          if (cut_tiles * sp > units) continue;  // all parts of a tile must run at the same time (one round)
+          kbp = (k_blocks + sp - 1) / sp;
+          if ((int64_t)(sp - 1) * kbp >= k_blocks) continue;  // an empty part
+          const int64_t rounds = (cut_tiles * sp + units - 1) / units;
+          const double fix = epi_units * (300.0 + 130.0 * sp) + 2500.0;  // dump + summed re-read
+          cost += rounds * (kbp * per_kb + (dbuf ? 300.0 : epi_c)) + fix;
+        }
+        if (cost < best_cost) {
+          best_cost = cost;
+          best.cta2 = cta2; best.mi = mi; best.bn = bn;
+          best.units = (int)units;
+          best.tiles_full = (tiles >= units_max) ? (int)tiles_full : (sp > 1 ? 0 : (int)tiles_full);
+          best.rem_splits = sp; best.kb_per_part = kbp;
+          best.stages = stages; best.m_tiles = m_tiles; best.n_tiles = n_tiles; best.k_blocks = k_blocks;
+          best.est_clocks = cost;
+        }
+      }
+    }
+  }
+  // a forced cut along K that is impossible (workspace too small, or it degenerates to whole tiles)
+  if (best.bn == 0 && tile_cfg >= 100000) return plan_gemm(epi, M, N, K, head_size, tile_cfg % 100000, ws_bytes);
+  return best;
 }
 
-template <typename T, int BN, int EPI>
+// Increments the row-parallel kernel of every rank adds to the push counter of the rank that owns
+// rows [lo, hi): one per (tile, epilogue slot whose 32 rows overlap the range), times the number of
+// K-parts for tiles that are cut (every part finishes a share of such a tile and reports it).
+uint32_t gemm_push_increments(const GemmPlan& p, int64_t M, int64_t lo, int64_t hi) {
+  if (hi <= lo) return 0;
+  const int bm = (p.cta2 ? 256 : 128) * p.mi;
+  const uint32_t slots_per_group = p.mi == 1 ? 2u : 1u;  // warps of a tile that cover the same 32 rows
+  const int64_t tiles = (int64_t)p.m_tiles * p.n_tiles;
+  uint64_t total = 0;
+  for (int mt = 0; mt < p.m_tiles; ++mt) {
+    const int64_t r0 = (int64_t)mt * bm, r1 = (r0 + bm < M ? r0 + bm : M);
+    uint32_t groups = 0;
+    for (int64_t g0 = r0; g0 < r1; g0 += 32) {
+      const int64_t g1 = (g0 + 32 < r1 ? g0 + 32 : r1);
+      if (g0 < hi && g1 > lo) ++groups;
+    }
+    if (!groups) continue;
+    // tiles mt, mt + m_tiles, ... : whole ones below tiles_full, cut ones from there on
+    uint64_t weight = 0;
+    for (int64_t t = mt; t < tiles; t += p.m_tiles) weight += (t < p.tiles_full) ? 1 : (uint64_t)p.rem_splits;
+    total += (uint64_t)groups * slots_per_group * weight;
+  }
+  return (uint32_t)total;
+}
+
+// Distance (k-blocks) of the L2 prefetch of weight boxes; SB200_L2_PREFETCH overrides (0 disables).
+static int l2_prefetch_distance() {
+  static int v = -1;
+  if (v < 0) {
+    const char* e = getenv("SB200_L2_PREFETCH");
+    v = e ? atoi(e) : 0;
+    if (v < 0) v = 0;
+  }
+  return v;
+}
+
+template <typename T, int EPI, bool CTA2, int MI>
 static int launch_sm100(const CUtensorMap& ta, const CUtensorMap& tb, const GemmArgs& g, const CommView& cv,
                         const ReduceArgs& ra, cudaStream_t s) {
-  using S = GemmSmem<BN>;
-  auto kern = gemm_sm100_kernel<T, BN, EPI>;
+  auto kern = gemm_sm100_kernel<T, EPI, CTA2, MI>;
   static thread_local int configured_dev = -1;
   int dev = 0;
   SB_CUDA(cudaGetDevice(&dev));
   if (configured_dev != dev) {
-    SB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, S::kTotal));
+    SB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBudget));
     configured_dev = dev;
   }
-  const int tiles = g.m_tiles * g.n_tiles;
-  int grid = tiles < sm_count() ? tiles : sm_count();
-  if (EPI == EPI_PUSH && grid < 1) grid = 1;
-  kern<<<grid, kGemmThreads, S::kTotal, s>>>(ta, tb, g, cv, ra);
-  SB_CHECK_LAUNCH("gemm_sm100_kernel");
+  const int smem = g.stages * gemm_stage_bytes(g.mi, g.bn, CTA2 ? 1 : 0) + kBarrierBytes + 1024;
+  int grid = g.units;
+  if (grid < 1) grid = 1;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(CTA2 ? 2 * grid : grid);
+  cfg.blockDim = dim3(kGemmThreads);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = s;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = CTA2 ? 2 : 1;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  SB_CUDA(cudaLaunchKernelEx(&cfg, kern, ta, tb, g, cv, ra));
   return SB200_OK;
 }
 
 template <typename T, int EPI>
-static int dispatch_bn(int bn, const CUtensorMap& ta, const CUtensorMap& tb, const GemmArgs& g, const CommView& cv,
+static int launch_mode(const CUtensorMap& ta, const CUtensorMap& tb, const GemmArgs& g, const CommView& cv,
                        const ReduceArgs& ra, cudaStream_t s) {
-  switch (bn) {
-    case 64: return launch_sm100<T, 64, EPI>(ta, tb, g, cv, ra, s);
-    case 128: return launch_sm100<T, 128, EPI>(ta, tb, g, cv, ra, s);
-    case 256: return launch_sm100<T, 256, EPI>(ta, tb, g, cv, ra, s);
-  }
-  set_error("unsupported GEMM tile width %d", bn);
-  return SB200_ERR_UNSUPPORTED;
+  if (g.cta2) return g.mi == 2 ? launch_sm100<T, EPI, true, 2>(ta, tb, g, cv, ra, s) : launch_sm100<T, EPI, true, 1>(ta, tb, g, cv, ra, s);
+  return g.mi == 2 ? launch_sm100<T, EPI, false, 2>(ta, tb, g, cv, ra, s) : launch_sm100<T, EPI, false, 1>(ta, tb, g, cv, ra, s);
 }
 
 template <typename T>
-static int dispatch_epi(int epi, int bn, const CUtensorMap& ta, const CUtensorMap& tb, const GemmArgs& g,
+static int dispatch_epi(int epi, const CUtensorMap& ta, const CUtensorMap& tb, const GemmArgs& g,
                         const CommView& cv, const ReduceArgs& ra, cudaStream_t s) {
   switch (epi) {
-    case EPI_STORE: return dispatch_bn<T, EPI_STORE>(bn, ta, tb, g, cv, ra, s);
-    case EPI_ROTARY: return dispatch_bn<T, EPI_ROTARY>(bn, ta, tb, g, cv, ra, s);
-    case EPI_SILU_MUL: return dispatch_bn<T, EPI_SILU_MUL>(bn, ta, tb, g, cv, ra, s);
-    case EPI_PUSH: return dispatch_bn<T, EPI_PUSH>(bn, ta, tb, g, cv, ra, s);
+    case EPI_STORE: return launch_mode<T, EPI_STORE>(ta, tb, g, cv, ra, s);
+    case EPI_ROTARY: return launch_mode<T, EPI_ROTARY>(ta, tb, g, cv, ra, s);
+    case EPI_SILU_MUL: return launch_mode<T, EPI_SILU_MUL>(ta, tb, g, cv, ra, s);
+    case EPI_PUSH: return launch_mode<T, EPI_PUSH>(ta, tb, g, cv, ra, s);
   }
   set_error("unknown GEMM epilogue %d", epi);
   return SB200_ERR_INVALID_ARGUMENT;
 }
 
-int run_gemm_sm100(int dtype, int epi, int tile_n, const void* x, int64_t ldx, const void* w, int64_t ldw,
-                   GemmArgs g, const CommView& cv, const ReduceArgs& ra, cudaStream_t s) {
-  const int bn = choose_bn(epi, g.M, g.N, g.head_size, tile_n);
-  SB_CHECK_ARG(bn != 0, "no GEMM tile width fits epilogue %d (head_size=%d, tile_n=%d)", epi, g.head_size, tile_n);
-  const int out_cols_per_tile = (epi == EPI_SILU_MUL) ? bn / 2 : bn;
-  const int64_t out_cols = (epi == EPI_SILU_MUL) ? g.N / 2 : g.N;
-  g.m_tiles = (g.M + kBM - 1) / kBM;
-  g.n_tiles = (int)((out_cols + out_cols_per_tile - 1) / out_cols_per_tile);
-  g.k_blocks = (g.K + kBK - 1) / kBK;
+int run_gemm_sm100(int dtype, int epi, const GemmPlan& plan, const void* x, int64_t ldx, const void* w, int64_t ldw,
+                   GemmArgs g, void* workspace, const CommView& cv, const ReduceArgs& ra, cudaStream_t s) {
+  SB_CHECK_ARG(plan.bn != 0, "no GEMM tile shape fits epilogue %d (head_size=%d)", epi, g.head_size);
+  g.cta2 = plan.cta2;
+  g.mi = plan.mi; g.bn = plan.bn; g.units = plan.units; g.tiles_full = plan.tiles_full;
+  g.rem_splits = plan.rem_splits; g.kb_per_part = plan.kb_per_part;
+  g.l2_prefetch = l2_prefetch_distance();
+  { const char* e = getenv("SB200_DEBUG"); g.debug = e ? atoi(e) : 0; }
+  g.stages = plan.stages; g.m_tiles = plan.m_tiles; g.n_tiles = plan.n_tiles; g.k_blocks = plan.k_blocks;
+  if (plan.rem_splits > 1) {
+    SB_CHECK_ARG(workspace && aligned16(workspace), "stream-K scheduling needs an aligned workspace");
+    g.ws_counters = reinterpret_cast<uint32_t*>(workspace);
+    g.ws = reinterpret_cast<float*>(reinterpret_cast<char*>(workspace) + kWsCounterBytes);
+  }
   CUtensorMap ta, tb;
-  int rc = make_tmap_2d(&ta, dtype, x, g.M, g.K, ldx, kBM, kBK);
+  int rc = make_tmap_2d(&ta, dtype, x, g.M, g.K, ldx, 128, kBK);
   if (rc) return rc;
-  rc = make_tmap_2d(&tb, dtype, w, g.N, g.K, ldw, (epi == EPI_SILU_MUL) ? bn / 2 : bn, kBK);
+  rc = make_tmap_2d(&tb, dtype, w, g.N, g.K, ldw, (epi == EPI_SILU_MUL || plan.cta2) ? plan.bn / 2 : plan.bn, kBK);
   if (rc) return rc;
-  if (dtype == SB200_BF16) return dispatch_epi<__nv_bfloat16>(epi, bn, ta, tb, g, cv, ra, s);
-  if (dtype == SB200_F16) return dispatch_epi<__half>(epi, bn, ta, tb, g, cv, ra, s);
+  if (dtype == SB200_BF16) return dispatch_epi<__nv_bfloat16>(epi, ta, tb, g, cv, ra, s);
+  if (dtype == SB200_F16) return dispatch_epi<__half>(epi, ta, tb, g, cv, ra, s);
   set_error("tcgen05 GEMM supports bf16/fp16 only");
   return SB200_ERR_UNSUPPORTED;
 }
@@ -195,7 +318,8 @@ using namespace sb200;
 
 extern "C" int sb200_gemm_colpar(void* out, int64_t ldo, const void* x, int64_t ldx, const void* w, int64_t ldw,
                                  const void* bias, int64_t T, int64_t N, int64_t K, int dtype, int epilogue,
-                                 const sb200_rotary_args* rot, uint32_t* status, int tile_n, sb200_stream_t stream) {
+                                 const sb200_rotary_args* rot, uint32_t* status, int tile_cfg, void* workspace,
+                                 int64_t workspace_bytes, sb200_stream_t stream) {
   SB_CHECK_ARG(T >= 0 && N > 0 && K > 0 && T <= INT32_MAX && N <= INT32_MAX && K <= INT32_MAX,
                "gemm_colpar: bad shape T=%lld N=%lld K=%lld", (long long)T, (long long)N, (long long)K);
   if (T == 0) return SB200_OK;
@@ -232,5 +356,20 @@ extern "C" int sb200_gemm_colpar(void* out, int64_t ldo, const void* x, int64_t 
   }
   CommView cv = {};
   ReduceArgs ra = {};
-  return run_gemm_sm100(dtype, epi, tile_n, x, ldx, w, ldw, g, cv, ra, s);
+  const GemmPlan plan = plan_gemm(epi, T, N, K, g.head_size, tile_cfg, workspace ? (size_t)workspace_bytes : 0);
+  return run_gemm_sm100(dtype, epi, plan, x, ldx, w, ldw, g, workspace, cv, ra, s);
+}
+
+// The tile shape and schedule sb200_gemm_colpar / sb200_gemm_rowpar would use (for tuning and tests).
+// out[0..10] = cta2, mi, bn, units, tiles_full, rem_splits, kb_per_part, stages, m_tiles, n_tiles, k_blocks.
+extern "C" int sb200_gemm_plan(int epilogue, int64_t T, int64_t N, int64_t K, int head_size, int tile_cfg,
+                               int64_t workspace_bytes, int* out) {
+  SB_CHECK_ARG(out != nullptr && T > 0 && N > 0 && K > 0, "gemm_plan: bad arguments");
+  const int epi = epilogue == SB200_EPI_ROTARY ? EPI_ROTARY : epilogue == SB200_EPI_SILU_MUL ? EPI_SILU_MUL
+                  : epilogue == 3 ? EPI_PUSH : EPI_STORE;
+  const GemmPlan p = plan_gemm(epi, T, N, K, head_size ? head_size : 128, tile_cfg, (size_t)workspace_bytes);
+  const int v[11] = {p.cta2, p.mi, p.bn, p.units, p.tiles_full, p.rem_splits, p.kb_per_part, p.stages, p.m_tiles,
+                     p.n_tiles, p.k_blocks};
+  for (int i = 0; i < 11; ++i) out[i] = v[i];
+  return p.bn ? SB200_OK : SB200_ERR_UNSUPPORTED;
 }

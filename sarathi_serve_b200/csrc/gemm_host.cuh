@@ -8,9 +8,18 @@ namespace sb200 {
 
 int make_tmap_2d(CUtensorMap* map, int dtype, const void* ptr, int64_t rows, int64_t cols, int64_t ld_elems,
                  int box_rows, int box_cols);
-int choose_bn(int epi, int64_t M, int64_t N, int head_size, int tile_n);
-int run_gemm_sm100(int dtype, int epi, int tile_n, const void* x, int64_t ldx, const void* w, int64_t ldw, GemmArgs g,
-                   const CommView& cv, const ReduceArgs& ra, cudaStream_t s);
+// First bytes of a split-K workspace hold the per-(tile, slot) arrival counters (zero between launches).
+constexpr size_t kWsCounterBytes = 64 * 1024;
+
+struct GemmPlan {
+  int cta2, mi, bn, units, tiles_full, rem_splits, kb_per_part, stages, m_tiles, n_tiles, k_blocks;
+  double est_clocks;
+};
+// tile_cfg: 0 = choose; else BN + 1000*MODE + 100000*S (MODE 1|2: one CTA, 3|4: CTA pairs; S >= 2: cut along K).  ws_bytes: split-K workspace available (0 = none).
+GemmPlan plan_gemm(int epi, int64_t M, int64_t N, int64_t K, int head_size, int tile_cfg, size_t ws_bytes);
+uint32_t gemm_push_increments(const GemmPlan& p, int64_t M, int64_t lo, int64_t hi);
+int run_gemm_sm100(int dtype, int epi, const GemmPlan& plan, const void* x, int64_t ldx, const void* w, int64_t ldw,
+                   GemmArgs g, void* workspace, const CommView& cv, const ReduceArgs& ra, cudaStream_t s);
 int run_gemm_f32(float* C, int64_t ldc, const float* A, int64_t lda, const float* B, int64_t ldb, const float* bias,
                  int M, int N, int K, cudaStream_t s);
 

@@ -1,14 +1,30 @@
 // Persistent, warp-specialised bf16/fp16 GEMM for sm_100a:
 //   C[M, N] = A[M, K] * B[N, K]^T        (both operands K-major, fp32 accumulate)
 // TMA (128-byte swizzle) feeds a multi-stage shared-memory ring, one elected
-// thread issues tcgen05.mma into a double-buffered TMEM accumulator, and four
-// epilogue warps drain TMEM with tcgen05.ld while the next tile's main loop
-// runs.  Row-major nn.Linear weights [out, in] are consumed as the K-major B
-// operand as they are.
+// thread issues tcgen05.mma into TMEM accumulators, and eight epilogue warps
+// drain TMEM with tcgen05.ld.  Row-major nn.Linear weights [out, in] are
+// consumed as the K-major B operand as they are.
 //
-// Roles (192 threads): warp 0 = TMA producer, warp 1 = TMEM owner + MMA issuer,
-// warps 2..5 = epilogue (warp w drains TMEM lanes 32*(w%4) .. +31, i.e. rows of
-// the 128-row tile).
+// Tile shape is a run-time choice of the host (gemm.cu):
+//   BM = 128 * MI rows  (MI = 1 or 2 accumulators that share every B tile: with
+//                        MI = 2 each weight byte crosses L2 -> shared memory
+//                        half as often per flop); 256 * MI rows for CTA pairs,
+//   BN = 32..256 columns in steps of 32 (UMMA N),
+//   scheduling: whole tiles go round-robin to the G scheduling units (CTAs or
+//        CTA pairs) for as many full rounds as there are; the tiles of the
+//        last, partial round (all tiles, when there are fewer than G) can be
+//        cut along K into S parts so that they still occupy all units.  Every
+//        part leaves an fp32 partial tile in a workspace, and the last one to
+//        arrive (per 32-row slot) sums the parts in part order and runs the
+//        epilogue.  So neither wave quantisation nor a small tile count leaves
+//        SMs idle, and the result does not depend on arrival order.
+// When MI * BN <= 256 the accumulators are double buffered in TMEM and the
+// epilogue of tile i overlaps the main loop of tile i+1.
+//
+// Roles (320 threads): warp 0 = TMA producer, warp 1 = TMEM owner + MMA issuer,
+// warps 2..9 = epilogue.  Epilogue warp w may read TMEM lanes 32*(w%4)..+31
+// (rows of a 128-row accumulator); the two warps that share a lane quarter
+// split the work by accumulator (MI = 2) or by alternating work units (MI = 1).
 //
 // Epilogues (the reference ops they absorb are cited where they are defined):
 //   EPI_STORE    out = acc (+ bias)
@@ -26,9 +42,11 @@ namespace sb200 {
 
 enum GemmEpilogue { EPI_STORE = 0, EPI_ROTARY = 1, EPI_SILU_MUL = 2, EPI_PUSH = 3 };
 
-constexpr int kBM = 128;          // tile rows  (UMMA M)
-constexpr int kBK = 64;           // K elements per stage: 128 bytes of bf16 = one swizzle row
-constexpr int kGemmThreads = 192;
+constexpr int kBK = 64;            // K elements per stage: 128 bytes of bf16 = one swizzle row
+constexpr int kGemmThreads = 320;  // 10 warps
+constexpr int kEpiWarps = 8;
+constexpr int kSmemBudget = 226 * 1024;  // dynamic shared memory requested (static use is a few bytes)
+constexpr int kBarrierBytes = 1024;
 
 struct GemmArgs {
   int M, N, K;             // N counts B rows (for EPI_SILU_MUL: 2*d)
@@ -41,19 +59,31 @@ struct GemmArgs {
   int head_size;
   int rot_cols;            // columns [0, rot_cols) hold q and k heads, the rest (v) is stored as is
   int is_neox;
-  // tiling
+  // tiling (host-chosen)
+  int mi;                  // accumulators per tile (BM = 128 * mi)
+  int bn;                  // tile columns
+  int units;               // G: scheduling units launched (CTAs, or CTA pairs)
+  int tiles_full;          // tiles handed out whole, round-robin (a multiple of units)
+  int rem_splits;          // S: parts each remaining tile is cut into along K (1 = not cut)
+  int kb_per_part;         // k-blocks per part
+  int stages;              // shared-memory ring depth
+  int l2_prefetch;         // k-blocks ahead at which the B boxes are prefetched into L2 (0 = off)
+  int debug;               // profiling switches (0 in production)
   int m_tiles, n_tiles, k_blocks;
+  float* ws;               // partial-tile workspace: [cut tiles * S][BM][bn] fp32
+  uint32_t* ws_counters;   // [cut tiles][arrived[16], done[16]], zero between launches
+  int cta2;                // 1: tiles of 256 rows computed by CTA pairs (cta_group::2)
   uint32_t* status;        // device word: first error of this launch (0 = none); may be null
 };
 
-template <int BN> struct GemmSmem {
-  static constexpr int kStageBytesA = kBM * kBK * 2;
-  static constexpr int kStageBytesB = BN * kBK * 2;
-  static constexpr int kStageBytes = kStageBytesA + kStageBytesB;
-  static constexpr int kStages = (BN == 256) ? 4 : (BN == 128 ? 6 : 8);
-  static constexpr int kBarrierBytes = 1024;
-  static constexpr int kTotal = kStages * kStageBytes + kBarrierBytes + 1024;  // + alignment slack
-};
+// Shared memory of one pipeline stage in one CTA (a CTA of a pair keeps half of the B tile).
+__host__ __device__ inline int gemm_stage_bytes(int mi, int bn, int cta2 = 0) {
+  return cta2 ? (mi * 128 + bn / 2) * kBK * 2 : (mi * 128 + bn) * kBK * 2;
+}
+__host__ __device__ inline int gemm_max_stages(int mi, int bn, int cta2 = 0) {
+  int s = (kSmemBudget - kBarrierBytes - 1024) / gemm_stage_bytes(mi, bn, cta2);
+  return s > 8 ? 8 : s;
+}
 
 template <typename T> struct Pack2;
 template <> struct Pack2<__nv_bfloat16> {
@@ -99,29 +129,276 @@ __device__ __forceinline__ void load_row32(const T* src, float* f) {
   }
 }
 
+// Where an epilogue warp gets the fp32 accumulator chunk (32 columns of its row) from.
+struct TmemSource {
+  uint32_t row_addr;  // TMEM address of (lane quarter, first column of the accumulator)
+  __device__ __forceinline__ void load32(int col, float* f) const {
+    uint32_t r[32];
+    ptx::tmem_ld_32x32(row_addr + (uint32_t)col, r);
+#pragma unroll
+    for (int j = 0; j < 32; ++j) f[j] = __uint_as_float(r[j]);
+  }
+};
+// Scheduling.  Tiles are numbered M-fastest.  With G scheduling units (CTAs or CTA pairs):
+//   * the first `tiles_full` tiles (a multiple of G) are handed out round-robin, whole: unit p
+//     computes tiles p, p+G, ...  Neighbouring units then work on the M-tiles of the same
+//     weight tile at the same time, so a weight tile comes from HBM once and hits in L2 after;
+//   * each of the remaining `rem_tiles` tiles is cut along K into S parts of `kbp` k-blocks
+//     (S = 1: not cut), and the rem_tiles*S parts are handed out round-robin as well.  A part
+//     leaves an fp32 partial tile in workspace slot `part index`; the last part of a tile to
+//     arrive (per 32-row slot) sums all S in part order and runs the epilogue.
+struct Sched {
+  int G, tiles_full, rem_tiles, S, kbp, k_blocks;
+};
+struct Segment {
+  int tile, kb0, kb1;
+  int parts;       // parts this tile is cut into (1: whole)
+  int part_slot;   // workspace slot of this part; the tile's parts are slots first_slot .. first_slot+parts-1
+  int first_slot;
+  int rem_index;   // index of the tile among the cut tiles (selects its arrival counters)
+  bool valid;
+};
+// it-th work item of unit p.
+__device__ __forceinline__ Segment segment_of(const Sched& sc, int p, int it) {
+  Segment sg;
+  sg.valid = true;
+  const int nA = sc.tiles_full / sc.G;
+  if (it < nA) {
+    sg.tile = p + it * sc.G;
+    sg.kb0 = 0; sg.kb1 = sc.k_blocks; sg.parts = 1; sg.part_slot = 0; sg.first_slot = 0; sg.rem_index = 0;
+    return sg;
+  }
+  const long long j = (long long)p + (long long)(it - nA) * sc.G;
+  if (j >= (long long)sc.rem_tiles * sc.S) { sg.valid = false; return sg; }
+  const int rt = (int)(j / sc.S), sp = (int)(j - (long long)rt * sc.S);
+  sg.tile = sc.tiles_full + rt;
+  sg.kb0 = sp * sc.kbp;
+  sg.kb1 = min(sc.k_blocks, sg.kb0 + sc.kbp);
+  sg.parts = sc.S;
+  sg.part_slot = (int)j;
+  sg.first_slot = rt * sc.S;
+  sg.rem_index = rt;
+  return sg;
+}
+
+// Partial tiles are kept column-major in the workspace ([BN columns][BM rows] fp32): the 32 lanes
+// of an epilogue warp hold 32 consecutive rows, so every load / store instruction of a warp moves
+// one full 128-byte line and the 32 instructions of a chunk are independent of each other.
+struct WorkspaceSource {
+  const float* ws;       // first slot of the tile's parts, at this thread's row
+  size_t slot_stride;    // floats per slot (BM * BN)
+  int bm;                // rows of the tile = stride between columns
+  int parts;
+  __device__ __forceinline__ void load32(int col, float* f) const {
+#pragma unroll
+    for (int j = 0; j < 32; ++j) f[j] = 0.f;
+    int i = 0;
+    for (; i + 1 < parts; i += 2) {  // two parts in flight; the order of the additions stays 0, 1, 2, ...
+      const float* p0 = ws + (size_t)i * slot_stride + (size_t)col * bm;
+      const float* p1 = p0 + slot_stride;
+      float a[32], b[32];
+#pragma unroll
+      for (int j = 0; j < 32; ++j) { a[j] = __ldcg(p0 + (size_t)j * bm); b[j] = __ldcg(p1 + (size_t)j * bm); }
+#pragma unroll
+      for (int j = 0; j < 32; ++j) f[j] = (f[j] + a[j]) + b[j];
+    }
+    if (i < parts) {
+      const float* p0 = ws + (size_t)i * slot_stride + (size_t)col * bm;
+#pragma unroll
+      for (int j = 0; j < 32; ++j) f[j] += __ldcg(p0 + (size_t)j * bm);
+    }
+  }
+};
+
+// Per-thread view of the tile being finished.
+template <typename T> struct RowCtx {
+  int gm;          // global row of this thread
+  bool row_ok;
+  int n0;          // first global output column of the tile (for SILU_MUL: first column of d)
+  T* out_row;      // out + gm * ldo   (EPI_PUSH: the owner's partial slot row)
+  const T* cs;     // rotary: cache row of this token
+  bool vec_ok;
+};
+
+// Work units of a tile: the chunks an epilogue warp fetches together.
+//   STORE / PUSH : unit u = columns [32u, 32u+32)
+//   SILU_MUL     : unit u = gate columns [32u, ..) with up columns [bn/2 + 32u, ..)
+//   ROTARY       : unit u -> (head = u / upH, j = u % upH), upH = head_size/32 units per head;
+//                  for a NeoX-rotated head only j < upH/2 does work (chunks j and j + upH/2).
+template <int EPI> __device__ __forceinline__ int num_units(const GemmArgs& g) {
+  return EPI == EPI_SILU_MUL ? g.bn / 64 : g.bn / 32;
+}
+
+// Columns (inside the accumulator) a unit reads; returns how many chunks (0, 1 or 2).
+template <int EPI>
+__device__ __forceinline__ int unit_chunks(const GemmArgs& g, int n0, int u, int* cols) {
+  if (EPI == EPI_SILU_MUL) {
+    cols[0] = u * 32;
+    cols[1] = g.bn / 2 + u * 32;
+    return 2;
+  }
+  if (EPI == EPI_ROTARY) {
+    const int upH = g.head_size / 32;
+    const int head = u / upH, j = u - head * upH;
+    const bool rotate = (n0 + head * g.head_size) < g.rot_cols;
+    if (rotate && g.is_neox) {
+      if (j >= upH / 2) return 0;
+      cols[0] = head * g.head_size + j * 32;
+      cols[1] = cols[0] + g.head_size / 2;
+      return 2;
+    }
+    cols[0] = u * 32;
+    return 1;
+  }
+  cols[0] = u * 32;
+  return 1;
+}
+
+// Finish one unit: fetch its chunk(s) from `src`, apply the epilogue math, store.
+template <typename T, int EPI, typename Source>
+__device__ __forceinline__ void finish_unit(const GemmArgs& g, const RowCtx<T>& rc, const Source& src, int u) {
+  int cols[2];
+  const int nch = unit_chunks<EPI>(g, rc.n0, u, cols);
+  if (nch == 0) return;
+  float a[32];
+  src.load32(cols[0], a);  // warp-uniform (TMEM loads are .sync.aligned)
+  if constexpr (EPI == EPI_STORE || EPI == EPI_PUSH) {
+    const int gn = rc.n0 + cols[0];
+    if (rc.row_ok && gn < g.N) {
+      if (EPI == EPI_STORE && g.bias) {
+        const T* bias = reinterpret_cast<const T*>(g.bias);
+#pragma unroll
+        for (int j = 0; j < 32; ++j)
+          if (gn + j < g.N) a[j] += DT<T>::to_f(bias[gn + j]);
+      }
+      store_row32<T>(rc.out_row + gn, a, g.N - gn, rc.vec_ok);
+    }
+  } else if constexpr (EPI == EPI_SILU_MUL) {
+    // Reference: gate_up = F.linear(x) rounded to T, then silu_and_mul
+    // (csrc/activation_kernels.cu:8-25): out = (T)(silu(gate)) * up.
+    float b[32];
+    src.load32(cols[1], b);
+    const int d = g.N / 2;
+    const int gn = rc.n0 + cols[0];
+    if (rc.row_ok && gn < d) {
+#pragma unroll
+      for (int j = 0; j < 32; ++j) {
+        const float gte = rt<T>(a[j]), up = rt<T>(b[j]);
+        const float sl = rt<T>(gte / (1.0f + expf(-gte)));
+        a[j] = rt<T>(sl * up);
+      }
+      store_row32<T>(rc.out_row + gn, a, d - gn, rc.vec_ok);
+    }
+  } else {  // EPI_ROTARY
+    // Reference: F.linear output rounded to T (tensor_parallel/layers.py:278-284), then
+    // rotary_embedding in T arithmetic on the q and k heads (csrc/pos_encoding_kernels.cu:8-76).
+    const int gn = rc.n0 + cols[0];
+    if (nch == 2) {  // NeoX pair of chunks: x = cols[0].., y = x + head_size/2
+      float b[32];
+      src.load32(cols[1], b);
+      if (rc.row_ok && gn < g.N) {
+        const int half = g.head_size / 2;
+        const int in_head = cols[0] % g.head_size;  // = j*32
+        float co[32], si[32];
+        load_row32<T>(rc.cs + in_head, co);
+        load_row32<T>(rc.cs + half + in_head, si);
+#pragma unroll
+        for (int j = 0; j < 32; ++j) {
+          const float x = rt<T>(a[j]), y = rt<T>(b[j]);
+          a[j] = rt<T>(rt<T>(x * co[j]) - rt<T>(y * si[j]));
+          b[j] = rt<T>(rt<T>(y * co[j]) + rt<T>(x * si[j]));
+        }
+        store_row32<T>(rc.out_row + gn, a, g.N - gn, rc.vec_ok);
+        store_row32<T>(rc.out_row + gn + half, b, g.N - gn - half, rc.vec_ok);
+      }
+    } else if (rc.row_ok && gn < g.N) {
+      const int head0 = (cols[0] / g.head_size) * g.head_size;
+      if ((rc.n0 + head0) < g.rot_cols) {  // GPT-J style: pairs (2i, 2i+1), cos/sin index = column_in_head / 2
+        const int half = g.head_size / 2;
+        const int in_head = cols[0] - head0;
+#pragma unroll
+        for (int j = 0; j < 32; j += 2) {
+          const int p = (in_head + j) >> 1;
+          const float co = DT<T>::to_f(rc.cs[p]), si = DT<T>::to_f(rc.cs[half + p]);
+          const float x = rt<T>(a[j]), y = rt<T>(a[j + 1]);
+          a[j] = rt<T>(rt<T>(x * co) - rt<T>(y * si));
+          a[j + 1] = rt<T>(rt<T>(y * co) + rt<T>(x * si));
+        }
+      }
+      store_row32<T>(rc.out_row + gn, a, g.N - gn, rc.vec_ok);
+    }
+  }
+}
+
+// Per-thread context of the rows an epilogue warp finishes.
+template <typename T, int EPI>
+__device__ __forceinline__ RowCtx<T> make_row_ctx(const GemmArgs& g, const CommView& comm, const ReduceArgs& red,
+                                                  int gm, int n0) {
+  RowCtx<T> rc;
+  rc.gm = gm;
+  rc.row_ok = gm < g.M;
+  rc.n0 = n0;
+  rc.cs = nullptr;
+  if constexpr (EPI == EPI_PUSH) {
+    const int owner = rc.row_ok ? gm / red.rows_per_rank : 0;
+    const int lr = gm - owner * red.rows_per_rank;
+    rc.out_row = rc.row_ok ? reinterpret_cast<T*>(comm.heap[owner] + comm.partial_off[red.set]) +
+                                 ((size_t)comm.rank * red.rows_per_rank + lr) * (size_t)g.N
+                           : nullptr;
+    rc.vec_ok = (g.N & 7) == 0;
+  } else {
+    rc.out_row = reinterpret_cast<T*>(g.out) + (size_t)gm * g.ldo;
+    rc.vec_ok = ((g.ldo & 7) == 0) && aligned16(g.out);
+    if (EPI == EPI_ROTARY && rc.row_ok)
+      rc.cs = reinterpret_cast<const T*>(g.cos_sin) + g.positions[gm] * g.head_size;
+  }
+  return rc;
+}
+
 // ---------------------------------------------------------------------------
 // The kernel.  `comm` / `red` are used only by EPI_PUSH.
-template <typename T, int BN, int EPI>
+//   CTA2 = false: one CTA per tile of 128*MI x BN.
+//   CTA2 = true : a cluster of two CTAs per tile of 256 x BN (tcgen05 cta_group::2): CTA r of the
+//                 pair loads rows [128r, 128r+128) of the A tile and rows [r*BN/2, (r+1)*BN/2) of the
+//                 B tile, the even CTA issues the MMAs for both, each CTA drains its own 128
+//                 accumulator rows.  Per SM this halves the shared-memory traffic of the B operand.
+template <typename T, int EPI, bool CTA2, int MI>
 __global__ void __launch_bounds__(kGemmThreads, 1)
 gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                   const GemmArgs g, const CommView comm, const ReduceArgs red) {
-  using S = GemmSmem<BN>;
-  constexpr int kStages = S::kStages;
-  constexpr uint32_t kTmemCols = 2 * BN;  // two accumulator buffers (power of two >= 32)
-  constexpr uint32_t kIdesc = ptx::make_idesc(DT<T>::id == SB200_BF16 ? 1 : 0, BN);
+  constexpr uint32_t kTmemCols = 512;
+  const int BN = g.bn;  // (MI is a template parameter: the MMA issue loop must be fully unrolled)
+  const int BM = (CTA2 ? 256 : 128) * MI;        // rows of a tile
+  const int b_rows = CTA2 ? BN / 2 : BN;         // B rows this CTA keeps in shared memory
+  const int a_bytes = MI * 128 * kBK * 2;
+  const int stage_bytes = a_bytes + b_rows * kBK * 2;
+  const int kStages = g.stages;
+  const bool dbuf = (MI * BN * 2) <= (int)kTmemCols;  // room for two sets of accumulators
+  const uint32_t idesc = ptx::make_idesc(DT<T>::id == SB200_BF16 ? 1 : 0, BN, CTA2 ? 256 : 128);
+  const uint32_t cta_rank = CTA2 ? ptx::cluster_ctarank() : 0u;
+  const bool leader = cta_rank == 0;
+  const int unit_id = CTA2 ? (int)(blockIdx.x >> 1) : (int)blockIdx.x;     // CTA or CTA pair
+  const int num_units_grid = CTA2 ? (int)(gridDim.x >> 1) : (int)gridDim.x;
 
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* stage_base = smem;
-  uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + kStages * S::kStageBytes);
-  uint64_t* empty_bar = full_bar + kStages;
-  uint64_t* tmem_full = empty_bar + kStages;   // [2]
-  uint64_t* tmem_empty = tmem_full + 2;        // [2]
+  uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + (size_t)kStages * stage_bytes);
+  uint64_t* empty_bar = full_bar + 8;
+  uint64_t* tmem_full = empty_bar + 8;   // [2]
+  uint64_t* tmem_empty = tmem_full + 2;  // [2]
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tmem_empty + 2);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int num_tiles = g.m_tiles * g.n_tiles;
+  // this unit's work items
+  Sched sc;
+  sc.G = num_units_grid;
+  sc.tiles_full = g.tiles_full;
+  sc.rem_tiles = g.m_tiles * g.n_tiles - g.tiles_full;
+  sc.S = g.rem_splits;
+  sc.kbp = g.kb_per_part;
+  sc.k_blocks = g.k_blocks;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < kStages; ++s) {
@@ -130,7 +407,7 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
     }
     for (int b = 0; b < 2; ++b) {
       ptx::mbar_init(&tmem_full[b], 1);
-      ptx::mbar_init(&tmem_empty[b], 4);  // one arrival per epilogue warp
+      ptx::mbar_init(&tmem_empty[b], CTA2 ? 2 * kEpiWarps : kEpiWarps);  // one arrival per epilogue warp (of both CTAs)
     }
     *abort_flag = 0;
     ptx::mbar_fence_init();
@@ -140,11 +417,12 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
     ptx::prefetch_tensormap(&tmap_b);
   }
   if (warp == 1) {
-    ptx::tmem_alloc(tmem_slot, kTmemCols);
-    ptx::tmem_relinquish();
+    if (CTA2) { ptx::tmem_alloc_pair(tmem_slot, kTmemCols); ptx::tmem_relinquish_pair(); }
+    else      { ptx::tmem_alloc(tmem_slot, kTmemCols);      ptx::tmem_relinquish(); }
   }
   ptx::tc_fence_before();
   __syncthreads();
+  if (CTA2) ptx::cluster_sync_all();  // the peer's barriers are initialised before anything signals them
   ptx::tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
 
@@ -154,20 +432,48 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
-      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
-        const int mt = tile % g.m_tiles, nt = tile / g.m_tiles;
-        for (int kb = 0; kb < g.k_blocks; ++kb) {
+      for (int it = 0; ok; ++it) {
+        const Segment sg = segment_of(sc, unit_id, it);
+        if (!sg.valid) break;
+        const int mt = sg.tile % g.m_tiles, nt = sg.tile / g.m_tiles;
+        for (int kb = sg.kb0; kb < sg.kb1; ++kb) {
           if (!ptx::mbar_wait(&empty_bar[stage], phase ^ 1u, abort_flag)) { ok = false; break; }
-          uint8_t* sa = stage_base + stage * S::kStageBytes;
-          uint8_t* sb = sa + S::kStageBytesA;
-          ptx::mbar_expect_tx(&full_bar[stage], S::kStageBytes);
-          ptx::tma_load_2d(sa, &tmap_a, &full_bar[stage], kb * kBK, mt * kBM);
-          if (EPI == EPI_SILU_MUL) {
-            // B tile = BN/2 rows of the gate shard followed by the matching BN/2 rows of the up shard
-            ptx::tma_load_2d(sb, &tmap_b, &full_bar[stage], kb * kBK, nt * (BN / 2));
-            ptx::tma_load_2d(sb + S::kStageBytesB / 2, &tmap_b, &full_bar[stage], kb * kBK, g.N / 2 + nt * (BN / 2));
+          uint8_t* sa = stage_base + (size_t)stage * stage_bytes;
+          uint8_t* sb = sa + a_bytes;
+          if (g.l2_prefetch > 0 && kb + g.l2_prefetch < sg.kb1) {
+            // weights are read once: start their trip from HBM to L2 a few stages early
+            const int pk = (kb + g.l2_prefetch) * kBK;
+            if (CTA2) {
+              ptx::tma_prefetch_l2_2d(&tmap_b, pk, (EPI == EPI_SILU_MUL) ? (int)cta_rank * (g.N / 2) + nt * (BN / 2)
+                                                                        : nt * BN + (int)cta_rank * (BN / 2));
+            } else {
+              ptx::tma_prefetch_l2_2d(&tmap_b, pk, (EPI == EPI_SILU_MUL) ? nt * (BN / 2) : nt * BN);
+              if (EPI == EPI_SILU_MUL) ptx::tma_prefetch_l2_2d(&tmap_b, pk, g.N / 2 + nt * (BN / 2));
+            }
+          }
+          if constexpr (CTA2) {
+            // both CTAs' bytes are counted on the leader's barrier; only the leader announces them
+            const uint32_t bar = ptx::map_to_cta(ptx::smem_u32(&full_bar[stage]), 0);
+            if (leader) ptx::mbar_expect_tx(&full_bar[stage], (uint32_t)(2 * stage_bytes));
+#pragma unroll
+            for (int a = 0; a < MI; ++a)  // accumulator a covers tile rows [256a, 256a+256): this CTA's half of them
+              ptx::tma_load_2d_pair(sa + a * (128 * kBK * 2), &tmap_a, bar, kb * kBK, mt * BM + a * 256 + (int)cta_rank * 128);
+            if (EPI == EPI_SILU_MUL)  // even CTA: gate rows, odd CTA: the matching up rows
+              ptx::tma_load_2d_pair(sb, &tmap_b, bar, kb * kBK, (int)cta_rank * (g.N / 2) + nt * (BN / 2));
+            else
+              ptx::tma_load_2d_pair(sb, &tmap_b, bar, kb * kBK, nt * BN + (int)cta_rank * (BN / 2));
           } else {
-            ptx::tma_load_2d(sb, &tmap_b, &full_bar[stage], kb * kBK, nt * BN);
+            ptx::mbar_expect_tx(&full_bar[stage], (uint32_t)stage_bytes);
+#pragma unroll
+            for (int a = 0; a < MI; ++a)
+              ptx::tma_load_2d(sa + a * (128 * kBK * 2), &tmap_a, &full_bar[stage], kb * kBK, mt * BM + a * 128);
+            if (EPI == EPI_SILU_MUL) {
+              // B tile = BN/2 rows of the gate shard followed by the matching BN/2 rows of the up shard
+              ptx::tma_load_2d(sb, &tmap_b, &full_bar[stage], kb * kBK, nt * (BN / 2));
+              ptx::tma_load_2d(sb + (BN / 2) * (kBK * 2), &tmap_b, &full_bar[stage], kb * kBK, g.N / 2 + nt * (BN / 2));
+            } else {
+              ptx::tma_load_2d(sb, &tmap_b, &full_bar[stage], kb * kBK, nt * BN);
+            }
           }
           if (++stage == kStages) { stage = 0; phase ^= 1u; }
         }
@@ -175,186 +481,148 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
     }
   } else if (warp == 1) {
     // -------------------------------------------------------------- MMA issuer
-    if (lane == 0) {
+    if (lane == 0 && leader) {
       int stage = 0;
       uint32_t phase = 0;
       int local = 0;
       bool ok = true;
-      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++local) {
-        const int buf = local & 1;
-        const uint32_t use = (uint32_t)(local >> 1);  // how many times this buffer was used before
+      for (; ok; ++local) {
+        const Segment sg = segment_of(sc, unit_id, local);
+        if (!sg.valid) break;
+        const int kb0 = sg.kb0, kb1 = sg.kb1;
+        const int buf = dbuf ? (local & 1) : 0;
+        const uint32_t use = (uint32_t)(dbuf ? (local >> 1) : local);  // earlier uses of this buffer
         if (!ptx::mbar_wait(&tmem_empty[buf], (use & 1u) ^ 1u, abort_flag)) { ok = false; break; }
         ptx::tc_fence_after();
-        const uint32_t d_tmem = tmem_base + (uint32_t)(buf * BN);
-        for (int kb = 0; kb < g.k_blocks; ++kb) {
+        const uint32_t d_tmem = tmem_base + (uint32_t)(buf * MI * BN);
+        for (int kb = kb0; kb < kb1; ++kb) {
           if (!ptx::mbar_wait(&full_bar[stage], phase, abort_flag)) { ok = false; break; }
           ptx::tc_fence_after();
-          const uint32_t sa = ptx::smem_u32(stage_base + stage * S::kStageBytes);
-          const uint64_t da = ptx::make_smem_desc_sw128(sa);
-          const uint64_t db = ptx::make_smem_desc_sw128(sa + S::kStageBytesA);
+          const uint32_t sa = ptx::smem_u32(stage_base + (size_t)stage * stage_bytes);
+          const uint64_t db = ptx::make_smem_desc_sw128(sa + a_bytes);
 #pragma unroll
           for (int k = 0; k < kBK / 16; ++k) {
             // advance 16 elements = 32 bytes along K inside the swizzle row: +2 in 16-byte units
-            ptx::umma_f16(d_tmem, da + (uint64_t)(k * 2), db + (uint64_t)(k * 2), kIdesc, (kb | k) ? 1u : 0u);
+            const uint32_t acc = (kb > kb0 || k > 0) ? 1u : 0u;
+#pragma unroll
+            for (int a = 0; a < MI; ++a) {
+              const uint64_t da = ptx::make_smem_desc_sw128(sa + a * (128 * kBK * 2));
+              if (CTA2) ptx::umma_f16_pair(d_tmem + (uint32_t)(a * BN), da + (uint64_t)(k * 2), db + (uint64_t)(k * 2), idesc, acc);
+              else ptx::umma_f16(d_tmem + (uint32_t)(a * BN), da + (uint64_t)(k * 2), db + (uint64_t)(k * 2), idesc, acc);
+            }
           }
-          ptx::umma_commit(&empty_bar[stage]);  // frees the smem stage once these MMAs have read it
+          // frees the smem stage (in both CTAs of a pair) once these MMAs have read it
+          if (CTA2) ptx::umma_commit_pair(&empty_bar[stage]); else ptx::umma_commit(&empty_bar[stage]);
           if (++stage == kStages) { stage = 0; phase ^= 1u; }
         }
-        if (ok) ptx::umma_commit(&tmem_full[buf]);  // accumulator complete
+        if (ok) {  // accumulators complete
+          if (CTA2) ptx::umma_commit_pair(&tmem_full[buf]); else ptx::umma_commit(&tmem_full[buf]);
+        }
       }
     }
   } else {
     // ---------------------------------------------------------------- epilogue
-    const int q = warp & 3;  // TMEM lane quarter this warp may read
+    const int q = warp & 3;            // TMEM lane quarter this warp may read
+    const int hsel = (warp - 2) >> 2;  // 0 or 1: which of the two warps of this quarter
+    const int slot = (int)cta_rank * 8 + hsel * 4 + q;  // split-K arrival slot of this warp
+    const int U = num_units<EPI>(g);
+    const int a0 = (MI == 2) ? hsel : 0;                   // accumulator this warp drains
+    const int row_in_tile = (CTA2 ? a0 * 256 + (int)cta_rank * 128 : a0 * 128) + q * 32 + lane;
+    const int u_first = (MI == 2) ? 0 : hsel, u_step = (MI == 2) ? 1 : 2;
+    const uint32_t empty_remote = CTA2 ? ptx::map_to_cta(ptx::smem_u32(&tmem_empty[0]), 0) : 0u;
     int local = 0;
     bool ok = true;
-    for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++local) {
+    for (; ok; ++local) {
+      const Segment sg = segment_of(sc, unit_id, local);
+      if (!sg.valid) break;
+      const int tile = sg.tile, S = sg.parts;
       const int mt = tile % g.m_tiles, nt = tile / g.m_tiles;
-      const int buf = local & 1;
-      const uint32_t use = (uint32_t)(local >> 1);
+      const int buf = dbuf ? (local & 1) : 0;
+      const uint32_t use = (uint32_t)(dbuf ? (local >> 1) : local);
       ok = __all_sync(0xffffffffu, ptx::mbar_wait(&tmem_full[buf], use & 1u, abort_flag) ? 1 : 0) != 0;
       if (!ok) break;  // warp-uniform: no lane is left behind in an aligned tcgen05.ld
       ptx::tc_fence_after();
-      const uint32_t t_row = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(buf * BN);
-      const int gm = mt * kBM + q * 32 + lane;  // global row of this thread
-      const bool row_ok = gm < g.M;
-      T* out = reinterpret_cast<T*>(g.out);
 
-      if constexpr (EPI == EPI_STORE) {
-        const bool vec_ok = ((g.ldo & 7) == 0) && aligned16(g.out);
-        const T* bias = reinterpret_cast<const T*>(g.bias);
-#pragma unroll 1
-        for (int c = 0; c < BN / 32; ++c) {
-          uint32_t r[32];
-          ptx::tmem_ld_32x32(t_row + c * 32, r);
-          const int gn = nt * BN + c * 32;
-          if (row_ok && gn < g.N) {
+      const int n0 = nt * (EPI == EPI_SILU_MUL ? BN / 2 : BN);
+      const RowCtx<T> rc = make_row_ctx<T, EPI>(g, comm, red, mt * BM + row_in_tile, n0);
+      const TmemSource tsrc{tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)((buf * MI + a0) * BN)};
+      if (S == 1) {
+        for (int u = u_first; u < U; u += u_step) finish_unit<T, EPI>(g, rc, tsrc, u);
+      } else {
+        // the tile is cut along K: leave this part in its workspace slot ...
+        float* ws_row = g.ws + (size_t)sg.part_slot * BM * BN + row_in_tile;  // column-major slot: (row, col) at col*BM + row
+        for (int u = u_first; u < U; u += u_step) {
+          int cols[2];
+          const int nch = unit_chunks<EPI>(g, n0, u, cols);
+          for (int c = 0; c < nch; ++c) {
             float f[32];
+            tsrc.load32(cols[c], f);
+            if (g.debug & 1) continue;
+            float* p = ws_row + (size_t)cols[c] * BM;
 #pragma unroll
-            for (int j = 0; j < 32; ++j) f[j] = __uint_as_float(r[j]);
-            if (bias) {
-#pragma unroll
-              for (int j = 0; j < 32; ++j)
-                if (gn + j < g.N) f[j] += DT<T>::to_f(bias[gn + j]);
-            }
-            store_row32<T>(out + (size_t)gm * g.ldo + gn, f, g.N - gn, vec_ok);
-          }
-        }
-      } else if constexpr (EPI == EPI_ROTARY) {
-        // Reference: F.linear output rounded to T (tensor_parallel/layers.py:278-284), then
-        // rotary_embedding in T arithmetic on the q and k heads (csrc/pos_encoding_kernels.cu:8-76).
-        // Requires BN % head_size == 0, rot_dim == head_size, (head_size/2) % 32 == 0 for NeoX.
-        const bool vec_ok = ((g.ldo & 7) == 0) && aligned16(g.out);
-        const T* cs = row_ok ? reinterpret_cast<const T*>(g.cos_sin) + g.positions[gm] * g.head_size : nullptr;
-        const int half = g.head_size / 2;
-        const int chunks_per_head = g.head_size / 32;
-#pragma unroll 1
-        for (int h0 = 0; h0 < BN; h0 += g.head_size) {
-          const int gh = nt * BN + h0;  // first global column of this head
-          const bool rotate = gh < g.rot_cols;
-          if (rotate && g.is_neox) {
-#pragma unroll 1
-            for (int c = 0; c < chunks_per_head / 2; ++c) {
-              uint32_t rx[32], ry[32];
-              ptx::tmem_ld_32x32(t_row + h0 + c * 32, rx);
-              ptx::tmem_ld_32x32(t_row + h0 + half + c * 32, ry);
-                  if (row_ok && gh < g.N) {
-                float co[32], si[32], fx[32], fy[32];
-                load_row32<T>(cs + c * 32, co);
-                load_row32<T>(cs + half + c * 32, si);
-#pragma unroll
-                for (int j = 0; j < 32; ++j) {
-                  const float x = rt<T>(__uint_as_float(rx[j])), y = rt<T>(__uint_as_float(ry[j]));
-                  fx[j] = rt<T>(rt<T>(x * co[j]) - rt<T>(y * si[j]));
-                  fy[j] = rt<T>(rt<T>(y * co[j]) + rt<T>(x * si[j]));
-                }
-                store_row32<T>(out + (size_t)gm * g.ldo + gh + c * 32, fx, g.N - (gh + c * 32), vec_ok);
-                store_row32<T>(out + (size_t)gm * g.ldo + gh + half + c * 32, fy, g.N - (gh + half + c * 32), vec_ok);
-              }
-            }
-          } else {
-#pragma unroll 1
-            for (int c = 0; c < chunks_per_head; ++c) {
-              uint32_t r[32];
-              ptx::tmem_ld_32x32(t_row + h0 + c * 32, r);
-                  const int gn = gh + c * 32;
-              if (row_ok && gn < g.N) {
-                float f[32];
-#pragma unroll
-                for (int j = 0; j < 32; ++j) f[j] = __uint_as_float(r[j]);
-                if (rotate) {  // GPT-J style: pairs (2i, 2i+1); cos/sin index = column_in_head / 2
-#pragma unroll
-                  for (int j = 0; j < 32; j += 2) {
-                    const int p = (c * 32 + j) >> 1;
-                    const float co = DT<T>::to_f(cs[p]), si = DT<T>::to_f(cs[half + p]);
-                    const float x = rt<T>(f[j]), y = rt<T>(f[j + 1]);
-                    f[j] = rt<T>(rt<T>(x * co) - rt<T>(y * si));
-                    f[j + 1] = rt<T>(rt<T>(y * co) + rt<T>(x * si));
-                  }
-                }
-                store_row32<T>(out + (size_t)gm * g.ldo + gn, f, g.N - gn, vec_ok);
-              }
-            }
-          }
-        }
-      } else if constexpr (EPI == EPI_SILU_MUL) {
-        // Reference: gate_up = F.linear(x) rounded to T, then silu_and_mul
-        // (csrc/activation_kernels.cu:8-25): out = (T)(silu(gate)) * up.
-        const int d = g.N / 2;
-        const bool vec_ok = ((g.ldo & 7) == 0) && aligned16(g.out);
-#pragma unroll 1
-        for (int c = 0; c < BN / 64; ++c) {
-          uint32_t rg[32], ru[32];
-          ptx::tmem_ld_32x32(t_row + c * 32, rg);
-          ptx::tmem_ld_32x32(t_row + BN / 2 + c * 32, ru);
-          const int gn = nt * (BN / 2) + c * 32;
-          if (row_ok && gn < d) {
-            float f[32];
-#pragma unroll
-            for (int j = 0; j < 32; ++j) {
-              const float gte = rt<T>(__uint_as_float(rg[j])), up = rt<T>(__uint_as_float(ru[j]));
-              const float sl = rt<T>(gte / (1.0f + expf(-gte)));
-              f[j] = rt<T>(sl * up);
-            }
-            store_row32<T>(out + (size_t)gm * g.ldo + gn, f, d - gn, vec_ok);
-          }
-        }
-      } else {  // EPI_PUSH
-        // Partial rows go to the owner's slot [set][src = my rank][local row][H].
-        const int owner = row_ok ? gm / red.rows_per_rank : 0;
-        const int lr = gm - owner * red.rows_per_rank;
-        T* dst_row = row_ok ? reinterpret_cast<T*>(comm.heap[owner] + comm.partial_off[red.set]) +
-                                  ((size_t)comm.rank * red.rows_per_rank + lr) * (size_t)g.N
-                            : nullptr;
-#pragma unroll 1
-        for (int c = 0; c < BN / 32; ++c) {
-          uint32_t r[32];
-          ptx::tmem_ld_32x32(t_row + c * 32, r);
-          const int gn = nt * BN + c * 32;
-          if (row_ok && gn < g.N) {
-            float f[32];
-#pragma unroll
-            for (int j = 0; j < 32; ++j) f[j] = __uint_as_float(r[j]);
-            store_row32<T>(dst_row + gn, f, g.N - gn, (g.N & 7) == 0);
+            for (int j = 0; j < 32; ++j) __stcg(p + (size_t)j * BM, f[j]);
           }
         }
       }
 
-      // TMEM buffer drained: hand it back to the MMA warp.
+      // TMEM drained: hand the buffer back to the MMA warp (of the leader CTA).
       ptx::tc_fence_before();
       __syncwarp();
-      if (lane == 0) ptx::mbar_arrive(&tmem_empty[buf]);
+      if (lane == 0) {
+        if (CTA2) ptx::mbar_arrive_cluster(empty_remote + (uint32_t)(buf * 8));
+        else ptx::mbar_arrive(&tmem_empty[buf]);
+      }
+
+      bool finished_here = (S == 1);  // did this warp produce final (stored / pushed) values for its rows?
+      if (S > 1) {
+        // ... and, once every part of the tile has left its share for these 32 rows, finish 1/S of
+        // the units: all S parts work on the fix-up at once instead of one of them doing it alone.
+        // (The parts of a tile are the LAST work item of S different, co-resident units, so the
+        // wait below cannot depend on anything that has not been scheduled; it is bounded anyway.)
+        if (!(g.debug & 4)) __threadfence();
+        __syncwarp();
+        uint32_t* ctr_arrive = g.ws_counters + (size_t)sg.rem_index * 32 + slot;
+        uint32_t* ctr_done = ctr_arrive + 16;
+        int arrived = 1;
+        if (lane == 0) {
+          atomicAdd(ctr_arrive, 1u);
+          const long long t0 = clock64();
+          while (ld_acquire_gpu(ctr_arrive) < (uint32_t)S) {
+            __nanosleep(32);
+            if (*abort_flag || clock64() - t0 > ptx::kWaitLimitCycles) { arrived = 0; *abort_flag = 1; break; }
+          }
+        }
+        arrived = __shfl_sync(0xffffffffu, arrived, 0);
+        if (!arrived) { ok = false; break; }
+        if (!(g.debug & 2)) {
+          const int my_part = sg.part_slot - sg.first_slot;
+          const WorkspaceSource wsrc{g.ws + (size_t)sg.first_slot * BM * BN + row_in_tile, (size_t)BM * BN, BM, S};
+          int k = 0;
+          for (int u = u_first; u < U; u += u_step, ++k)
+            if (k % S == my_part) finish_unit<T, EPI>(g, rc, wsrc, u);
+        }
+        finished_here = true;
+        __syncwarp();
+        if (lane == 0 && atomicAdd(ctr_done, 1u) == (uint32_t)(S - 1)) {  // last reader: ready for the next launch
+          *ctr_arrive = 0;
+          *ctr_done = 0;
+        }
+      }
 
       if constexpr (EPI == EPI_PUSH) {
-        // Publish this warp's 32 rows to their owner(s): stores of all lanes first, then one
-        // release-increment per owner.  The host's push target counts (32-row group, owner) pairs.
-        __threadfence_system();
-        __syncwarp();
-        if (lane == 0) {
-          const int r_lo = mt * kBM + q * 32, r_hi = min(g.M, r_lo + 32) - 1;
-          if (r_hi >= r_lo)
-            for (int o = r_lo / red.rows_per_rank; o <= r_hi / red.rows_per_rank; ++o)
-              red_release_sys_add(comm_counter(comm, o, CC_PUSH0 + red.set), 1u);
+        // Publish this warp's rows to their owner(s): the stores of all lanes first, then one
+        // release-increment per owner.  Exactly one epilogue warp per (tile, slot) gets here with
+        // finished_here set for a whole tile and S of them (one per part) for a tile cut along K, so
+        // the host can count the increments per (tile, slot, owner of the slot's rows).
+        if (finished_here) {
+          __threadfence_system();
+          __syncwarp();
+          if (lane == 0) {
+            const int r_lo = mt * BM + row_in_tile - lane, r_hi = min(g.M, r_lo + 32) - 1;
+            if (r_hi >= r_lo)
+              for (int o = r_lo / red.rows_per_rank; o <= r_hi / red.rows_per_rank; ++o)
+                red_release_sys_add(comm_counter(comm, o, CC_PUSH0 + red.set), 1u);
+          }
         }
       }
     }
@@ -363,9 +631,10 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
   // -------------------------------------------------------------- common exit
   ptx::tc_fence_before();
   __syncthreads();
+  if (CTA2) ptx::cluster_sync_all();  // the peer no longer signals our barriers / writes our TMEM
   if (warp == 1) {
     ptx::tc_fence_after();
-    ptx::tmem_dealloc(tmem_base, kTmemCols);
+    if (CTA2) ptx::tmem_dealloc_pair(tmem_base, kTmemCols); else ptx::tmem_dealloc(tmem_base, kTmemCols);
   }
   if (*abort_flag) {
     if (threadIdx.x == 0) {
@@ -382,6 +651,7 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
       if (finish_phase(comm, red) && (red.out_copy || red.resid_copy))
         copy_out_phase<T>(comm, red, blockIdx.x * kGemmThreads + threadIdx.x, gridDim.x * kGemmThreads);
     }
+    advance_targets(comm, red);
   }
 }
 

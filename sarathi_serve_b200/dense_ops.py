@@ -14,6 +14,19 @@ from . import _native as N
 EPI_NONE, EPI_ROTARY, EPI_SILU_MUL = 0, 1, 2
 
 _status_words: dict = {}
+_workspaces: dict = {}
+
+# Split-K workspace per device: 64 KiB of arrival counters (kept zero by the kernels) + fp32 partial tiles.
+WORKSPACE_BYTES = (64 << 10) + (96 << 20)
+
+
+def workspace(device: torch.device) -> torch.Tensor:
+    key = (device.type, device.index if device.index is not None else torch.cuda.current_device())
+    w = _workspaces.get(key)
+    if w is None:
+        w = torch.zeros(WORKSPACE_BYTES, dtype=torch.uint8, device=device)
+        _workspaces[key] = w
+    return w
 
 
 def status_word(device: torch.device) -> torch.Tensor:
@@ -34,6 +47,14 @@ def check_status(device: torch.device) -> None:
     if v != 0:
         w.zero_()
         raise RuntimeError(f"sm_100a GEMM pipeline wait timed out (device status code {v})")
+
+
+def _ws(x: torch.Tensor):
+    """(pointer, bytes) of the split-K workspace for x's device; fp32 runs the FFMA kernel and needs none."""
+    if x.dtype == torch.float32:
+        return None, 0
+    w = workspace(x.device)
+    return N.ptr(w), w.numel()
 
 
 def _rows_2d(x: torch.Tensor, what: str) -> torch.Tensor:
@@ -65,7 +86,7 @@ def linear(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor] =
         bias = bias.contiguous()
     N.check(N.lib().sb200_gemm_colpar(N.ptr(out), out.stride(0), N.ptr(x2), x2.stride(0), N.ptr(weight),
                                       weight.stride(0), N.ptr(bias), T, Nn, K, N.dtype_id(x2), EPI_NONE, None,
-                                      N.ptr(status_word(x2.device)), tile_n, N.stream_ptr()), "gemm_colpar")
+                                      N.ptr(status_word(x2.device)), tile_n, *_ws(x2), N.stream_ptr()), "gemm_colpar")
     return out.view(*lead, Nn) if len(lead) != 1 else out
 
 
@@ -93,7 +114,8 @@ def linear_rotary(x: torch.Tensor, weight: torch.Tensor, positions: torch.Tensor
                        1 if is_neox else 0)
     N.check(N.lib().sb200_gemm_colpar(N.ptr(out), out.stride(0), N.ptr(x2), x2.stride(0), N.ptr(weight),
                                       weight.stride(0), None, T, Nn, K, N.dtype_id(x2), EPI_ROTARY,
-                                      ctypes.byref(rot), N.ptr(status_word(x2.device)), tile_n, N.stream_ptr()),
+                                      ctypes.byref(rot), N.ptr(status_word(x2.device)), tile_n, *_ws(x2),
+                                      N.stream_ptr()),
             "gemm_colpar[rotary]")
     return out
 
@@ -110,6 +132,16 @@ def linear_silu_mul(x: torch.Tensor, weight: torch.Tensor, out: Optional[torch.T
         out = torch.empty(T, Nn // 2, dtype=x2.dtype, device=x2.device)
     N.check(N.lib().sb200_gemm_colpar(N.ptr(out), out.stride(0), N.ptr(x2), x2.stride(0), N.ptr(weight),
                                       weight.stride(0), None, T, Nn, K, N.dtype_id(x2), EPI_SILU_MUL, None,
-                                      N.ptr(status_word(x2.device)), tile_n, N.stream_ptr()),
+                                      N.ptr(status_word(x2.device)), tile_n, *_ws(x2), N.stream_ptr()),
             "gemm_colpar[silu_mul]")
     return out
+
+
+def gemm_plan(epilogue: int, T: int, Nn: int, K: int, head_size: int = 128, tile_cfg: int = 0,
+              workspace_bytes: int = WORKSPACE_BYTES) -> dict:
+    """The tile shape / schedule the library would use for a [T, K] x [Nn, K]^T projection."""
+    out = (ctypes.c_int * 11)()
+    N.check(N.lib().sb200_gemm_plan(epilogue, T, Nn, K, head_size, tile_cfg, workspace_bytes, out), "gemm_plan")
+    keys = ("cta_pairs", "accumulators", "bn", "units", "tiles_full", "k_parts", "kb_per_part", "stages", "m_tiles",
+            "n_tiles", "k_blocks")
+    return dict(zip(keys, out))

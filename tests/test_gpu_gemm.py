@@ -22,14 +22,21 @@ def _check_status():
     dense_ops.check_status(torch.device("cuda", torch.cuda.current_device()))
 
 
+# tile configuration = BN + 1000*MI + 100000*splitK (0 = chosen by the library)
+TILE_CFGS = [0, 64, 96, 128, 160, 224, 256, 2064, 2128, 2256, 301128, 402256, 1602128, 200032,
+             3064, 3128, 3192, 3256, 203256, 503128, 4064, 4128, 4256, 304256]  # 3xxx/4xxx = CTA pairs (cta_group::2)
+
+
 @pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16, torch.float32])
-@pytest.mark.parametrize("tile_n", [0, 64, 128, 256])
+@pytest.mark.parametrize("tile_n", TILE_CFGS)
 @pytest.mark.parametrize("T,N,K", [(128, 128, 64), (128, 256, 128), (512, 768, 4096), (288, 768, 1024), (1, 256, 512),
                                    (65, 200, 264), (300, 1000, 1000), (512, 6144, 512), (1024, 8, 4096)])
 def test_linear(dtype, tile_n, T, N, K):
     from sarathi_serve_b200 import dense_ops
     if dtype == torch.float32 and tile_n not in (0,):
-        pytest.skip("tile width applies to the tensor-core path only")
+        pytest.skip("tile shape applies to the tensor-core path only")
+    if tile_n // 100000 > (K + 63) // 64:
+        pytest.skip("more splits than k-blocks")
     x, w = _rand((T, K), dtype, T + N + K), _rand((N, K), dtype, 7 * N + K, 0.05)
     b = _rand((N,), dtype, 3)
     ref = x.float().cuda() @ w.float().cuda().t()
@@ -65,16 +72,20 @@ def test_linear_rejects_misaligned_stride():
 
 @pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
 @pytest.mark.parametrize("neox", [True, False])
+@pytest.mark.parametrize("tile_n", [0, 256, 2256, 401256, 302256, 3256, 303256, 4256, 204128])
 @pytest.mark.parametrize("T,nq,nkv,hd,K", [(512, 4, 1, 128, 4096), (288, 8, 2, 64, 1024), (65, 2, 2, 128, 512),
                                            (7, 1, 1, 256, 256)])
-def test_linear_rotary(dtype, neox, T, nq, nkv, hd, K):
+def test_linear_rotary(dtype, neox, tile_n, T, nq, nkv, hd, K):
     from sarathi_serve_b200 import dense_ops
     N = (nq + 2 * nkv) * hd
     x, w = _rand((T, K), dtype, T + K), _rand((N, K), dtype, N, 0.03)
     g = torch.Generator().manual_seed(5)
     pos = torch.randint(0, 2048, (T,), generator=g, dtype=torch.int64)
     cache = O.cos_sin_cache(hd, hd, 2048, 10000.0, dtype)
-    out = dense_ops.linear_rotary(x.cuda(), w.cuda(), pos.cuda(), cache.cuda(), hd, (nq + nkv) * hd, neox)
+    if tile_n // 100000 > (K + 63) // 64 or (tile_n and (tile_n % 1000) % hd):
+        pytest.skip("tile configuration does not fit this case")
+    out = dense_ops.linear_rotary(x.cuda(), w.cuda(), pos.cuda(), cache.cuda(), hd, (nq + nkv) * hd, neox,
+                                  tile_n=tile_n)
     _check_status()
     # oracle: GEMM rounded to the dtype (GPU fp32 matmul of the same operands), then the rotary restatement
     ref = (x.float().cuda() @ w.float().cuda().t()).to(dtype).cpu()
@@ -86,10 +97,12 @@ def test_linear_rotary(dtype, neox, T, nq, nkv, hd, K):
 
 
 @pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
-@pytest.mark.parametrize("tile_n", [0, 64, 128, 256])
+@pytest.mark.parametrize("tile_n", [0, 64, 128, 192, 256, 2128, 2256, 501256, 402128, 3064, 3128, 3256, 403256, 4128, 4256, 304256])
 @pytest.mark.parametrize("T,d,K", [(512, 1792, 4096), (288, 1408, 1024), (65, 96, 512), (1, 64, 64)])
 def test_linear_silu_mul(dtype, tile_n, T, d, K):
     from sarathi_serve_b200 import dense_ops
+    if tile_n // 100000 > (K + 63) // 64:
+        pytest.skip("more splits than k-blocks")
     x, w = _rand((T, K), dtype, T + K), _rand((2 * d, K), dtype, d, 0.05)
     out = dense_ops.linear_silu_mul(x.cuda(), w.cuda(), tile_n=tile_n)
     _check_status()
