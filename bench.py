@@ -235,17 +235,30 @@ def run_native(a):
         return float(tt.item())
 
     with torch.inference_mode():
-        # ---- device-resident value
+        # ---- tile configurations for this shape (timed candidates; every rank adopts rank 0's choice)
+        layers[0].tune(T)
+        barrier()
+        # ---- device-resident value: K steps captured once in a CUDA graph, replayed for the timed region
         for i in range(a.warmup):
             step_resident(i)
+        barrier()
+        comm.check_status()
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.stream(side):
+            with torch.cuda.graph(graph, stream=side):
+                for i in range(a.steps):
+                    step_resident(i)
+        torch.cuda.current_stream().wait_stream(side)
+        graph.replay()  # untimed: first replay of a fresh graph
         barrier()
         sampler = ClockSampler(local)
         if rank == 0:
             sampler.start()
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         e0.record()
-        for i in range(a.steps):
-            step_resident(i)
+        graph.replay()
         e1.record()
         barrier()
         ms_resident = max_over_ranks(e0.elapsed_time(e1) / a.steps)
@@ -312,7 +325,8 @@ def run_native(a):
                 "clocks": clocks,
                 "e2e": {"value": T / (ms_e2e * 1e-3), "unit": UNIT, "ms_per_step": ms_e2e,
                         "h2d_bytes_per_step": T * H * es + T * 8, "d2h_bytes_per_step": T * H * es},
-                "gpu_launches": 4 * a.steps,
+                "gpu_launches": 4 * a.steps, "launch_mode": "one CUDA graph of all timed steps",
+                "tile_cfgs": {k[0] + f"[{k[2]}x{k[3]}]": v for k, v in dense_ops._tuned.items()},
                 "roofline": {"bound": "tensor", "kernel": "gemm_sm100_kernel<bf16, EPI_SILU_MUL> (gate_up + SiLU*mul)",
                              "achieved": achieved, "peak": peak_tf, "unit": "TFLOP/s", "frac": achieved / peak_tf,
                              "peak_source": f"{peak_src} (burst bf16)", "ms_per_launch": ms_kernel, "traffic": None}}

@@ -256,6 +256,36 @@ int sb200_gemm_rowpar(sb200_comm* comm, const void* x, int64_t ldx, const void* 
                       const void* norm_w, float eps, int write_resid_all, void* out_copy, void* resid_copy,
                       int tile_cfg, sb200_stream_t stream, void** out_ptr, void** resid_ptr);
 
+/* ---------------------------------------------------- mixture-of-experts GEMMs */
+
+/* The expert GEMMs of a tensor-parallel MoE layer on the tcgen05 kernel.  They work on the
+ * expert-sorted, block-padded slot order produced by sb200_moe_align_block_size with
+ * block_size = sb200_moe_block_rows() (one tile row block = one expert).  rows_cap = capacity of
+ * the sorted order (a multiple of the block); *num_post_pad (device) = rows in use.
+ * Replace: fused_experts / invoke_fused_moe_kernel / the Triton fused_moe_kernel,
+ * sarathi/model_executor/layers/fused_moe/fused_moe.py:15-148,207-259,411-544. */
+int sb200_moe_block_rows(void);
+/* xs[r, :] = x[sorted_ids[r] / top_k, :] for r < *num_post_pad (zeros for padding slots). */
+int sb200_moe_gather_rows(void* xs, const void* x, const int32_t* sorted_ids, const int32_t* num_post_pad,
+                          int64_t rows_cap, int64_t T, int64_t H, int top_k, int dtype, sb200_stream_t stream);
+/* act[r, 0:d] = silu(xs[r] . w13[e][0:d]^T) * (xs[r] . w13[e][d:2d]^T), e = expert_ids[r / block];
+ * w13: [E, 2d, K] (fused_moe/layer.py:80-90). */
+int sb200_moe_gemm1(void* act, const void* xs, const void* w13, const int32_t* expert_ids,
+                    const int32_t* num_post_pad, int64_t rows_cap, int E, int64_t two_d, int64_t K, int dtype,
+                    uint32_t* status, int tile_cfg, sb200_stream_t stream);
+/* out3[sorted_ids[r], :] = (act[r] . w2[e]^T) * topk_weights[sorted_ids[r]]; w2: [E, H, d];
+ * out3: [num_slots = T * top_k, H]; padding rows write nothing. */
+int sb200_moe_gemm2(void* out3, const void* act, const void* w2, const int32_t* expert_ids,
+                    const int32_t* num_post_pad, const int32_t* sorted_ids, const float* topk_weights,
+                    int64_t rows_cap, int64_t num_slots, int E, int64_t H, int64_t d, int dtype,
+                    uint32_t* status, int tile_cfg, sb200_stream_t stream);
+/* out[t, :] = sum_j in3[t * top_k + j, :] (fp32 sum rounded once; fused_moe.py:539-543). */
+int sb200_moe_sum(void* out, const void* in3, int64_t T, int top_k, int64_t H, int dtype, sb200_stream_t stream);
+/* The same sum fused into the push phase of the all-reduce over the tensor-parallel ranks
+ * (fused_moe/layer.py:128-132); results as sb200_all_reduce without bias / residual / norm. */
+int sb200_moe_sum_all_reduce(sb200_comm* comm, const void* in3, int64_t T, int top_k, int64_t H, int dtype,
+                             void* out_copy, sb200_stream_t stream, void** out_ptr);
+
 #ifdef __cplusplus
 }
 #endif

@@ -301,6 +301,17 @@ def decoder_layer_distributed(p: Dict[str, torch.Tensor], x: torch.Tensor, posit
     return hidden + d
 
 
+def moe_layer(x: torch.Tensor, gate_w: torch.Tensor, w13: Sequence[torch.Tensor], w2: Sequence[torch.Tensor],
+              top_k: int, renormalize: bool = True) -> torch.Tensor:
+    """models/mixtral.py:102-108 + layers/fused_moe/layer.py:122-134 over len(w13) simulated ranks:
+    router logits from the replicated gate (F.linear), fused_topk, each rank's fused_experts on its
+    shard of every expert (w13[r]: [E, 2I/tp, H], w2[r]: [E, H, I/tp]), then the SUM all-reduce."""
+    logits = linear(x, gate_w)
+    wts, ids, _ = topk_softmax(logits, top_k, renormalize)
+    parts = [fused_experts(x, w13[r], w2[r], wts, ids.long()) for r in range(len(w13))]
+    return sum_over_ranks(parts)
+
+
 def rel_err(a: torch.Tensor, ref: torch.Tensor) -> float:
     """The parity measure used everywhere: max|a - ref| / max|ref| (element-wise relative
     error is meaningless near zero)."""

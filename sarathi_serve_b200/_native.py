@@ -40,6 +40,12 @@ _PP = ctypes.POINTER(c_void_p)
 _GEMM_SIGS: dict = {
     "sb200_gemm_colpar": (_I, [_P, _L, _P, _L, _P, _L, _P, _L, _L, _L, _I, _I, ctypes.POINTER(RotaryArgs), _P, _I, _P,
                                _L, _P]),
+    "sb200_moe_block_rows": (_I, []),
+    "sb200_moe_gather_rows": (_I, [_P, _P, _P, _P, _L, _L, _L, _I, _I, _P]),
+    "sb200_moe_gemm1": (_I, [_P, _P, _P, _P, _P, _L, _I, _L, _L, _I, _P, _I, _P]),
+    "sb200_moe_gemm2": (_I, [_P, _P, _P, _P, _P, _P, _P, _L, _L, _I, _L, _L, _I, _P, _I, _P]),
+    "sb200_moe_sum": (_I, [_P, _P, _L, _I, _L, _I, _P]),
+    "sb200_moe_sum_all_reduce": (_I, [_P, _P, _L, _I, _L, _I, _P, _P, _PP]),
     "sb200_gemm_plan": (_I, [_I, _L, _L, _L, _I, _I, _L, ctypes.POINTER(c_int)]),
     "sb200_comm_heap_bytes": (_L, [_L]),
     "sb200_comm_create": (_I, [_PP, _I, _I, _L]),

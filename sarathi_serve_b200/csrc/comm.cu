@@ -50,7 +50,10 @@ static size_t scratch_off(const sb200_comm* c) { return kCounterBytes + 6 * c->r
 // Standalone all-reduce: push rows of a local tensor, then the shared phases.
 template <typename T>
 __global__ void __launch_bounds__(256)
-all_reduce_kernel(const CommView c, const ReduceArgs a, const T* __restrict__ in) {
+all_reduce_kernel(const CommView c, const ReduceArgs a, const T* __restrict__ in, const int rows_per_token) {
+  // `in` is [T, rows_per_token, H]: the rows of a token are summed (fp32, rounded to T) while they are
+  // pushed -- rows_per_token = 1 for a plain all-reduce, top_k for the per-slot expert outputs of the
+  // MoE layer (the reference's torch.sum(dim=1) before its all-reduce, fused_moe.py:539-543).
   constexpr int N = Vec16<T>::N;
   const int nvec = a.H / N;
   const size_t total = (size_t)a.T * nvec;
@@ -59,13 +62,27 @@ all_reduce_kernel(const CommView c, const ReduceArgs a, const T* __restrict__ in
     const int t = (int)(i / nvec), v = (int)(i - (size_t)t * nvec);
     const int owner = t / a.rows_per_rank, lr = t - owner * a.rows_per_rank;
     T* dst = (T*)(c.heap[owner] + c.partial_off[a.set]) + ((size_t)c.rank * a.rows_per_rank + lr) * a.H + (size_t)v * N;
-    st16(dst, ld16(in + i * N));
+    if (rows_per_token == 1) {
+      st16(dst, ld16(in + i * N));
+    } else {
+      float acc[N];
+#pragma unroll
+      for (int j = 0; j < N; ++j) acc[j] = 0.f;
+      for (int s = 0; s < rows_per_token; ++s) {
+        const Vec16<T> x = ld16(in + ((size_t)t * rows_per_token + s) * a.H + (size_t)v * N);
+#pragma unroll
+        for (int j = 0; j < N; ++j) acc[j] += DT<T>::to_f(x.v[j]);
+      }
+      Vec16<T> o;
+#pragma unroll
+      for (int j = 0; j < N; ++j) o.v[j] = DT<T>::from_f(acc[j]);
+      st16(dst, o);
+    }
   }
-  __threadfence_system();
+  fence_scope(c.world > 1);
   __syncthreads();
-  if (threadIdx.x < c.world) red_release_sys_add(comm_counter(c, threadIdx.x, CC_PUSH0 + a.set), 1u);
-  const int warps = blockDim.x / 32;
-  reduce_phase<T>(c, a, blockIdx.x * warps + (threadIdx.x >> 5), gridDim.x * warps);
+  if (threadIdx.x < c.world) red_add_relaxed(comm_counter(c, threadIdx.x, CC_PUSH0 + a.set), 1u, c.world > 1);
+  reduce_phase<T>(c, a, blockIdx.x, gridDim.x);
   if (a.out_copy || a.resid_copy || blockIdx.x == 0) {
     if (finish_phase(c, a) && (a.out_copy || a.resid_copy))
       copy_out_phase<T>(c, a, blockIdx.x * blockDim.x + threadIdx.x, gridDim.x * blockDim.x);
@@ -129,22 +146,22 @@ static void commit_call(sb200_comm* c, CallPlan* p, uint32_t pushes_to_me, void*
 }
 
 template <typename T>
-static int launch_all_reduce(const CallPlan& p, const void* in, int grid, cudaStream_t s) {
-  all_reduce_kernel<T><<<grid, 256, 0, s>>>(p.cv, p.ra, (const T*)in);
+static int launch_all_reduce(const CallPlan& p, const void* in, int rows_per_token, int grid, cudaStream_t s) {
+  all_reduce_kernel<T><<<grid, 256, 0, s>>>(p.cv, p.ra, (const T*)in, rows_per_token);
   SB_CHECK_LAUNCH("all_reduce_kernel");
   return SB200_OK;
 }
 
 static int do_all_reduce(sb200_comm* c, const void* in, int64_t T_, int64_t H, int dtype, const void* bias,
                          const void* residual, const void* norm_w, float eps, int write_resid_all, void* out_copy,
-                         void* resid_copy, cudaStream_t s, void** out_ptr, void** resid_ptr) {
+                         void* resid_copy, cudaStream_t s, void** out_ptr, void** resid_ptr, int rows_per_token = 1) {
   CallPlan p;
   int rc = plan_call(c, T_, H, dtype, bias, residual, norm_w, eps, write_resid_all, out_copy, resid_copy, &p);
   if (rc) return rc;
   SB_CHECK_ARG(in && aligned16(in), "all_reduce: input must be a 16-byte aligned device pointer");
   const int grid = all_reduce_grid(T_, H, dtype, p.ra.rows_per_rank);
   commit_call(c, &p, (uint32_t)(c->world * grid), out_ptr, resid_ptr);
-  SB_DISPATCH_FLOAT(dtype, return (launch_all_reduce<scalar_t>(p, in, grid, s)));
+  SB_DISPATCH_FLOAT(dtype, return (launch_all_reduce<scalar_t>(p, in, rows_per_token, grid, s)));
   return SB200_OK;
 }
 
@@ -275,6 +292,13 @@ extern "C" int sb200_all_reduce(sb200_comm* comm, const void* in, int64_t T, int
                                 void** resid_ptr) {
   return do_all_reduce(comm, in, T, H, dtype, bias, residual, norm_w, eps, write_resid_all, out_copy, resid_copy,
                        (cudaStream_t)stream, out_ptr, resid_ptr);
+}
+
+extern "C" int sb200_moe_sum_all_reduce(sb200_comm* comm, const void* in3, int64_t T, int top_k, int64_t H, int dtype,
+                                        void* out_copy, sb200_stream_t stream, void** out_ptr) {
+  SB_CHECK_ARG(top_k >= 1, "moe_sum_all_reduce: top_k must be positive");
+  return do_all_reduce(comm, in3, T, H, dtype, nullptr, nullptr, nullptr, 0.f, 0, out_copy, nullptr,
+                       (cudaStream_t)stream, out_ptr, nullptr, top_k);
 }
 
 extern "C" int sb200_gemm_rowpar(sb200_comm* comm, const void* x, int64_t ldx, const void* w, int64_t ldw, int64_t T,

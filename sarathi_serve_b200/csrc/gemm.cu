@@ -101,14 +101,22 @@ GemmPlan plan_gemm(int epi, int64_t M, int64_t N, int64_t K, int head_size, int 
       if (!f_mode && bm > 128 && M <= bm / 2) continue;  // half of the tile would be empty
       const int units_max = cta2 ? sms / 2 : sms;     // CTAs or CTA pairs that run at once
       const int64_t total = tiles * k_blocks;
-      // per-k-block clocks of one SM
+      // per-k-block clocks of one SM (constants fitted to measurements on B200):
+      //   a tcgen05.mma of K=16 occupies the tensor pipe for at least ~137 clocks whatever its
+      //   shape, so a k-block (4 MMAs per accumulator) costs >= 548*MI clocks; its nominal time
+      //   is M*N*16*2 / 8192 flop/clk; the stage also has to cross L2 -> shared memory
+      //   (~50 B/clk/SM with every SM pulling) and shared memory itself (fill + operand reads).
       const double stage = gemm_stage_bytes(mi, bn, cta2);
-      const double mma = 2.0 * mi * bn;                                        // tensor pipe
+      const double mma_nominal = 2.0 * mi * bn * 1.08;
+      const double mma_floor = 548.0 * mi;
       const double b_rows = cta2 ? bn / 2.0 : bn;
-      const double smem_rd = mi * (128 + b_rows) * kBK * 2;                    // operands the MMAs read
-      double per_kb = mma;
-      if ((stage + smem_rd) / 128.0 > per_kb) per_kb = (stage + smem_rd) / 128.0;
-      if (stage / 44.0 > per_kb) per_kb = stage / 44.0;  // L2 -> SM at ~44 B/clk/SM when every SM pulls
+      const double smem_rd = mi * (128 + b_rows) * kBK * 2;
+      double per_kb = mma_nominal > mma_floor ? mma_nominal : mma_floor;
+      if ((stage + smem_rd) / 100.0 > per_kb) per_kb = (stage + smem_rd) / 100.0;
+      if (stage / 50.0 > per_kb) per_kb = stage / 50.0;
+      const int64_t busy_sms = (tiles < units_max ? tiles : units_max) * (cta2 ? 2 : 1);
+      if (busy_sms > sms / 2) per_kb *= 1.0 + 0.25 * (double)(busy_sms - sms / 2) / (sms / 2);  // L2 contention
+      if (mi == 2) per_kb *= 1.4;  // single-buffered accumulators, shallow ring: measured well above the model
       const double epi_units = (mi == 2 ? bn / 32.0 : bn / 64.0);
       const double epi_c = epi_units * 450.0 + 400.0;
       const bool dbuf = mi * bn * 2 <= 512;
@@ -119,7 +127,7 @@ GemmPlan plan_gemm(int epi, int64_t M, int64_t N, int64_t K, int head_size, int 
         if (f_s && sp != f_s) continue;
         int64_t units = G;
         int kbp = k_blocks;
-        double cost = 2500.0 + (dbuf ? epi_c : 0.0);
+        double cost = 9000.0 + (dbuf ? epi_c : 0.0);
         if (tiles >= units_max || sp == 1) cost += (tiles_full / G) * full_item;
         if (sp == 1) {
           if (rem) cost += full_item;
@@ -136,7 +144,7 @@ GemmPlan plan_gemm(int epi, int64_t M, int64_t N, int64_t K, int head_size, int 
           kbp = (k_blocks + sp - 1) / sp;
           if ((int64_t)(sp - 1) * kbp >= k_blocks) continue;  // an empty part
           const int64_t rounds = (cut_tiles * sp + units - 1) / units;
-          const double fix = epi_units * (300.0 + 130.0 * sp) + 2500.0;  // dump + summed re-read
+          const double fix = epi_units * 700.0 + 4500.0;  // dump, wait for the other parts, summed re-read of 1/S of the tile
           cost += rounds * (kbp * per_kb + (dbuf ? 300.0 : epi_c)) + fix;
         }
         if (cost < best_cost) {
@@ -237,13 +245,15 @@ static int dispatch_epi(int epi, const CUtensorMap& ta, const CUtensorMap& tb, c
     case EPI_ROTARY: return launch_mode<T, EPI_ROTARY>(ta, tb, g, cv, ra, s);
     case EPI_SILU_MUL: return launch_mode<T, EPI_SILU_MUL>(ta, tb, g, cv, ra, s);
     case EPI_PUSH: return launch_mode<T, EPI_PUSH>(ta, tb, g, cv, ra, s);
+    case EPI_MOE_SCATTER: return launch_mode<T, EPI_MOE_SCATTER>(ta, tb, g, cv, ra, s);
   }
   set_error("unknown GEMM epilogue %d", epi);
   return SB200_ERR_INVALID_ARGUMENT;
 }
 
 int run_gemm_sm100(int dtype, int epi, const GemmPlan& plan, const void* x, int64_t ldx, const void* w, int64_t ldw,
-                   GemmArgs g, void* workspace, const CommView& cv, const ReduceArgs& ra, cudaStream_t s) {
+                   GemmArgs g, void* workspace, const CommView& cv, const ReduceArgs& ra, cudaStream_t s,
+                   int64_t b_rows) {
   SB_CHECK_ARG(plan.bn != 0, "no GEMM tile shape fits epilogue %d (head_size=%d)", epi, g.head_size);
   g.cta2 = plan.cta2;
   g.mi = plan.mi; g.bn = plan.bn; g.units = plan.units; g.tiles_full = plan.tiles_full;
@@ -259,7 +269,8 @@ int run_gemm_sm100(int dtype, int epi, const GemmPlan& plan, const void* x, int6
   CUtensorMap ta, tb;
   int rc = make_tmap_2d(&ta, dtype, x, g.M, g.K, ldx, 128, kBK);
   if (rc) return rc;
-  rc = make_tmap_2d(&tb, dtype, w, g.N, g.K, ldw, (epi == EPI_SILU_MUL || plan.cta2) ? plan.bn / 2 : plan.bn, kBK);
+  rc = make_tmap_2d(&tb, dtype, w, b_rows > 0 ? b_rows : g.N, g.K, ldw,
+                    (epi == EPI_SILU_MUL || plan.cta2) ? plan.bn / 2 : plan.bn, kBK);
   if (rc) return rc;
   if (dtype == SB200_BF16) return dispatch_epi<__nv_bfloat16>(epi, ta, tb, g, cv, ra, s);
   if (dtype == SB200_F16) return dispatch_epi<__half>(epi, ta, tb, g, cv, ra, s);

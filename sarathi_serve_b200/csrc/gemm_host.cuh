@@ -19,7 +19,8 @@ struct GemmPlan {
 GemmPlan plan_gemm(int epi, int64_t M, int64_t N, int64_t K, int head_size, int tile_cfg, size_t ws_bytes);
 uint32_t gemm_push_increments(const GemmPlan& p, int64_t M, int64_t lo, int64_t hi);
 int run_gemm_sm100(int dtype, int epi, const GemmPlan& plan, const void* x, int64_t ldx, const void* w, int64_t ldw,
-                   GemmArgs g, void* workspace, const CommView& cv, const ReduceArgs& ra, cudaStream_t s);
+                   GemmArgs g, void* workspace, const CommView& cv, const ReduceArgs& ra, cudaStream_t s,
+                   int64_t b_rows = 0);  // b_rows: rows of the B matrix when it is taller than g.N (stacked experts)
 int run_gemm_f32(float* C, int64_t ldc, const float* A, int64_t lda, const float* B, int64_t ldb, const float* bias,
                  int M, int N, int K, cudaStream_t s);
 

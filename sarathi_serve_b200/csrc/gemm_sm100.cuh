@@ -33,6 +33,12 @@
 //   EPI_PUSH     row-parallel projection: partial rows go to the owner rank's
 //                reduce slots; the reduce / residual / norm / broadcast phases of
 //                comm.cuh run in the same kernel after the tiles.
+//   EPI_MOE_SCATTER  second expert GEMM: row r of the expert-sorted activations is scaled by its
+//                routed weight and stored at its (token, k) slot.
+// Grouped (mixture-of-experts) mode: when `expert_ids` is set, the rows of A are the
+// expert-sorted, block-padded slots of moe_align_block_size (block = tile rows), tile row block
+// mt uses the weights of expert expert_ids[mt] (B rows offset by expert * rows_per_expert), and
+// row blocks at or beyond *num_post_pad are skipped.
 #pragma once
 
 #include "comm.cuh"
@@ -40,7 +46,7 @@
 
 namespace sb200 {
 
-enum GemmEpilogue { EPI_STORE = 0, EPI_ROTARY = 1, EPI_SILU_MUL = 2, EPI_PUSH = 3 };
+enum GemmEpilogue { EPI_STORE = 0, EPI_ROTARY = 1, EPI_SILU_MUL = 2, EPI_PUSH = 3, EPI_MOE_SCATTER = 4 };
 
 constexpr int kBK = 64;            // K elements per stage: 128 bytes of bf16 = one swizzle row
 constexpr int kGemmThreads = 320;  // 10 warps
@@ -70,6 +76,13 @@ struct GemmArgs {
   int l2_prefetch;         // k-blocks ahead at which the B boxes are prefetched into L2 (0 = off)
   int debug;               // profiling switches (0 in production)
   int m_tiles, n_tiles, k_blocks;
+  // grouped (MoE) mode
+  const int32_t* expert_ids;    // [m_tiles] expert of each row block, or null
+  const int32_t* num_post_pad;  // [1] rows in use (device value)
+  int rows_per_expert;          // B rows per expert
+  const int32_t* sorted_ids;    // EPI_MOE_SCATTER: [rows] (token, k) slot of each sorted row (>= num_slots: padding)
+  const float* topk_w;          // EPI_MOE_SCATTER: [num_slots] routed weight of each slot
+  int num_slots;
   float* ws;               // partial-tile workspace: [cut tiles * S][BM][bn] fp32
   uint32_t* ws_counters;   // [cut tiles][arrived[16], done[16]], zero between launches
   int cta2;                // 1: tiles of 256 rows computed by CTA pairs (cta_group::2)
@@ -218,6 +231,7 @@ template <typename T> struct RowCtx {
   T* out_row;      // out + gm * ldo   (EPI_PUSH: the owner's partial slot row)
   const T* cs;     // rotary: cache row of this token
   bool vec_ok;
+  float scale;     // EPI_MOE_SCATTER: routed weight of this row's slot
 };
 
 // Work units of a tile: the chunks an epilogue warp fetches together.
@@ -225,6 +239,7 @@ template <typename T> struct RowCtx {
 //   SILU_MUL     : unit u = gate columns [32u, ..) with up columns [bn/2 + 32u, ..)
 //   ROTARY       : unit u -> (head = u / upH, j = u % upH), upH = head_size/32 units per head;
 //                  for a NeoX-rotated head only j < upH/2 does work (chunks j and j + upH/2).
+// (EPI_MOE_SCATTER uses the units of STORE.)
 template <int EPI> __device__ __forceinline__ int num_units(const GemmArgs& g) {
   return EPI == EPI_SILU_MUL ? g.bn / 64 : g.bn / 32;
 }
@@ -262,7 +277,16 @@ __device__ __forceinline__ void finish_unit(const GemmArgs& g, const RowCtx<T>& 
   if (nch == 0) return;
   float a[32];
   src.load32(cols[0], a);  // warp-uniform (TMEM loads are .sync.aligned)
-  if constexpr (EPI == EPI_STORE || EPI == EPI_PUSH) {
+  if constexpr (EPI == EPI_MOE_SCATTER) {
+    // Reference: the second fused_moe_kernel launch multiplies the fp32 accumulator by the routed
+    // weight before rounding to T (layers/fused_moe/fused_moe.py:130-147, MUL_ROUTED_WEIGHT).
+    const int gn = rc.n0 + cols[0];
+    if (rc.row_ok && gn < g.N) {
+#pragma unroll
+      for (int j = 0; j < 32; ++j) a[j] *= rc.scale;
+      store_row32<T>(rc.out_row + gn, a, g.N - gn, rc.vec_ok);
+    }
+  } else if constexpr (EPI == EPI_STORE || EPI == EPI_PUSH) {
     const int gn = rc.n0 + cols[0];
     if (rc.row_ok && gn < g.N) {
       if (EPI == EPI_STORE && g.bias) {
@@ -339,7 +363,15 @@ __device__ __forceinline__ RowCtx<T> make_row_ctx(const GemmArgs& g, const CommV
   rc.row_ok = gm < g.M;
   rc.n0 = n0;
   rc.cs = nullptr;
-  if constexpr (EPI == EPI_PUSH) {
+  rc.scale = 1.f;
+  if constexpr (EPI == EPI_MOE_SCATTER) {
+    int slot = g.num_slots;
+    if (rc.row_ok) slot = g.sorted_ids[gm];
+    rc.row_ok = rc.row_ok && slot < g.num_slots;  // padding rows produce nothing
+    rc.out_row = reinterpret_cast<T*>(g.out) + (size_t)(rc.row_ok ? slot : 0) * g.ldo;
+    rc.vec_ok = ((g.ldo & 7) == 0) && aligned16(g.out);
+    if (rc.row_ok) rc.scale = g.topk_w[slot];
+  } else if constexpr (EPI == EPI_PUSH) {
     const int owner = rc.row_ok ? gm / red.rows_per_rank : 0;
     const int lr = gm - owner * red.rows_per_rank;
     rc.out_row = rc.row_ok ? reinterpret_cast<T*>(comm.heap[owner] + comm.partial_off[red.set]) +
@@ -399,6 +431,8 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
   sc.S = g.rem_splits;
   sc.kbp = g.kb_per_part;
   sc.k_blocks = g.k_blocks;
+  // grouped mode: rows of A in use (a device value written by moe_align_block_size earlier in the stream)
+  const int rows_in_use = g.expert_ids ? min(g.M, *g.num_post_pad) : g.M;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < kStages; ++s) {
@@ -436,6 +470,11 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
         const Segment sg = segment_of(sc, unit_id, it);
         if (!sg.valid) break;
         const int mt = sg.tile % g.m_tiles, nt = sg.tile / g.m_tiles;
+        int b_row0 = 0;  // grouped mode: first B row of this row block's expert
+        if (g.expert_ids) {
+          if (mt * BM >= rows_in_use) continue;  // row block beyond the padded slots: every role skips it
+          b_row0 = g.expert_ids[mt] * g.rows_per_expert;
+        }
         for (int kb = sg.kb0; kb < sg.kb1; ++kb) {
           if (!ptx::mbar_wait(&empty_bar[stage], phase ^ 1u, abort_flag)) { ok = false; break; }
           uint8_t* sa = stage_base + (size_t)stage * stage_bytes;
@@ -459,9 +498,9 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
             for (int a = 0; a < MI; ++a)  // accumulator a covers tile rows [256a, 256a+256): this CTA's half of them
               ptx::tma_load_2d_pair(sa + a * (128 * kBK * 2), &tmap_a, bar, kb * kBK, mt * BM + a * 256 + (int)cta_rank * 128);
             if (EPI == EPI_SILU_MUL)  // even CTA: gate rows, odd CTA: the matching up rows
-              ptx::tma_load_2d_pair(sb, &tmap_b, bar, kb * kBK, (int)cta_rank * (g.N / 2) + nt * (BN / 2));
+              ptx::tma_load_2d_pair(sb, &tmap_b, bar, kb * kBK, b_row0 + (int)cta_rank * (g.N / 2) + nt * (BN / 2));
             else
-              ptx::tma_load_2d_pair(sb, &tmap_b, bar, kb * kBK, nt * BN + (int)cta_rank * (BN / 2));
+              ptx::tma_load_2d_pair(sb, &tmap_b, bar, kb * kBK, b_row0 + nt * BN + (int)cta_rank * (BN / 2));
           } else {
             ptx::mbar_expect_tx(&full_bar[stage], (uint32_t)stage_bytes);
 #pragma unroll
@@ -469,10 +508,10 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
               ptx::tma_load_2d(sa + a * (128 * kBK * 2), &tmap_a, &full_bar[stage], kb * kBK, mt * BM + a * 128);
             if (EPI == EPI_SILU_MUL) {
               // B tile = BN/2 rows of the gate shard followed by the matching BN/2 rows of the up shard
-              ptx::tma_load_2d(sb, &tmap_b, &full_bar[stage], kb * kBK, nt * (BN / 2));
-              ptx::tma_load_2d(sb + (BN / 2) * (kBK * 2), &tmap_b, &full_bar[stage], kb * kBK, g.N / 2 + nt * (BN / 2));
+              ptx::tma_load_2d(sb, &tmap_b, &full_bar[stage], kb * kBK, b_row0 + nt * (BN / 2));
+              ptx::tma_load_2d(sb + (BN / 2) * (kBK * 2), &tmap_b, &full_bar[stage], kb * kBK, b_row0 + g.N / 2 + nt * (BN / 2));
             } else {
-              ptx::tma_load_2d(sb, &tmap_b, &full_bar[stage], kb * kBK, nt * BN);
+              ptx::tma_load_2d(sb, &tmap_b, &full_bar[stage], kb * kBK, b_row0 + nt * BN);
             }
           }
           if (++stage == kStages) { stage = 0; phase ^= 1u; }
@@ -484,11 +523,13 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
     if (lane == 0 && leader) {
       int stage = 0;
       uint32_t phase = 0;
-      int local = 0;
+      int used = 0;  // tiles actually computed (selects the TMEM buffer)
       bool ok = true;
-      for (; ok; ++local) {
-        const Segment sg = segment_of(sc, unit_id, local);
+      for (int it = 0; ok; ++it) {
+        const Segment sg = segment_of(sc, unit_id, it);
         if (!sg.valid) break;
+        if (g.expert_ids && (sg.tile % g.m_tiles) * BM >= rows_in_use) continue;
+        const int local = used++;
         const int kb0 = sg.kb0, kb1 = sg.kb1;
         const int buf = dbuf ? (local & 1) : 0;
         const uint32_t use = (uint32_t)(dbuf ? (local >> 1) : local);  // earlier uses of this buffer
@@ -530,13 +571,15 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
     const int row_in_tile = (CTA2 ? a0 * 256 + (int)cta_rank * 128 : a0 * 128) + q * 32 + lane;
     const int u_first = (MI == 2) ? 0 : hsel, u_step = (MI == 2) ? 1 : 2;
     const uint32_t empty_remote = CTA2 ? ptx::map_to_cta(ptx::smem_u32(&tmem_empty[0]), 0) : 0u;
-    int local = 0;
+    int used = 0;
     bool ok = true;
-    for (; ok; ++local) {
-      const Segment sg = segment_of(sc, unit_id, local);
+    for (int it = 0; ok; ++it) {
+      const Segment sg = segment_of(sc, unit_id, it);
       if (!sg.valid) break;
       const int tile = sg.tile, S = sg.parts;
       const int mt = tile % g.m_tiles, nt = tile / g.m_tiles;
+      if (g.expert_ids && mt * BM >= rows_in_use) continue;
+      const int local = used++;
       const int buf = dbuf ? (local & 1) : 0;
       const uint32_t use = (uint32_t)(dbuf ? (local >> 1) : local);
       ok = __all_sync(0xffffffffu, ptx::mbar_wait(&tmem_full[buf], use & 1u, abort_flag) ? 1 : 0) != 0;
@@ -615,13 +658,13 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
         // finished_here set for a whole tile and S of them (one per part) for a tile cut along K, so
         // the host can count the increments per (tile, slot, owner of the slot's rows).
         if (finished_here) {
-          __threadfence_system();
+          fence_scope(comm.world > 1);
           __syncwarp();
           if (lane == 0) {
             const int r_lo = mt * BM + row_in_tile - lane, r_hi = min(g.M, r_lo + 32) - 1;
             if (r_hi >= r_lo)
               for (int o = r_lo / red.rows_per_rank; o <= r_hi / red.rows_per_rank; ++o)
-                red_release_sys_add(comm_counter(comm, o, CC_PUSH0 + red.set), 1u);
+                red_add_relaxed(comm_counter(comm, o, CC_PUSH0 + red.set), 1u, comm.world > 1);
           }
         }
       }
@@ -645,8 +688,7 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
   }
 
   if constexpr (EPI == EPI_PUSH) {
-    const int warps_per_cta = kGemmThreads / 32;
-    reduce_phase<T>(comm, red, blockIdx.x * warps_per_cta + warp, gridDim.x * warps_per_cta);
+    reduce_phase<T>(comm, red, blockIdx.x, gridDim.x);
     if (red.out_copy || red.resid_copy || blockIdx.x == 0) {
       if (finish_phase(comm, red) && (red.out_copy || red.resid_copy))
         copy_out_phase<T>(comm, red, blockIdx.x * kGemmThreads + threadIdx.x, gridDim.x * kGemmThreads);

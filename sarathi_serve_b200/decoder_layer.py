@@ -19,8 +19,9 @@ import torch
 import torch.nn as nn
 
 from . import parallel_state as ps
+from .fused_moe import FusedMoE
 from .nn_layers import RMSNorm, SiluAndMul, get_rope
-from .tp_layers import ColumnParallelLinear, RowParallelLinear
+from .tp_layers import ColumnParallelLinear, ReplicatedLinear, RowParallelLinear
 
 
 class LlamaMLP(nn.Module):
@@ -127,6 +128,15 @@ class LlamaDecoderLayer(nn.Module):
         act = self.mlp.gate_up_proj.forward_silu_mul(h)
         return self.mlp.down_proj.forward_fused(act, resid, next_norm_weight, next_eps, out=out)
 
+    def tune(self, num_tokens: int) -> None:
+        """Autotune the four projections for batches of ``num_tokens`` tokens (all tensor-parallel ranks together)."""
+        sa = self.self_attn
+        fused_rot = sa.qkv_proj.weight.dtype in (torch.bfloat16, torch.float16)
+        sa.qkv_proj.tune(num_tokens, "rotary" if fused_rot else "store", sa.head_dim)
+        sa.o_proj.tune(num_tokens)
+        self.mlp.gate_up_proj.tune(num_tokens, "silu" if fused_rot else "store")
+        self.mlp.down_proj.tune(num_tokens)
+
     def forward(self, positions: torch.Tensor, hidden_states: torch.Tensor, layer_cache_idx: int,
                 attention_backend_wrapper) -> torch.Tensor:
         normed = self.input_layernorm(hidden_states)
@@ -142,3 +152,58 @@ class LlamaDecoderLayer(nn.Module):
         layer's input_layernorm (or the model's final norm)."""
         return self._attn_mlp(positions, normed, residual, layer_cache_idx, attention_backend_wrapper,
                               next_norm.weight.data, next_norm.variance_epsilon)
+
+
+class MixtralMoE(nn.Module):
+    """Router + experts of a Mixtral block, every expert sharded over the tensor-parallel ranks
+    (sarathi/model_executor/models/mixtral.py:58-108): ``gate`` is a replicated [E, H] linear,
+    ``experts`` a FusedMoE that also all-reduces its output."""
+
+    def __init__(self, num_experts: int, top_k: int, hidden_size: int, intermediate_size: int,
+                 params_dtype: Optional[torch.dtype] = None, layer_id: Optional[int] = None):
+        super().__init__()
+        self.hidden_size = hidden_size
+        self.gate = ReplicatedLinear(hidden_size, num_experts, bias=False, params_dtype=params_dtype,
+                                     layer_id=layer_id)
+        self.experts = FusedMoE(num_experts=num_experts, top_k=top_k, hidden_size=hidden_size,
+                                intermediate_size=intermediate_size, params_dtype=params_dtype, reduce_results=True,
+                                renormalize=True, layer_id=layer_id)
+
+    def forward(self, hidden_states: torch.Tensor) -> torch.Tensor:
+        num_tokens, hidden_size = hidden_states.shape
+        hidden_states = hidden_states.view(-1, self.hidden_size)
+        router_logits, _ = self.gate(hidden_states)
+        final_hidden_states = self.experts(hidden_states, router_logits)
+        return final_hidden_states.view(num_tokens, hidden_size)
+
+
+class MixtralDecoderLayer(nn.Module):
+    """Mixtral decoder layer (mixtral.py:194-258): Llama-style attention block, MoE feed-forward.
+    Attribute / parameter names follow the reference: ``self_attn``, ``block_sparse_moe``,
+    ``input_layernorm``, ``post_attention_layernorm``."""
+
+    def __init__(self, config, layer_id: Optional[int] = None) -> None:
+        super().__init__()
+        self.hidden_size = config.hidden_size
+        rope_theta = getattr(config, "rope_theta", 10000)
+        self.self_attn = LlamaAttention(hidden_size=self.hidden_size, num_heads=config.num_attention_heads,
+                                        num_kv_heads=config.num_key_value_heads, rope_theta=rope_theta,
+                                        max_position_embeddings=getattr(config, "max_position_embeddings", 8192),
+                                        layer_id=layer_id)
+        self.block_sparse_moe = MixtralMoE(num_experts=config.num_local_experts, top_k=config.num_experts_per_tok,
+                                           hidden_size=config.hidden_size,
+                                           intermediate_size=config.intermediate_size, layer_id=layer_id)
+        self.input_layernorm = RMSNorm(config.hidden_size, eps=config.rms_norm_eps, layer_id=layer_id)
+        self.post_attention_layernorm = RMSNorm(config.hidden_size, eps=config.rms_norm_eps, layer_id=layer_id)
+
+    def forward(self, positions: torch.Tensor, hidden_states: torch.Tensor, layer_cache_idx: int,
+                attention_backend_wrapper) -> torch.Tensor:
+        sa = self.self_attn
+        normed = self.input_layernorm(hidden_states)
+        q, k, v = sa.qkv_rotary(positions, normed)
+        attn_out = attention_backend_wrapper.forward(q, k, v, layer_cache_idx, sa.scaling, sa.layer_id)
+        # o_proj + all-reduce + residual add + post-attention RMSNorm in one kernel
+        h, resid = sa.o_proj.forward_fused(attn_out, hidden_states, self.post_attention_layernorm.weight.data,
+                                           self.post_attention_layernorm.variance_epsilon)
+        moe_out = self.block_sparse_moe(h.clone())  # the experts overwrite their input; `h` lives in the comm heap
+        return resid + moe_out

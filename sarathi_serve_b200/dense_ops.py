@@ -145,3 +145,95 @@ def gemm_plan(epilogue: int, T: int, Nn: int, K: int, head_size: int = 128, tile
     keys = ("cta_pairs", "accumulators", "bn", "units", "tiles_full", "k_parts", "kb_per_part", "stages", "m_tiles",
             "n_tiles", "k_blocks")
     return dict(zip(keys, out))
+
+
+# ---------------------------------------------------------------- autotuning
+_tuned: dict = {}
+
+
+def tuned_cfg(kind: str, T: int, Nn: int, K: int, dtype: torch.dtype) -> int:
+    """Tile configuration found by ``autotune`` for this problem, or 0 (library default)."""
+    return _tuned.get((kind, T, Nn, K, dtype), 0)
+
+
+def _candidates(kind: str, T: int, Nn: int, K: int, head_size: int):
+    epi = {"store": EPI_NONE, "rotary": EPI_ROTARY, "silu": EPI_SILU_MUL, "push": 3}[kind]
+    seen, out = set(), []
+    for mode in (1, 3, 4):
+        for bn in (64, 96, 128, 160, 192, 224, 256):
+            for s in (1, 2, 3, 4, 6, 8):
+                cfg = bn + 1000 * mode + 100000 * s
+                try:
+                    p = gemm_plan(epi, T, Nn, K, head_size, cfg)
+                except RuntimeError:
+                    continue
+                key = tuple(p.values())
+                if key in seen:
+                    continue
+                seen.add(key)
+                # encode what the planner actually accepted, so that the key reproduces the plan
+                mode_eff = (2 + p["accumulators"]) if p["cta_pairs"] else p["accumulators"]
+                out.append(p["bn"] + 1000 * mode_eff + 100000 * p["k_parts"])
+    return sorted(set(out))
+
+
+def autotune(kind: str, T: int, Nn: int, K: int, dtype: torch.dtype, device: torch.device, head_size: int = 128,
+             group=None, launches: int = 6, reps: int = 3) -> int:
+    """Time the tile configurations the planner accepts for one projection shape (CUDA-graph
+    replay of ``launches`` back-to-back kernels over rotating weight copies) and remember the
+    fastest.  ``kind``: "store" | "rotary" | "silu" | "push" (row-parallel: tuned with the plain
+    store epilogue, which has the same main loop).  With ``group`` (tensor-parallel ranks) rank 0's
+    choice is broadcast so that every rank uses the same schedule."""
+    key = (kind, T, Nn, K, dtype)
+    if key in _tuned:
+        return _tuned[key]
+    if dtype == torch.float32:
+        _tuned[key] = 0
+        return 0
+    run_kind = "store" if kind == "push" else kind
+    ncopy = max(2, min(8, int(260e6 // (Nn * K * 2)) + 1))
+    ws = [torch.randn(Nn, K, device=device, dtype=torch.float32).mul_(0.02).to(dtype) for _ in range(ncopy)]
+    x = torch.randn(T, K, device=device, dtype=torch.float32).to(dtype)
+    pos = torch.zeros(T, dtype=torch.int64, device=device)
+    cache = torch.ones(8, head_size, device=device, dtype=dtype)
+
+    def call(i, cfg):
+        if run_kind == "silu":
+            return linear_silu_mul(x, ws[i % ncopy], tile_n=cfg)
+        if run_kind == "rotary":
+            return linear_rotary(x, ws[i % ncopy], pos, cache, head_size, (Nn // head_size // 2) * head_size, True,
+                                 tile_n=cfg)
+        return linear(x, ws[i % ncopy], tile_n=cfg)
+
+    best, best_us = 0, float("inf")
+    stream = torch.cuda.Stream(device=device)
+    for cfg in [0] + _candidates(kind, T, Nn, K, head_size):
+        try:
+            with torch.cuda.stream(stream):
+                call(0, cfg)
+                torch.cuda.synchronize(device)
+                graph = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(graph, stream=stream):
+                    for i in range(launches):
+                        call(i, cfg)
+                graph.replay()
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                e0.record(stream)
+                for _ in range(reps):
+                    graph.replay()
+                e1.record(stream)
+                torch.cuda.synchronize(device)
+            us = e0.elapsed_time(e1) * 1e3 / (launches * reps)
+        except RuntimeError:
+            continue
+        if us < best_us:
+            best, best_us = cfg, us
+    if group is not None:
+        import torch.distributed as dist
+        box = [best]
+        dist.broadcast_object_list(box, src=dist.get_global_rank(group, 0) if hasattr(dist, "get_global_rank") else 0,
+                                   group=group)
+        best = box[0]
+    _tuned[key] = best
+    check_status(device)
+    return best

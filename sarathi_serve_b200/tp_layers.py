@@ -61,8 +61,17 @@ class ColumnParallelLinear(torch.nn.Module):
         self.weight = Parameter(torch.empty(self.output_size_per_partition, self.input_size,
                                             device=_param_device(), dtype=dtype), requires_grad=False)
 
+    def _cfg(self, kind: str, x: torch.Tensor) -> int:
+        return dense_ops.tuned_cfg(kind, x.shape[0] if x.dim() == 2 else x.numel() // x.shape[-1],
+                                   self.weight.shape[0], self.weight.shape[1], x.dtype)
+
+    def tune(self, num_tokens: int, kind: str = "store", head_size: int = 128) -> int:
+        """Pick the fastest tile configuration for [num_tokens, in] inputs (see dense_ops.autotune)."""
+        return dense_ops.autotune(kind, num_tokens, self.weight.shape[0], self.weight.shape[1], self.weight.dtype,
+                                  self.weight.device, head_size)
+
     def apply_weights(self, x: torch.Tensor, bias: Optional[torch.Tensor]) -> torch.Tensor:
-        return dense_ops.linear(x, self.weight, bias)
+        return dense_ops.linear(x, self.weight, bias, tile_n=self._cfg("store", x))
 
     def forward(self, input_) -> Tuple[torch.Tensor, Optional[torch.Tensor]]:
         bias = self.bias if not self.skip_bias_add else None
@@ -76,7 +85,8 @@ class ColumnParallelLinear(torch.nn.Module):
         assert self.bias is None and not self.gather_output
         if dense_ops.fused_rotary_supported(input_, rotary_emb.head_size, rotary_emb.rotary_dim):
             return dense_ops.linear_rotary(input_, self.weight, positions, rotary_emb.cos_sin_cache,
-                                           rotary_emb.head_size, rot_cols, rotary_emb.is_neox_style)
+                                           rotary_emb.head_size, rot_cols, rotary_emb.is_neox_style,
+                                           tile_n=self._cfg("rotary", input_))
         qkv = dense_ops.linear(input_, self.weight)
         n_rot_heads = rot_cols // rotary_emb.head_size
         # one call over q|k as a single strided "query" view; no separate key tensor
@@ -87,7 +97,7 @@ class ColumnParallelLinear(torch.nn.Module):
         """gate_up projection returning silu(gate) * up ([T, N/(2 tp)])."""
         assert self.bias is None and not self.gather_output
         if input_.dtype in (torch.bfloat16, torch.float16):
-            return dense_ops.linear_silu_mul(input_, self.weight)
+            return dense_ops.linear_silu_mul(input_, self.weight, tile_n=self._cfg("silu", input_))
         from . import activation_ops
         gate_up = dense_ops.linear(input_, self.weight)
         out = torch.empty(gate_up.shape[0], gate_up.shape[1] // 2, dtype=gate_up.dtype, device=gate_up.device)
@@ -130,6 +140,16 @@ class RowParallelLinear(torch.nn.Module):
     def apply_weights(self, x: torch.Tensor) -> torch.Tensor:
         return dense_ops.linear(x, self.weight)
 
+    def tune(self, num_tokens: int) -> int:
+        """Pick the fastest tile configuration of the fused GEMM for [num_tokens, in/tp] inputs; every rank of
+        the tensor-parallel group must call this together (rank 0's choice is shared)."""
+        group = ps.get_tensor_model_parallel_group() if self.world_size > 1 else None
+        return dense_ops.autotune("push", num_tokens, self.weight.shape[0], self.weight.shape[1], self.weight.dtype,
+                                  self.weight.device, group=group)
+
+    def _cfg(self, x: torch.Tensor) -> int:
+        return dense_ops.tuned_cfg("push", x.shape[0], self.weight.shape[0], self.weight.shape[1], x.dtype)
+
     def _comm(self, T: int):
         es = torch.empty((), dtype=self.weight.dtype).element_size()
         rows = -(-T // self.world_size) * self.world_size
@@ -144,7 +164,7 @@ class RowParallelLinear(torch.nn.Module):
             lead = input_parallel.shape[:-1]
             x2 = input_parallel.reshape(-1, input_parallel.shape[-1])
             out = torch.empty(x2.shape[0], self.output_size, dtype=x2.dtype, device=x2.device)
-            self._comm(x2.shape[0]).rowpar_linear(x2, self.weight, bias=add_bias, out=out)
+            self._comm(x2.shape[0]).rowpar_linear(x2, self.weight, bias=add_bias, out=out, tile_n=self._cfg(x2))
             output = out.view(*lead, self.output_size)
         else:
             # No reduction: the bias (if any) is added to the local product, as the reference does.
@@ -165,7 +185,7 @@ class RowParallelLinear(torch.nn.Module):
         return self._comm(input_.shape[0]).rowpar_linear(input_, self.weight, bias=add_bias, residual=residual,
                                                          norm_weight=norm_weight, eps=eps,
                                                          resid_everywhere=resid_everywhere, out=out,
-                                                         resid_out=resid_out)
+                                                         resid_out=resid_out, tile_n=self._cfg(input_))
 
 
 class ReplicatedLinear(torch.nn.Module):

@@ -1,0 +1,95 @@
+"""GPU parity of the mixture-of-experts path (routing -> block alignment -> gather -> two grouped
+tcgen05 GEMMs -> sum over the k slots) against the CPU oracle, through the package's
+reference-shaped API (fused_topk / fused_experts / fused_moe / FusedMoE / MixtralMoE)."""
+import pytest
+import torch
+
+from helpers import rel_err
+from oracle import tp_layer_oracle as O
+from sarathi_serve_b200 import synthetic as S
+
+pytestmark = pytest.mark.gpu
+
+
+def _check_status():
+    from sarathi_serve_b200 import dense_ops
+    dense_ops.check_status(torch.device("cuda", torch.cuda.current_device()))
+
+
+@pytest.mark.parametrize("case_name,world", [("mini_moe", 1), ("mini_moe", 2), ("config5", 8)])
+def test_fused_experts_and_routing(case_name, world):
+    """One rank's shard of the experts (TP-sharded along the intermediate dimension)."""
+    from sarathi_serve_b200 import fused_moe as FM
+    case = S.MOE_CASES[case_name]
+    d = S.generate_moe(case, world=world, rank=0)
+    x, w13, w2, logits = d["x"], d["w13"], d["w2"], d["logits"]
+    # routing: ids bit-exact against the oracle
+    wts, ids = FM.fused_topk(x.cuda(), logits.cuda(), case.top_k, True)
+    ow, oids, _ = O.topk_softmax(logits, case.top_k, renormalize=True)
+    assert torch.equal(ids.cpu(), oids)
+    assert torch.allclose(wts.cpu(), ow, rtol=1e-5, atol=1e-7)
+    # block alignment with the GEMM's block: bit-exact
+    s_ids, e_ids, npp = FM.moe_align_block_size(ids, FM.block_rows(), case.num_experts)
+    os_, oe, on = O.moe_align_block_size(oids.long(), FM.block_rows(), case.num_experts)
+    n = int(on)
+    assert int(npp) == n and torch.equal(s_ids.cpu(), os_) and torch.equal(e_ids[:n // FM.block_rows()].cpu(), oe[:n // FM.block_rows()])
+    # experts
+    out = FM.fused_experts(x.cuda(), w13.cuda(), w2.cuda(), wts, ids, inplace=False)
+    _check_status()
+    ref = O.fused_experts(x, w13, w2, ow, oids.long())
+    assert rel_err(out, ref) <= 2e-2
+    # in place + the one-call form
+    xin = x.cuda().clone()
+    out2 = FM.fused_moe(xin, w13.cuda(), w2.cuda(), logits.cuda(), case.top_k, renormalize=True, inplace=True)
+    assert out2 is xin and torch.equal(out2, out)
+
+
+@pytest.mark.parametrize("T", [1, 7, 129, 300])
+def test_fused_experts_token_counts(T):
+    """Ragged token counts, an expert that receives nothing, fp16."""
+    from sarathi_serve_b200 import fused_moe as FM
+    g = torch.Generator().manual_seed(T)
+    H, I, E, k = 256, 384, 8, 2
+    x = torch.randn(T, H, generator=g).to(torch.float16)
+    w13 = (torch.randn(E, 2 * I, H, generator=g) * 0.05).to(torch.float16)
+    w2 = (torch.randn(E, H, I, generator=g) * 0.05).to(torch.float16)
+    logits = torch.randn(T, E, generator=g)
+    logits[:, 3] = -30.0  # expert 3 is never chosen
+    wts, ids = FM.fused_topk(x.cuda(), logits.cuda(), k, True)
+    assert not bool((ids == 3).any())
+    out = FM.fused_experts(x.cuda(), w13.cuda(), w2.cuda(), wts, ids)
+    _check_status()
+    ow, oids, _ = O.topk_softmax(logits, k, renormalize=True)
+    assert rel_err(out, O.fused_experts(x, w13, w2, ow, oids.long())) <= 2e-2
+
+
+def test_mixtral_moe_block_tp1():
+    """MixtralMoE module (gate + FusedMoE) at tensor-parallel size 1 against the oracle's MoE layer."""
+    from sarathi_serve_b200 import parallel_state as ps
+    from sarathi_serve_b200.decoder_layer import MixtralMoE
+    ps.destroy_model_parallel()
+    ps.initialize_model_parallel(1)
+    try:
+        case = S.MOE_CASES["mini_moe"]
+        d = S.generate_moe(case)
+        g = torch.Generator().manual_seed(5)
+        gate_w = (torch.randn(case.num_experts, case.hidden_size, generator=g) * 0.05).to(case.dtype)
+        old = torch.get_default_dtype()
+        torch.set_default_dtype(case.dtype)
+        try:
+            moe = MixtralMoE(case.num_experts, case.top_k, case.hidden_size, case.intermediate_size)
+        finally:
+            torch.set_default_dtype(old)
+        sd = moe.state_dict()
+        assert set(sd) == {"gate.weight", "experts.w13_weight", "experts.w2_weight"}
+        with torch.no_grad():
+            sd["gate.weight"].copy_(gate_w)
+            sd["experts.w13_weight"].copy_(d["w13"])
+            sd["experts.w2_weight"].copy_(d["w2"])
+        x = d["x"].cuda()
+        out = moe(x.clone())
+        _check_status()
+        ref = O.moe_layer(d["x"], gate_w, [d["w13"]], [d["w2"]], case.top_k)
+        assert rel_err(out, ref) <= 2e-2
+    finally:
+        ps.destroy_model_parallel()

@@ -165,6 +165,40 @@ def _body_layer(rank, world):
             assert _rel(out[::step], gold["out"]) <= TOL[case.dtype], (case_name, "fixture")
 
 
+def _body_moe(rank, world):
+    """Tensor-parallel MoE block: experts sharded along the intermediate dimension, k-slot sum fused
+    into the all-reduce."""
+    from oracle import tp_layer_oracle as O
+    from sarathi_serve_b200 import parallel_state as ps, synthetic as S
+    from sarathi_serve_b200.decoder_layer import MixtralMoE
+    for case_name in ("mini_moe", "config5"):
+        case = S.MOE_CASES[case_name]
+        if case_name == "config5":  # a 2-rank slice of the 8-way sharded experts keeps the CPU oracle affordable
+            shards = [S.generate_moe(case, world=8, rank=r) for r in range(world)]
+        else:
+            shards = [S.generate_moe(case, world=world, rank=r) for r in range(world)]
+        g = torch.Generator().manual_seed(5)
+        gate_w = (torch.randn(case.num_experts, case.hidden_size, generator=g) * 0.05).to(case.dtype)
+        old = torch.get_default_dtype()
+        torch.set_default_dtype(case.dtype)
+        try:
+            moe = MixtralMoE(case.num_experts, case.top_k, case.hidden_size,
+                             shards[0]["w2"].shape[2] * world)
+        finally:
+            torch.set_default_dtype(old)
+        sd = moe.state_dict()
+        with torch.no_grad():
+            sd["gate.weight"].copy_(gate_w)
+            sd["experts.w13_weight"].copy_(shards[rank]["w13"])
+            sd["experts.w2_weight"].copy_(shards[rank]["w2"])
+        x = shards[0]["x"]
+        out = moe(x.cuda().clone())
+        ps.get_tensor_model_parallel_comm().check_status()
+        if rank == 0:
+            ref = O.moe_layer(x, gate_w, [s_["w13"] for s_ in shards], [s_["w2"] for s_ in shards], case.top_k)
+            assert _rel(out, ref) <= 2e-2, case_name
+
+
 def _body_lost_peer(rank, world):
     """Rank 1 sits one collective out; rank 0's wait is bounded and reports a timeout."""
     import torch.distributed as dist
@@ -195,6 +229,10 @@ def test_rowpar_linear_two_gpus():
 
 def test_decoder_layer_two_gpus():
     _run("_body_layer", 29803)
+
+
+def test_moe_block_two_gpus():
+    _run("_body_moe", 29805)
 
 
 def test_lost_peer_reports_timeout():
