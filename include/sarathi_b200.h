@@ -228,6 +228,10 @@ int sb200_comm_set_wait_limit(sb200_comm* comm, int64_t cycles);
  * SB200_ERR_PEER_TIMEOUT if a bounded wait ran out since the last clear. */
 int sb200_comm_status(sb200_comm* comm, sb200_stream_t stream, uint32_t* host_status);
 int sb200_comm_clear_status(sb200_comm* comm, sb200_stream_t stream);
+/* Profiling aid: with a device buffer of 148 * 8 uint64, thread 0 of every CTA of the collective
+ * kernels records %globaltimer (ns) at: 0 start, 1 tiles/push issued, 2 reduce entered, 3 every
+ * rank's push flag seen, 4 rows reduced, 5 every rank's done flag seen, 6 exit.  NULL switches it off (default). */
+int sb200_comm_set_trace(sb200_comm* comm, void* device_buffer);
 
 /* Sum `in` [T, H] over the ranks; then, on the summed rows,
  *   z = sum (+ bias) (+ residual);   y = norm_w ? rms_norm(z, norm_w, eps) : z.

@@ -74,6 +74,10 @@ class TPComm:
     def set_wait_limit_cycles(self, cycles: int) -> None:
         N.check(N.lib().sb200_comm_set_wait_limit(self._h, int(cycles)), "comm_set_wait_limit")
 
+    def set_trace(self, buffer: Optional[torch.Tensor]) -> None:
+        """Profiling aid: int64 tensor [>=148*8] on this device receives per-CTA phase time stamps (ns)."""
+        N.check(N.lib().sb200_comm_set_trace(self._h, N.ptr(buffer)), "comm_set_trace")
+
     def check_status(self) -> None:
         """Synchronises the current stream; raises if a device-side wait on a peer ran out."""
         st = ctypes.c_uint32(0)

@@ -21,6 +21,7 @@ struct sb200_comm {
   bool ipc_opened[sb200::kMaxRanks];
   uint64_t seq;
   long long wait_cycles;
+  unsigned long long* trace;
 };
 
 namespace sb200 {
@@ -47,21 +48,22 @@ static CommView make_view(const sb200_comm* c) {
 }
 static size_t scratch_off(const sb200_comm* c) { return kCounterBytes + 6 * c->region_bytes; }
 
-// Standalone all-reduce: push rows of a local tensor, then the shared phases.
+// Standalone all-reduce: copy the rows of a local tensor into the heap, then the shared phases.
 template <typename T>
 __global__ void __launch_bounds__(256)
-all_reduce_kernel(const CommView c, const ReduceArgs a, const T* __restrict__ in, const int rows_per_token) {
+all_reduce_kernel(const __grid_constant__ CommView c, const __grid_constant__ ReduceArgs a, const T* __restrict__ in,
+                  const int rows_per_token) {
   // `in` is [T, rows_per_token, H]: the rows of a token are summed (fp32, rounded to T) while they are
-  // pushed -- rows_per_token = 1 for a plain all-reduce, top_k for the per-slot expert outputs of the
+  // copied -- rows_per_token = 1 for a plain all-reduce, top_k for the per-slot expert outputs of the
   // MoE layer (the reference's torch.sum(dim=1) before its all-reduce, fused_moe.py:539-543).
   constexpr int N = Vec16<T>::N;
+  trace_mark(a, 0);
   const int nvec = a.H / N;
   const size_t total = (size_t)a.T * nvec;
   const size_t stride = (size_t)gridDim.x * blockDim.x;
   for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += stride) {
     const int t = (int)(i / nvec), v = (int)(i - (size_t)t * nvec);
-    const int owner = t / a.rows_per_rank, lr = t - owner * a.rows_per_rank;
-    T* dst = (T*)(c.heap[owner] + c.partial_off[a.set]) + ((size_t)c.rank * a.rows_per_rank + lr) * a.H + (size_t)v * N;
+    T* dst = (T*)(c.heap[c.rank] + c.partial_off[a.set]) + i * N;
     if (rows_per_token == 1) {
       st16(dst, ld16(in + i * N));
     } else {
@@ -79,15 +81,15 @@ all_reduce_kernel(const CommView c, const ReduceArgs a, const T* __restrict__ in
       st16(dst, o);
     }
   }
-  fence_scope(c.world > 1);
+  trace_mark(a, 1);
   __syncthreads();
-  if (threadIdx.x < c.world) red_add_relaxed(comm_counter(c, threadIdx.x, CC_PUSH0 + a.set), 1u, c.world > 1);
-  reduce_phase<T>(c, a, blockIdx.x, gridDim.x);
-  if (a.out_copy || a.resid_copy || blockIdx.x == 0) {
-    if (finish_phase(c, a) && (a.out_copy || a.resid_copy))
-      copy_out_phase<T>(c, a, blockIdx.x * blockDim.x + threadIdx.x, gridDim.x * blockDim.x);
-  }
+  if (threadIdx.x < c.world) signal_push(c, a, threadIdx.x);  // this CTA's rows for every owner are stored
+  reduce_phase<T, kMaxVecPerLaneAllReduce>(c, a, blockIdx.x, gridDim.x);
+  trace_mark(a, 4);
+  gather_phase<T>(c, a, blockIdx.x, gridDim.x);
+  trace_mark(a, 5);
   advance_targets(c, a);
+  trace_mark(a, 6);
 }
 
 static int all_reduce_grid(int64_t T_, int64_t H, int dtype, int rows_per_rank) {
@@ -109,11 +111,13 @@ struct CallPlan {
 // rank adds to this rank's push counter during the call.
 static int plan_call(sb200_comm* c, int64_t T_, int64_t H, int dtype, const void* bias, const void* residual,
                      const void* norm_w, float eps, int write_resid_all, void* out_copy, void* resid_copy,
-                     CallPlan* p) {
+                     CallPlan* p, int max_vec_per_lane = kMaxVecPerLaneAllReduce) {
   SB_CHECK_ARG(c != nullptr, "null communication context");
   const size_t es = dtype_size(dtype);
   SB_CHECK_ARG(T_ > 0 && H > 0 && T_ <= INT32_MAX && H <= INT32_MAX, "bad shape T=%lld H=%lld", (long long)T_, (long long)H);
   SB_CHECK_ARG((H * es) % 16 == 0, "row length %lld is not a multiple of 16 bytes", (long long)H);
+  SB_CHECK_ARG(H * es <= (size_t)16 * 32 * kReduceWarps * max_vec_per_lane, "row length %lld exceeds %d bytes",
+               (long long)H, 16 * 32 * kReduceWarps * max_vec_per_lane);
   const int rpr = (int)((T_ + c->world - 1) / c->world);
   SB_CHECK_ARG((size_t)T_ * H * es <= c->region_bytes && (size_t)rpr * c->world * H * es <= c->region_bytes,
                "batch of %lld x %lld elements exceeds the context's region size (%zu bytes)", (long long)T_,
@@ -132,14 +136,13 @@ static int plan_call(sb200_comm* c, int64_t T_, int64_t H, int dtype, const void
   a.write_resid_all = write_resid_all;
   a.out_copy = out_copy; a.resid_copy = resid_copy;
   a.wait_cycles = c->wait_cycles;
+  a.trace = c->trace;
   p->cv = make_view(c);
   return SB200_OK;
 }
 
-static void commit_call(sb200_comm* c, CallPlan* p, uint32_t pushes_to_me, void** out_ptr, void** resid_ptr) {
+static void commit_call(sb200_comm* c, CallPlan* p, void** out_ptr, void** resid_ptr) {
   const int set = p->ra.set;
-  p->ra.push_per_call = pushes_to_me;
-  p->ra.done_per_call = (uint32_t)p->ra.T;
   if (out_ptr) *out_ptr = (char*)c->heap[c->rank] + p->cv.out_off[set];
   if (resid_ptr) *resid_ptr = p->ra.norm_w ? (void*)((char*)c->heap[c->rank] + p->cv.resid_off[set]) : nullptr;
   c->seq++;
@@ -160,7 +163,8 @@ static int do_all_reduce(sb200_comm* c, const void* in, int64_t T_, int64_t H, i
   if (rc) return rc;
   SB_CHECK_ARG(in && aligned16(in), "all_reduce: input must be a 16-byte aligned device pointer");
   const int grid = all_reduce_grid(T_, H, dtype, p.ra.rows_per_rank);
-  commit_call(c, &p, (uint32_t)(c->world * grid), out_ptr, resid_ptr);
+  for (int o = 0; o < c->world; ++o) p.ra.push_expected[o] = (uint32_t)grid;  // every CTA reports once per owner
+  commit_call(c, &p, out_ptr, resid_ptr);
   SB_DISPATCH_FLOAT(dtype, return (launch_all_reduce<scalar_t>(p, in, rows_per_token, grid, s)));
   return SB200_OK;
 }
@@ -264,6 +268,12 @@ extern "C" int sb200_comm_set_wait_limit(sb200_comm* c, int64_t cycles) {
   return SB200_OK;
 }
 
+extern "C" int sb200_comm_set_trace(sb200_comm* c, void* device_buffer) {
+  SB_CHECK_ARG(c, "comm_set_trace: null context");
+  c->trace = (unsigned long long*)device_buffer;
+  return SB200_OK;
+}
+
 extern "C" int sb200_comm_status(sb200_comm* c, sb200_stream_t stream, uint32_t* host_status) {
   SB_CHECK_ARG(c && host_status, "comm_status: bad arguments");
   uint32_t* w = reinterpret_cast<uint32_t*>(c->heap[c->rank]) + CC_STATUS;
@@ -321,17 +331,21 @@ extern "C" int sb200_gemm_rowpar(sb200_comm* comm, const void* x, int64_t ldx, c
                          s, out_ptr, resid_ptr);
   }
   CallPlan p;
-  int rc = plan_call(comm, T, N, dtype, bias, residual, norm_w, eps, write_resid_all, out_copy, resid_copy, &p);
+  int rc = plan_call(comm, T, N, dtype, bias, residual, norm_w, eps, write_resid_all, out_copy, resid_copy, &p,
+                     kMaxVecPerLaneGemm);
   if (rc) return rc;
   SB_CHECK_ARG(N % 8 == 0, "gemm_rowpar: output width must be a multiple of 8");
   // split-K partial tiles live in the context's scratch region (its counters stay zero between launches)
   void* ws = sb200_comm_scratch(comm);
   const GemmPlan plan = plan_gemm(EPI_PUSH, T, N, K, 0, tile_cfg, comm->region_bytes);
   SB_CHECK_ARG(plan.bn != 0, "gemm_rowpar: bad tile configuration %d", tile_cfg);
-  // pushes into this rank per call: what one rank's kernel reports for my rows, times the ranks
+  // arrivals this rank's kernel reports for each owner's rows (the arrival that completes a count
+  // sends that owner its flag)
   const int rpr = p.ra.rows_per_rank;
-  const int64_t lo = (int64_t)comm->rank * rpr, hi = (lo + rpr < T ? lo + rpr : T);  // my rows [lo, hi)
-  const uint32_t per_rank = gemm_push_increments(plan, T, lo, hi);
+  for (int o = 0; o < comm->world; ++o) {
+    const int64_t lo = (int64_t)o * rpr, hi = (lo + rpr < T ? lo + rpr : T);
+    p.ra.push_expected[o] = gemm_push_increments(plan, T, lo, hi);
+  }
   GemmArgs g = {};
   g.M = (int)T; g.N = (int)N; g.K = (int)K;
   g.head_size = 128;
@@ -341,6 +355,6 @@ extern "C" int sb200_gemm_rowpar(sb200_comm* comm, const void* x, int64_t ldx, c
   if (rc) return rc;
   rc = make_tmap_2d(&probe, dtype, w, N, K, ldw, plan.cta2 ? plan.bn / 2 : plan.bn, kBK);
   if (rc) return rc;
-  commit_call(comm, &p, (uint32_t)comm->world * per_rank, out_ptr, resid_ptr);
+  commit_call(comm, &p, out_ptr, resid_ptr);
   return run_gemm_sm100(dtype, EPI_PUSH, plan, x, ldx, w, ldw, g, ws, p.cv, p.ra, s);
 }

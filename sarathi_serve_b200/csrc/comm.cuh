@@ -1,22 +1,32 @@
 // Device-side view of the tensor-parallel communication context and the
-// reduce / broadcast phases shared by the fused row-parallel GEMM and the
+// reduce / gather phases shared by the fused row-parallel GEMM and the
 // standalone all-reduce.
 //
 // Every rank owns one "symmetric heap" with the same layout, mapped into every
-// peer (P2P over NVLink/NVSwitch).  One collective call ("epoch") runs as:
-//   push    : each rank writes its partial rows into the OWNER's heap
-//             (slot [set][src_rank]), then bumps the owner's push counter;
-//   reduce  : the owner waits for all pushes, sums the partials in fp32 (+bias,
-//             +residual), optionally RMS-normalises, and stores the finished
-//             rows into EVERY rank's output buffers, bumping their done counter;
-//   finish  : each rank waits until all rows have landed in its own buffers.
-// Row t is owned by rank t / rows_per_rank.  Buffers and counters are double
-// buffered by call parity (`set`); counters only ever grow and are compared
-// against cumulative targets that live next to them and are advanced on the
-// device at the end of each call, so nothing is reset and no per-call value
-// comes from the host (a captured CUDA graph of collectives can be replayed).
-// Two ranks can be at most one call apart because every call ends with the
-// finish wait, which needs every rank's reduce of the same call.
+// peer (P2P over NVLink/NVSwitch).  Data crosses the links only through LOADS:
+// a rank stores into its own memory and tells its peers with one flag store.
+// One collective call ("epoch") runs as:
+//   produce : each rank writes its partial [T, H] into its OWN heap; when the
+//             rows of owner o are complete it stores the call's epoch number
+//             into o's push flag for this rank;
+//   reduce  : the owner of a row waits for every rank's push flag, loads the
+//             row from every heap, sums in fp32 (+bias, +residual), optionally
+//             RMS-normalises, and stores the finished row into its own heap;
+//             when all its rows are done it stores the epoch into every peer's
+//             done flag for this rank;
+//   gather  : each rank waits for the done flags and copies the rows it does
+//             not own from their owners' heaps into its own.
+// Row t is owned by rank t / rows_per_rank.  Buffers and flags are double
+// buffered by call parity (`set`).  Remote stores carry flags only, so the
+// system-scope fence in front of a flag has nothing but local stores to wait
+// for.  The warps / CTAs of a rank count their arrivals in LOCAL counters, and
+// whoever completes a count writes the flag.  Epochs live on the device and
+// advance at the end of each call, so no per-call value comes from the host
+// and a captured CUDA graph of collectives can be replayed.
+// Two ranks can be at most one call apart: a rank that owns rows cannot finish
+// call n before every rank has produced for call n, and a buffer of parity
+// `set` is rewritten in call n+2 at the earliest, after every reader of call n
+// has been released by the flags of call n.
 // All waits are bounded; a wait that runs out sets the status word and the
 // kernel returns.
 #pragma once
@@ -27,20 +37,19 @@ namespace sb200 {
 
 constexpr int kMaxRanks = 8;
 
-// counters (uint32) at the start of each heap
+// control words (uint32) at the start of each heap; groups sit on separate 128-byte lines
 enum CommCounter {
-  CC_PUSH0 = 0,   // pushes received, set 0 / 1
-  CC_PUSH1 = 1,
-  CC_DONE0 = 2,   // finished rows received, set 0 / 1
-  CC_DONE1 = 3,
-  CC_STATUS = 4,  // first error recorded by a kernel on this rank (0 = none)
-  CC_PUSH_TGT0 = 8,   // cumulative number of pushes this rank has been promised, set 0 / 1
-  CC_PUSH_TGT1 = 9,   //   (advanced on the device by the last CTA of each collective kernel, so a
-  CC_DONE_TGT0 = 10,  //    captured CUDA graph can be replayed: no per-call host value is baked in)
-  CC_DONE_TGT1 = 11,
-  CC_EXIT_TICKET = 12,  // CTAs of the running collective kernel that have finished
-  CC_BARRIER = 16,      // [kMaxRanks] generic barrier slots
-  CC_COUNT = 64
+  CC_STATUS = 0,        // first error recorded by a kernel on this rank (0 = none)
+  CC_EXIT_TICKET = 1,   // CTAs of the running collective kernel that have finished
+  CC_EPOCH0 = 2,        // epoch number of the last completed call, set 0 / 1
+  CC_EPOCH1 = 3,
+  CC_LOCAL_DONE = 4,    // local: reduce teams of the running call that have finished their rows
+  CC_LOCAL_PUSH = 32,   // local: [kMaxRanks] arrivals of this rank's own pushes, per destination owner
+  CC_PUSH_FLAG0 = 64,   // [kMaxRanks] written by rank s: "my partial rows that you own are stored" (epoch), set 0
+  CC_PUSH_FLAG1 = 96,   //   ... set 1
+  CC_DONE_FLAG0 = 128,  // [kMaxRanks] written by rank s: "all rows I own are finished in my heap" (epoch), set 0
+  CC_DONE_FLAG1 = 160,  //   ... set 1
+  CC_COUNT = 192
 };
 
 enum CommStatusCode {
@@ -64,9 +73,8 @@ __device__ __forceinline__ uint32_t* comm_counter(const CommView& c, int r, int 
   return reinterpret_cast<uint32_t*>(c.heap[r]) + which;
 }
 
-// Memory-ordering helpers.  Counters of a multi-rank context are written by peers over NVLink and
-// need system scope; a single-rank context (tensor-parallel size 1) stays at GPU scope, which is
-// much cheaper.  Polling uses relaxed loads; one acquire fence follows the successful poll.
+// Memory-ordering helpers.  Flags of a multi-rank context are written by peers over NVLink and
+// need system scope; a single-rank context (tensor-parallel size 1) stays at GPU scope.
 __device__ __forceinline__ uint32_t ld_acquire_gpu(const uint32_t* p) {
   uint32_t v;
   asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
@@ -78,28 +86,39 @@ __device__ __forceinline__ uint32_t ld_relaxed(const uint32_t* p, bool sys) {
   else asm volatile("ld.relaxed.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
   return v;
 }
-__device__ __forceinline__ void fence_scope(bool sys) {
-  if (sys) __threadfence_system(); else __threadfence();
-}
-// Counter increment that publishes the caller's earlier stores; the CALLER has already executed
-// fence_scope() after those stores (one fence can cover several increments).
-__device__ __forceinline__ void red_add_relaxed(uint32_t* p, uint32_t v, bool sys) {
-  if (sys) asm volatile("red.relaxed.sys.global.add.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
-  else asm volatile("red.relaxed.gpu.global.add.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+__device__ __forceinline__ void st_release(uint32_t* p, uint32_t v, bool sys) {
+  if (sys) asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+  else asm volatile("st.release.gpu.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
 }
 
-// Bounded spin until *p has reached `target` (wrap-safe).  Returns false on timeout.
-__device__ __forceinline__ bool wait_counter(const uint32_t* p, uint32_t target, long long limit_cycles, bool sys) {
-  bool ok = true;
-  if ((int32_t)(ld_relaxed(p, sys) - target) < 0) {
-    const long long t0 = clock64();
-    while ((int32_t)(ld_relaxed(p, sys) - target) < 0) {
-      __nanosleep(40);
-      if (clock64() - t0 > limit_cycles) { ok = false; break; }
-    }
+// Arrival counter increment with release + acquire semantics at GPU scope: publishes what the caller
+// (and the threads it has synchronised with through a barrier) stored before, and makes what earlier
+// arrivals published visible to the caller.  Returns the old value.
+__device__ __forceinline__ uint32_t arrive_acq_rel(uint32_t* p) {
+  uint32_t old;
+  asm volatile("atom.acq_rel.gpu.global.add.u32 %0, [%1], 1;" : "=r"(old) : "l"(p) : "memory");
+  return old;
+}
+
+__device__ __forceinline__ uint32_t ld_acquire(const uint32_t* p, bool sys) {
+  uint32_t v;
+  if (sys) asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  else asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+
+// Bounded spin until the flag word at p holds `epoch`.  Polls with relaxed loads; the load that ends
+// the wait is an acquire load that reads the value the signalling rank stored with st.release, so what
+// that rank wrote before its flag is visible to this thread (and, through a following barrier, to the
+// threads it releases).  A system-scope fence costs microseconds on this machine, an acquire load
+// does not, so no fence is used on the waiting side.  Returns false on timeout.
+__device__ __forceinline__ bool wait_flag(const uint32_t* p, uint32_t epoch, long long limit_cycles, bool sys) {
+  const long long t0 = clock64();
+  while (ld_relaxed(p, sys) != epoch) {
+    __nanosleep(20);
+    if (clock64() - t0 > limit_cycles) return false;
   }
-  fence_scope(sys);  // acquire: what the counted writers stored is visible from here on
-  return ok;
+  return ld_acquire(p, sys) == epoch;
 }
 
 __device__ __forceinline__ void record_status(const CommView& c, int code) {
@@ -110,8 +129,8 @@ struct ReduceArgs {
   int T, H;               // rows of the whole batch, row length
   int rows_per_rank;      // ownership granule: owner(t) = t / rows_per_rank
   int set;                // call parity
-  uint32_t push_per_call; // increments this rank's CC_PUSH[set] receives during this call
-  uint32_t done_per_call; // increments this rank's CC_DONE[set] receives during this call (= T)
+  uint32_t push_expected[kMaxRanks];  // arrivals this rank's own kernel reports per destination owner
+                                      // (epilogue warp-tiles of the GEMM, or CTAs of the all-reduce)
   const void* bias;       // [H] or null, added after the sum (reference: layers.py:448-453)
   const void* residual;   // [T, H] local tensor or null: z = sum + residual
   const void* norm_w;     // [H] or null: also produce rms_norm(z) * norm_w
@@ -120,18 +139,49 @@ struct ReduceArgs {
   void* out_copy;         // optional local [T, H] tensor that receives the primary result
   void* resid_copy;       // optional local [T, H] tensor that receives z when norm_w != null
   long long wait_cycles;
+  unsigned long long* trace;  // optional [gridDim.x][8] nanosecond time stamps of the phases (profiling aid), or null
 };
 
-// Primary result = rms_norm(z)*w when norm_w is set, else z.  It goes to the
-// `out` region of every rank; z additionally goes to the `resid` region when a
-// norm is applied (so the caller gets both the normalised rows and the new residual).
+__device__ __forceinline__ unsigned long long global_ns() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
+// Thread 0 of every CTA records when it passed phase boundary `slot`.
+__device__ __forceinline__ void trace_mark(const ReduceArgs& a, int slot) {
+  if (a.trace && threadIdx.x == 0) a.trace[(size_t)blockIdx.x * 8 + slot] = global_ns();
+}
+
+// Epoch number of the running call on this set.
+__device__ __forceinline__ uint32_t call_epoch(const CommView& c, const ReduceArgs& a) {
+  return *(volatile uint32_t*)comm_counter(c, c.rank, CC_EPOCH0 + a.set) + 1u;
+}
+
+// Called by ONE thread after the stores it and its group made to this rank's partial region and a
+// barrier (__syncwarp / __syncthreads) of that group: counts the arrival locally with a release
+// increment (which covers the group's stores); the arrival that completes this rank's share of
+// `owner`'s rows tells the owner with a single remote release store.
+__device__ __forceinline__ void signal_push(const CommView& c, const ReduceArgs& a, int owner) {
+  const uint32_t n = arrive_acq_rel(comm_counter(c, c.rank, CC_LOCAL_PUSH + owner)) + 1u;
+  if (n == a.push_expected[owner])
+    st_release(comm_counter(c, owner, (a.set ? CC_PUSH_FLAG1 : CC_PUSH_FLAG0) + c.rank), call_epoch(c, a), c.world > 1);
+}
+
+// Primary result = rms_norm(z)*w when norm_w is set, else z, kept in the `out` region; z is
+// additionally kept in the `resid` region when a norm is applied (so the caller gets both the
+// normalised rows and the new residual).
 //
-// A row is handled by a team of 1, 2, 4 or 8 warps of one CTA (as many as the grid can spare for
-// the rows this rank owns); a lane works on batches of kRB 16-byte vectors whose loads are issued
-// together, so a row costs a few memory round trips.  The teams' partial sums of squares meet in
+// A row is handled by a team of 1, 2, 4 or 8 warps of one CTA: as many as the grid can spare for
+// the rows this rank owns, and at least as many as it takes to hold the row in registers (VPL
+// 16-byte vectors per lane).  The loads of a row -- its residual and the partials of up
+// to SB source ranks -- are issued together, so a row costs about one memory round trip per SB
+// sources; z stays in registers for the normalisation.  The teams' partial sums of squares meet in
 // shared memory through named barriers.
-constexpr int kRB = 4;
-constexpr int kReduceWarps = 8;  // warps of a CTA that take part (warps 0..7)
+constexpr int kReduceWarps = 8;     // warps of a CTA that take part (warps 0..7)
+// A row has at most 32 * kReduceWarps * MAXVPL 16-byte vectors: MAXVPL = 4 (16 KiB rows) inside the GEMM
+// kernel, whose 320 threads leave 168 registers each, 8 (32 KiB rows) in the standalone all-reduce.
+constexpr int kMaxVecPerLaneGemm = 4;
+constexpr int kMaxVecPerLaneAllReduce = 8;
 
 template <typename T>
 __device__ __forceinline__ Vec16<T> ldcg16(const T* p) {
@@ -144,108 +194,81 @@ __device__ __forceinline__ void team_barrier(int id, int threads) {
   asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(threads) : "memory");
 }
 
-template <typename T>
-__device__ void reduce_phase(const CommView& c, const ReduceArgs& a, int cta, int num_ctas) {
+template <typename T, int VPL>
+__device__ __forceinline__ void reduce_rows(const CommView& c, const ReduceArgs& a, int gteam, int num_teams, int tw,
+                                            int team, int wt, int lane, int warp, int nrows, float* s_ss) {
   constexpr int N = Vec16<T>::N;
-  __shared__ float s_ss[kReduceWarps];
-  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  if (warp >= kReduceWarps) return;
-  const bool sys = c.world > 1;
-  const int row0 = c.rank * a.rows_per_rank;
-  const int nrows = max(0, min(a.rows_per_rank, a.T - row0));
-  // team width: as many warps per row as the grid can spare (power of two, at most a CTA's share)
-  int tw = 1;
-  while (tw < kReduceWarps && (long long)num_ctas * kReduceWarps >= (long long)nrows * tw * 2) tw <<= 1;
-  const int teams_per_cta = kReduceWarps / tw;
-  const int team = warp / tw, wt = warp - team * tw;
-  const int gteam = cta * teams_per_cta + team, num_teams = num_ctas * teams_per_cta;
-  if (gteam >= nrows) return;  // no row for this team: nothing to wait for either
-  {
-    bool ok = true;
-    if (lane == 0) {
-      const uint32_t target = *(volatile uint32_t*)comm_counter(c, c.rank, CC_PUSH_TGT0 + a.set) + a.push_per_call;
-      ok = wait_counter(comm_counter(c, c.rank, CC_PUSH0 + a.set), target, a.wait_cycles, sys);
-    }
-    ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
-    if (!ok && lane == 0) record_status(c, CS_TIMEOUT_PUSH);
-    // (a warp that timed out still walks its rows so that its team mates are not left at a barrier;
-    //  the status word tells the host that the results are not to be used)
-  }
+  constexpr int SB = 8 / VPL;  // source ranks whose loads are issued together (8 vectors in flight per lane)
   const int nvec = a.H / N;
+  const int row0 = c.rank * a.rows_per_rank;
   const T* bias = (const T*)a.bias;
   const T* resid = (const T*)a.residual;
   const T* nw = (const T*)a.norm_w;
-  const T* my_partial = (const T*)(c.heap[c.rank] + c.partial_off[a.set]);
-  const size_t src_stride = (size_t)a.rows_per_rank * a.H;  // elements between the slots of consecutive source ranks
-  const int vstep = 32 * tw;                                // vectors a team covers per step
+  const int vstep = 32 * tw, vbase = wt * 32 + lane;
   for (int lr = gteam; lr < nrows; lr += num_teams) {
-    const int t = row0 + lr;
-    const size_t row_off = (size_t)t * a.H;
-    float ss = 0.f;
-    // pass 1: z = round(sum_src partial + bias + residual); z is kept in the local resid/out region
-    T* zrow_local = (T*)(c.heap[c.rank] + (nw ? c.resid_off[a.set] : c.out_off[a.set])) + row_off;
-    for (int v0 = wt * 32 + lane; v0 < nvec; v0 += vstep * kRB) {
-      float acc[kRB][N];
+    const size_t row_off = (size_t)(row0 + lr) * a.H;
+    float acc[VPL][N];
+    Vec16<T> rv[VPL];
 #pragma unroll
-      for (int b = 0; b < kRB; ++b)
+    for (int b = 0; b < VPL; ++b) {
 #pragma unroll
-        for (int j = 0; j < N; ++j) acc[b][j] = 0.f;
-      Vec16<T> bv[kRB], rv[kRB];
+      for (int j = 0; j < N; ++j) acc[b][j] = 0.f;
+      const int v = vbase + vstep * b;
+      if (resid && v < nvec) rv[b] = ld16(resid + row_off + (size_t)v * N);
+    }
+    for (int s0 = 0; s0 < c.world; s0 += SB) {
+      Vec16<T> x[SB][VPL];
 #pragma unroll
-      for (int b = 0; b < kRB; ++b) {
-        const int v = v0 + vstep * b;
-        if (v < nvec) {
-          if (bias) bv[b] = ld16(bias + (size_t)v * N);
-          if (resid) rv[b] = ld16(resid + row_off + (size_t)v * N);
-        }
-      }
-      for (int s = 0; s < c.world; ++s) {
-        const T* p = my_partial + (size_t)s * src_stride + (size_t)lr * a.H;
-        Vec16<T> x[kRB];
+      for (int i = 0; i < SB; ++i)
+        if (s0 + i < c.world) {
+          const T* p = (const T*)(c.heap[s0 + i] + c.partial_off[a.set]) + row_off;
 #pragma unroll
-        for (int b = 0; b < kRB; ++b) {
-          const int v = v0 + vstep * b;
-          if (v < nvec) x[b] = ldcg16(p + (size_t)v * N);
-        }
-#pragma unroll
-        for (int b = 0; b < kRB; ++b)
-          if (v0 + vstep * b < nvec) {
-#pragma unroll
-            for (int j = 0; j < N; ++j) acc[b][j] += DT<T>::to_f(x[b].v[j]);
+          for (int b = 0; b < VPL; ++b) {
+            const int v = vbase + vstep * b;
+            if (v < nvec) x[i][b] = ldcg16(p + (size_t)v * N);
           }
-      }
-#pragma unroll
-      for (int b = 0; b < kRB; ++b) {
-        const int v = v0 + vstep * b;
-        if (v >= nvec) continue;
-        Vec16<T> z;
-#pragma unroll
-        for (int j = 0; j < N; ++j) {
-          float f = acc[b][j];
-          if (bias) f = rt<T>(rt<T>(f) + DT<T>::to_f(bv[b].v[j]));
-          if (resid) f = rt<T>(DT<T>::to_f(rv[b].v[j]) + rt<T>(f));
-          z.v[j] = DT<T>::from_f(f);
-          const float zf = DT<T>::to_f(z.v[j]);
-          ss += zf * zf;
         }
-        st16(zrow_local + (size_t)v * N, z);
-        if (nw) {
-          if (a.resid_copy) st16((T*)a.resid_copy + row_off + (size_t)v * N, z);
-          if (a.write_resid_all)
-            for (int d = 1; d < c.world; ++d) {
-              const int dst = (c.rank + d) % c.world;
-              st16((T*)(c.heap[dst] + c.resid_off[a.set]) + row_off + (size_t)v * N, z);
+#pragma unroll
+      for (int i = 0; i < SB; ++i)
+        if (s0 + i < c.world) {
+#pragma unroll
+          for (int b = 0; b < VPL; ++b)
+            if (vbase + vstep * b < nvec) {
+#pragma unroll
+              for (int j = 0; j < N; ++j) acc[b][j] += DT<T>::to_f(x[i][b].v[j]);
             }
-        } else {
-          if (a.out_copy) st16((T*)a.out_copy + row_off + (size_t)v * N, z);
-          for (int d = 1; d < c.world; ++d) {
-            const int dst = (c.rank + d) % c.world;
-            st16((T*)(c.heap[dst] + c.out_off[a.set]) + row_off + (size_t)v * N, z);
-          }
         }
+    }
+    // z = round(round(sum + bias) + residual)
+    Vec16<T> z[VPL];
+    float ss = 0.f;
+    T* zrow = (T*)(c.heap[c.rank] + (nw ? c.resid_off[a.set] : c.out_off[a.set])) + row_off;
+    T* zcopy = (T*)(nw ? a.resid_copy : a.out_copy);
+#pragma unroll
+    for (int b = 0; b < VPL; ++b) {
+      const int v = vbase + vstep * b;
+      if (v >= nvec) continue;
+      Vec16<T> bv;
+      if (bias) bv = ld16(bias + (size_t)v * N);
+#pragma unroll
+      for (int j = 0; j < N; ++j) {
+        float f = acc[b][j];
+        if (bias) f = rt<T>(rt<T>(f) + DT<T>::to_f(bv.v[j]));
+        if (resid) f = rt<T>(DT<T>::to_f(rv[b].v[j]) + rt<T>(f));
+        z[b].v[j] = DT<T>::from_f(f);
+        const float zf = DT<T>::to_f(z[b].v[j]);
+        ss += zf * zf;
       }
+      st16(zrow + (size_t)v * N, z[b]);
+      if (zcopy) st16(zcopy + row_off + (size_t)v * N, z[b]);
     }
     if (nw) {
+      Vec16<T> w[VPL];
+#pragma unroll
+      for (int b = 0; b < VPL; ++b) {
+        const int v = vbase + vstep * b;
+        if (v < nvec) w[b] = ld16(nw + (size_t)v * N);
+      }
       ss = warp_sum(ss);
       if (tw > 1) {
         if (lane == 0) s_ss[warp] = ss;
@@ -255,86 +278,160 @@ __device__ void reduce_phase(const CommView& c, const ReduceArgs& a, int cta, in
         team_barrier(1 + team, 32 * tw);  // everyone has read before the next row overwrites
       }
       const float inv = rsqrtf(ss / (float)a.H + a.eps);
-      __syncwarp();
-      // pass 2: y = round(z * inv) * w, to every rank (each lane re-reads the vectors it wrote itself)
-      for (int v0 = wt * 32 + lane; v0 < nvec; v0 += vstep * kRB) {
-        Vec16<T> z[kRB], w[kRB];
+      T* yrow = (T*)(c.heap[c.rank] + c.out_off[a.set]) + row_off;
 #pragma unroll
-        for (int b = 0; b < kRB; ++b) {
-          const int v = v0 + vstep * b;
-          if (v < nvec) {
-            z[b] = ld16(zrow_local + (size_t)v * N);
-            w[b] = ld16(nw + (size_t)v * N);
-          }
+      for (int b = 0; b < VPL; ++b) {
+        const int v = vbase + vstep * b;
+        if (v >= nvec) continue;
+        Vec16<T> y;
+#pragma unroll
+        for (int j = 0; j < N; ++j)
+          y.v[j] = DT<T>::from_f(rt<T>(DT<T>::to_f(z[b].v[j]) * inv) * DT<T>::to_f(w[b].v[j]));
+        st16(yrow + (size_t)v * N, y);
+        if (a.out_copy) st16((T*)a.out_copy + row_off + (size_t)v * N, y);
+      }
+    }
+  }
+}
+
+template <typename T, int MAXVPL>
+__device__ void reduce_phase(const CommView& c, const ReduceArgs& a, int cta, int num_ctas) {
+  constexpr int N = Vec16<T>::N;
+  __shared__ float s_ss[kReduceWarps];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  if (warp >= kReduceWarps) return;
+  const bool sys = c.world > 1;
+  const int row0 = c.rank * a.rows_per_rank;
+  const int nrows = max(0, min(a.rows_per_rank, a.T - row0));
+  if (nrows == 0) return;  // owns nothing: nobody waits for this rank's done flag
+  const int nvec = a.H / N;
+  // team width: what the row needs to fit in registers, then as many warps as the grid can spare
+  int tw = 1;
+  while (tw < kReduceWarps && nvec > 32 * tw * MAXVPL) tw <<= 1;
+  while (tw < kReduceWarps && 32 * tw < nvec && (long long)num_ctas * kReduceWarps >= (long long)nrows * tw * 2) tw <<= 1;
+  const int vpl = (nvec + 32 * tw - 1) / (32 * tw);
+  const int teams_per_cta = kReduceWarps / tw;
+  const int team = warp / tw, wt = warp - team * tw;
+  const int gteam = cta * teams_per_cta + team, num_teams = num_ctas * teams_per_cta;
+  const uint32_t epoch = call_epoch(c, a);
+  const int teams_with_rows = min(num_teams, nrows);
+  if (cta * teams_per_cta >= nrows) return;  // no row for any team of this CTA: nothing to wait for either
+  {
+    // lanes 0..world-1 of warp 0 wait for one source rank each; the other reduce warps wait at a barrier
+    trace_mark(a, 2);
+    if (warp == 0) {
+      bool ok = true;
+      if (lane < c.world)
+        ok = wait_flag(comm_counter(c, c.rank, (a.set ? CC_PUSH_FLAG1 : CC_PUSH_FLAG0) + lane), epoch, a.wait_cycles, sys);
+      ok = __all_sync(0xffffffffu, ok);
+      if (lane == 0 && !ok) record_status(c, CS_TIMEOUT_PUSH);
+    }
+    team_barrier(15, 32 * kReduceWarps);
+    trace_mark(a, 3);
+    // (after a timeout the warps still walk their rows -- the status word tells the host that the
+    //  results are not to be used -- so that every rank keeps counting the same arrivals)
+  }
+  if (gteam >= nrows) return;
+  if (vpl <= 1) reduce_rows<T, 1>(c, a, gteam, num_teams, tw, team, wt, lane, warp, nrows, s_ss);
+  else if (vpl <= 2) reduce_rows<T, 2>(c, a, gteam, num_teams, tw, team, wt, lane, warp, nrows, s_ss);
+  else if (vpl <= 4 || MAXVPL <= 4) reduce_rows<T, 4>(c, a, gteam, num_teams, tw, team, wt, lane, warp, nrows, s_ss);
+  else reduce_rows<T, (MAXVPL > 4 ? 8 : 4)>(c, a, gteam, num_teams, tw, team, wt, lane, warp, nrows, s_ss);
+  // publish: the team is counted locally (a release increment after the team's barrier covers the
+  // stores of all its warps), and the team that completes the count tells every peer, with one remote
+  // release store each, that this rank's rows are done
+  if (tw > 1) team_barrier(1 + team, 32 * tw); else __syncwarp();
+  if (wt == 0) {
+    uint32_t n = 0;
+    if (lane == 0) n = arrive_acq_rel(comm_counter(c, c.rank, CC_LOCAL_DONE)) + 1u;
+    n = __shfl_sync(0xffffffffu, n, 0);
+    if (n == (uint32_t)teams_with_rows && lane < c.world && lane != c.rank)
+      st_release(comm_counter(c, lane, (a.set ? CC_DONE_FLAG1 : CC_DONE_FLAG0) + c.rank), epoch, sys);
+  }
+}
+
+// Bring the rows other ranks own into this rank's heap (and the caller's tensors).  The CTAs split
+// into one group per peer; a group waits for its peer's done flag only, then copies that peer's rows
+// with several loads in flight per thread.  Called by all threads of every CTA.
+template <typename T>
+__device__ void gather_phase(const CommView& c, const ReduceArgs& a, int cta, int num_ctas) {
+  constexpr int N = Vec16<T>::N;
+  constexpr int U = 4;
+  __shared__ int s_ok;
+  const int others = c.world - 1;
+  if (others == 0) return;
+  const int nvec = a.H / N;
+  const uint32_t epoch = call_epoch(c, a);
+  const int groups = min(others, num_ctas);
+  const int group = cta % groups, rank_in_group = cta / groups;
+  const int ctas_in_group = (num_ctas - group + groups - 1) / groups;
+  const bool pull_resid = a.norm_w != nullptr && a.write_resid_all;
+  for (int j = group; j < others; j += groups) {
+    const int o = (c.rank + 1 + j) % c.world;
+    const int r0 = o * a.rows_per_rank;
+    const int n = min(a.rows_per_rank, a.T - r0);
+    if (n <= 0) continue;
+    if (threadIdx.x == 0) {
+      const bool ok = wait_flag(comm_counter(c, c.rank, (a.set ? CC_DONE_FLAG1 : CC_DONE_FLAG0) + o), epoch,
+                                a.wait_cycles, true);
+      if (!ok) record_status(c, CS_TIMEOUT_DONE);
+      s_ok = ok ? 1 : 0;
+    }
+    __syncthreads();
+    const bool ok = s_ok != 0;
+    __syncthreads();  // s_ok may be rewritten for the next peer
+    if (!ok) return;
+    const size_t base = (size_t)r0 * a.H;
+    const T* src_out = (const T*)(c.heap[o] + c.out_off[a.set]) + base;
+    const T* src_res = (const T*)(c.heap[o] + c.resid_off[a.set]) + base;
+    T* dst_out = (T*)(c.heap[c.rank] + c.out_off[a.set]) + base;
+    T* dst_res = (T*)(c.heap[c.rank] + c.resid_off[a.set]) + base;
+    T* cp_out = a.out_copy ? (T*)a.out_copy + base : nullptr;
+    T* cp_res = (pull_resid && a.resid_copy) ? (T*)a.resid_copy + base : nullptr;
+    const size_t total = (size_t)n * nvec;
+    const size_t stride = (size_t)ctas_in_group * blockDim.x;
+    for (size_t i0 = (size_t)rank_in_group * blockDim.x + threadIdx.x; i0 < total; i0 += stride * U) {
+      Vec16<T> y[U], z[U];
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        const size_t i = i0 + stride * u;
+        if (i < total) {
+          y[u] = ldcg16(src_out + i * N);
+          if (pull_resid) z[u] = ldcg16(src_res + i * N);
         }
+      }
 #pragma unroll
-        for (int b = 0; b < kRB; ++b) {
-          const int v = v0 + vstep * b;
-          if (v >= nvec) continue;
-          Vec16<T> y;
-#pragma unroll
-          for (int j = 0; j < N; ++j)
-            y.v[j] = DT<T>::from_f(rt<T>(DT<T>::to_f(z[b].v[j]) * inv) * DT<T>::to_f(w[b].v[j]));
-          if (a.out_copy) st16((T*)a.out_copy + row_off + (size_t)v * N, y);
-          for (int d = 0; d < c.world; ++d) {
-            const int dst = (c.rank + d) % c.world;
-            st16((T*)(c.heap[dst] + c.out_off[a.set]) + row_off + (size_t)v * N, y);
+      for (int u = 0; u < U; ++u) {
+        const size_t i = i0 + stride * u;
+        if (i < total) {
+          st16(dst_out + i * N, y[u]);
+          if (cp_out) st16(cp_out + i * N, y[u]);
+          if (pull_resid) {
+            st16(dst_res + i * N, z[u]);
+            if (cp_res) st16(cp_res + i * N, z[u]);
           }
         }
       }
     }
-    // publish the row: every warp of the team makes its stores visible, then the row is counted once on every rank
-    fence_scope(sys);
-    if (tw > 1) team_barrier(1 + team, 32 * tw); else __syncwarp();
-    if (wt == 0 && lane < c.world) red_add_relaxed(comm_counter(c, lane, CC_DONE0 + a.set), 1u, sys);
   }
-}
-
-// Wait until every row of this call has landed in this rank's buffers; one thread per CTA waits.
-__device__ __forceinline__ bool finish_phase(const CommView& c, const ReduceArgs& a) {
-  __shared__ int s_ok;
-  if (threadIdx.x == 0) {
-    const uint32_t target = *(volatile uint32_t*)comm_counter(c, c.rank, CC_DONE_TGT0 + a.set) + a.done_per_call;
-    const bool ok = wait_counter(comm_counter(c, c.rank, CC_DONE0 + a.set), target, a.wait_cycles, c.world > 1);
-    if (!ok) record_status(c, CS_TIMEOUT_DONE);
-    s_ok = ok ? 1 : 0;
-  }
-  __syncthreads();
-  return s_ok != 0;
 }
 
 // Last step of every collective kernel, called by all threads of every CTA after their phases:
-// the last CTA to get here advances the cumulative targets of this call's set.  Every CTA has
-// read the old targets by then (it reads them before it can finish), and the next collective on
-// this set is a later kernel on the same stream.
+// the last CTA to get here closes the call -- it advances this set's epoch and clears the local
+// arrival counters.  Every CTA has read the epoch by then (it reads it before it can finish), the
+// local counters are only touched by this rank's own kernels, and the next collective on this
+// context is a later kernel on the same stream.
 __device__ __forceinline__ void advance_targets(const CommView& c, const ReduceArgs& a) {
   __syncthreads();
   if (threadIdx.x == 0) {
     __threadfence();
     uint32_t* ticket = comm_counter(c, c.rank, CC_EXIT_TICKET);
     if (atomicAdd(ticket, 1u) == gridDim.x - 1) {
-      *(volatile uint32_t*)comm_counter(c, c.rank, CC_PUSH_TGT0 + a.set) += a.push_per_call;
-      *(volatile uint32_t*)comm_counter(c, c.rank, CC_DONE_TGT0 + a.set) += a.done_per_call;
+      *(volatile uint32_t*)comm_counter(c, c.rank, CC_EPOCH0 + a.set) += 1u;
+      for (int i = 0; i < kMaxRanks; ++i) *(volatile uint32_t*)comm_counter(c, c.rank, CC_LOCAL_PUSH + i) = 0u;
+      *(volatile uint32_t*)comm_counter(c, c.rank, CC_LOCAL_DONE) = 0u;
       *(volatile uint32_t*)ticket = 0;
       __threadfence();
     }
-  }
-}
-
-// Copy rows owned by OTHER ranks from the local heap regions into the caller's tensors.
-template <typename T>
-__device__ void copy_out_phase(const CommView& c, const ReduceArgs& a, int tid_global, int nthreads_global) {
-  constexpr int N = Vec16<T>::N;
-  const int nvec = a.H / N;
-  const int row0 = c.rank * a.rows_per_rank, row1 = min(a.T, row0 + a.rows_per_rank);
-  const size_t total = (size_t)a.T * nvec;
-  const T* src_out = (const T*)(c.heap[c.rank] + c.out_off[a.set]);
-  const T* src_res = (const T*)(c.heap[c.rank] + c.resid_off[a.set]);
-  for (size_t i = tid_global; i < total; i += nthreads_global) {
-    const int t = (int)(i / nvec);
-    if (t >= row0 && t < row1) continue;  // own rows were written directly by reduce_phase
-    if (a.out_copy) st16((T*)a.out_copy + i * N, ld16(src_out + i * N));
-    if (a.resid_copy && a.norm_w && a.write_resid_all) st16((T*)a.resid_copy + i * N, ld16(src_res + i * N));
   }
 }
 

@@ -30,9 +30,9 @@
 //   EPI_STORE    out = acc (+ bias)
 //   EPI_ROTARY   qkv projection: rotary embedding applied to the q and k heads
 //   EPI_SILU_MUL gate_up projection: out[:, j] = silu(gate_j) * up_j
-//   EPI_PUSH     row-parallel projection: partial rows go to the owner rank's
-//                reduce slots; the reduce / residual / norm / broadcast phases of
-//                comm.cuh run in the same kernel after the tiles.
+//   EPI_PUSH     row-parallel projection: partial rows go to this rank's heap;
+//                the reduce / residual / norm / gather phases of comm.cuh run in
+//                the same kernel after the tiles.
 //   EPI_MOE_SCATTER  second expert GEMM: row r of the expert-sorted activations is scaled by its
 //                routed weight and stored at its (token, k) slot.
 // Grouped (mixture-of-experts) mode: when `expert_ids` is set, the rows of A are the
@@ -372,11 +372,8 @@ __device__ __forceinline__ RowCtx<T> make_row_ctx(const GemmArgs& g, const CommV
     rc.vec_ok = ((g.ldo & 7) == 0) && aligned16(g.out);
     if (rc.row_ok) rc.scale = g.topk_w[slot];
   } else if constexpr (EPI == EPI_PUSH) {
-    const int owner = rc.row_ok ? gm / red.rows_per_rank : 0;
-    const int lr = gm - owner * red.rows_per_rank;
-    rc.out_row = rc.row_ok ? reinterpret_cast<T*>(comm.heap[owner] + comm.partial_off[red.set]) +
-                                 ((size_t)comm.rank * red.rows_per_rank + lr) * (size_t)g.N
-                           : nullptr;
+    // the partial [T, N] of this rank stays in its own heap; the owners of the rows come and read it
+    rc.out_row = reinterpret_cast<T*>(comm.heap[comm.rank] + comm.partial_off[red.set]) + (size_t)gm * (size_t)g.N;
     rc.vec_ok = (g.N & 7) == 0;
   } else {
     rc.out_row = reinterpret_cast<T*>(g.out) + (size_t)gm * g.ldo;
@@ -397,7 +394,8 @@ __device__ __forceinline__ RowCtx<T> make_row_ctx(const GemmArgs& g, const CommV
 template <typename T, int EPI, bool CTA2, int MI>
 __global__ void __launch_bounds__(kGemmThreads, 1)
 gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
-                  const GemmArgs g, const CommView comm, const ReduceArgs red) {
+                  const __grid_constant__ GemmArgs g, const __grid_constant__ CommView comm,
+                  const __grid_constant__ ReduceArgs red) {
   constexpr uint32_t kTmemCols = 512;
   const int BN = g.bn;  // (MI is a template parameter: the MMA issue loop must be fully unrolled)
   const int BM = (CTA2 ? 256 : 128) * MI;        // rows of a tile
@@ -423,6 +421,7 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  if constexpr (EPI == EPI_PUSH) trace_mark(red, 0);
   // this unit's work items
   Sched sc;
   sc.G = num_units_grid;
@@ -501,6 +500,8 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
               ptx::tma_load_2d_pair(sb, &tmap_b, bar, kb * kBK, b_row0 + (int)cta_rank * (g.N / 2) + nt * (BN / 2));
             else
               ptx::tma_load_2d_pair(sb, &tmap_b, bar, kb * kBK, b_row0 + nt * BN + (int)cta_rank * (BN / 2));
+          } else if (g.debug & 8) {
+            ptx::mbar_arrive(&full_bar[stage]);  // profiling: no loads, the MMAs run on whatever the stage holds
           } else {
             ptx::mbar_expect_tx(&full_bar[stage], (uint32_t)stage_bytes);
 #pragma unroll
@@ -549,6 +550,7 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
             for (int a = 0; a < MI; ++a) {
               const uint64_t da = ptx::make_smem_desc_sw128(sa + a * (128 * kBK * 2));
               if (CTA2) ptx::umma_f16_pair(d_tmem + (uint32_t)(a * BN), da + (uint64_t)(k * 2), db + (uint64_t)(k * 2), idesc, acc);
+              else if (g.debug & 16) {}  // profiling: loads only
               else ptx::umma_f16(d_tmem + (uint32_t)(a * BN), da + (uint64_t)(k * 2), db + (uint64_t)(k * 2), idesc, acc);
             }
           }
@@ -654,17 +656,15 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
 
       if constexpr (EPI == EPI_PUSH) {
         // Publish this warp's rows to their owner(s): the stores of all lanes first, then one
-        // release-increment per owner.  Exactly one epilogue warp per (tile, slot) gets here with
+        // arrival per owner (the arrival that completes an owner's count sends the flag).  Exactly one epilogue warp per (tile, slot) gets here with
         // finished_here set for a whole tile and S of them (one per part) for a tile cut along K, so
         // the host can count the increments per (tile, slot, owner of the slot's rows).
         if (finished_here) {
-          fence_scope(comm.world > 1);
           __syncwarp();
           if (lane == 0) {
             const int r_lo = mt * BM + row_in_tile - lane, r_hi = min(g.M, r_lo + 32) - 1;
             if (r_hi >= r_lo)
-              for (int o = r_lo / red.rows_per_rank; o <= r_hi / red.rows_per_rank; ++o)
-                red_add_relaxed(comm_counter(comm, o, CC_PUSH0 + red.set), 1u, comm.world > 1);
+              for (int o = r_lo / red.rows_per_rank; o <= r_hi / red.rows_per_rank; ++o) signal_push(comm, red, o);
           }
         }
       }
@@ -688,12 +688,13 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
   }
 
   if constexpr (EPI == EPI_PUSH) {
-    reduce_phase<T>(comm, red, blockIdx.x, gridDim.x);
-    if (red.out_copy || red.resid_copy || blockIdx.x == 0) {
-      if (finish_phase(comm, red) && (red.out_copy || red.resid_copy))
-        copy_out_phase<T>(comm, red, blockIdx.x * kGemmThreads + threadIdx.x, gridDim.x * kGemmThreads);
-    }
+    trace_mark(red, 1);
+    reduce_phase<T, kMaxVecPerLaneGemm>(comm, red, blockIdx.x, gridDim.x);
+    trace_mark(red, 4);
+    gather_phase<T>(comm, red, blockIdx.x, gridDim.x);
+    trace_mark(red, 5);
     advance_targets(comm, red);
+    trace_mark(red, 6);
   }
 }
 

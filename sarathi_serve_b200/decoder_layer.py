@@ -123,8 +123,10 @@ class LlamaDecoderLayer(nn.Module):
         sa = self.self_attn
         q, k, v = sa.qkv_rotary(positions, normed)
         attn_out = attn.forward(q, k, v, layer_cache_idx, sa.scaling, sa.layer_id)
+        # the mid-layer residual is only read by the down projection's tail, which touches the rows this
+        # rank owns: they need not be gathered on every rank
         h, resid = sa.o_proj.forward_fused(attn_out, residual, self.post_attention_layernorm.weight.data,
-                                           self.post_attention_layernorm.variance_epsilon)
+                                           self.post_attention_layernorm.variance_epsilon, resid_everywhere=False)
         act = self.mlp.gate_up_proj.forward_silu_mul(h)
         return self.mlp.down_proj.forward_fused(act, resid, next_norm_weight, next_eps, out=out)
 

@@ -133,66 +133,85 @@ def test_two_rank_gloo_groups_and_distributed_oracle():
     mp.spawn(_gloo_worker, args=(2, 29731, None), nprocs=2)
 
 
-# ------------------------------------------- host model of the counter protocol
+# --------------------------------------------- host model of the flag protocol
 class _Rank:
-    """Counters of one rank's heap (monotonic, compared against per-call targets)."""
+    """Control words of one rank's heap: per-source flags (written by peers) and local arrival counters."""
 
-    def __init__(self):
-        self.push = [0, 0]
-        self.done = [0, 0]
+    def __init__(self, world):
+        self.push_flag = [[0] * world, [0] * world]
+        self.done_flag = [[0] * world, [0] * world]
+        self.local_push = [0] * world
+        self.local_done = 0
+        self.epoch = [0, 0]
         self.lock = threading.Lock()
 
 
-def _wait(get, target, limit_s):
+def _wait(get, limit_s):
     t0 = time.perf_counter()
-    while get() < target:
+    while not get():
         if time.perf_counter() - t0 > limit_s:
             return False
         time.sleep(0.0005)
     return True
 
 
-def _run_protocol(world, calls, absent=None, limit_s=0.3):
-    """Each thread = one rank running `calls` collectives: push to every owner, wait for
-    its own pushes, 'reduce', signal done to everyone, wait for all rows.  Returns statuses."""
-    ranks = [_Rank() for _ in range(world)]
+def _run_protocol(world, calls, absent=None, limit_s=0.3, workers=3):
+    """Each rank = `workers` threads (its CTAs) running `calls` collectives with the device protocol:
+    a worker counts its arrival per owner locally, the arrival that completes the count stores the
+    epoch into the owner's flag; the owner waits for every source's flag, 'reduces', and the last of
+    its workers stores the done flag on every rank; everybody waits for every done flag; the last
+    worker to leave closes the call (epoch += 1, local counters cleared).  Returns per-rank status."""
+    ranks = [_Rank(world) for _ in range(world)]
     status = [0] * world
-    T = 16
-    rows = T // world
+    barriers = [threading.Barrier(workers) for _ in range(world)]
 
-    def body(r):
-        push_total, done_total = [0, 0], [0, 0]
+    def body(r, w):
+        me = ranks[r]
         for c in range(calls):
             s = c & 1
             if absent == (r, c):
-                return  # this rank never launches call c
-            for o in range(world):  # push phase
-                with ranks[o].lock:
-                    ranks[o].push[s] += 1
-            push_total[s] += world
-            done_total[s] += T
-            if not _wait(lambda: ranks[r].push[s], push_total[s], limit_s):
-                status[r] = 2
                 return
-            for o in range(world):  # reduce + broadcast: one count per owned row on every rank
-                with ranks[o].lock:
-                    ranks[o].done[s] += rows
-            if not _wait(lambda: ranks[r].done[s], done_total[s], limit_s):
+            epoch = me.epoch[s] + 1
+            for o in range(world):  # push phase: this worker's share for every owner
+                with me.lock:
+                    me.local_push[o] += 1
+                    last = me.local_push[o] == workers
+                if last:
+                    ranks[o].push_flag[s][r] = epoch
+            ok = _wait(lambda: all(f == epoch for f in me.push_flag[s]), limit_s)
+            if not ok:
+                status[r] = 2
+            with me.lock:  # reduce done: count locally, last worker tells everyone
+                me.local_done += 1
+                last = me.local_done == workers
+            if last:
+                for o in range(world):
+                    ranks[o].done_flag[s][r] = epoch
+            if ok and not _wait(lambda: all(f == epoch for f in me.done_flag[s]), limit_s):
                 status[r] = 3
+            try:
+                if barriers[r].wait(timeout=5) == 0:  # "last CTA": close the call
+                    me.epoch[s] = epoch
+                    me.local_push = [0] * world
+                    me.local_done = 0
+                barriers[r].wait(timeout=5)
+            except threading.BrokenBarrierError:
+                return
+            if status[r]:
                 return
 
-    th = [threading.Thread(target=body, args=(r,)) for r in range(world)]
+    th = [threading.Thread(target=body, args=(r, w)) for r in range(world) for w in range(workers)]
     [t.start() for t in th]
     [t.join() for t in th]
     return status
 
 
-def test_counter_protocol_completes_with_skewed_ranks():
+def test_flag_protocol_completes_with_skewed_ranks():
     assert _run_protocol(4, 25) == [0, 0, 0, 0]
     assert _run_protocol(2, 40) == [0, 0]
 
 
-def test_counter_protocol_reports_a_lost_rank_instead_of_hanging():
-    st = _run_protocol(4, 6, absent=(2, 3))
+def test_flag_protocol_reports_a_lost_rank_instead_of_hanging():
+    st = _run_protocol(4, 6, absent=(2, 3), workers=1)
     assert st[2] == 0  # the absent rank just stops
-    assert all(s in (2, 3) for i, s in enumerate(st) if i != 2), st
+    assert all(s_ in (2, 3) for i, s_ in enumerate(st) if i != 2), st
