@@ -38,6 +38,11 @@ UNIT = "tokens/s"
 L2_BYTES = 126 << 20
 
 
+# dram__bytes_read.sum + dram__bytes_write.sum of one gate_up launch at TP=1 (ncu --set full capture,
+# summarised in profiles/gemm_gate_up_silu_tp1_ncu_full.md)
+GATE_UP_TP1_DRAM_BYTES = 254.2e6
+
+
 def parse():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -46,6 +51,8 @@ def parse():
     ap.add_argument("--impl", default="native", choices=["native", "reference"])
     ap.add_argument("--workload", default="config2")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--tune-cache", default=None,
+                    help="JSON file of tile configurations: read if present (no tuning launches), else written")
     ap.add_argument("--cpu-baseline-seconds", type=float, default=15.0)
     return ap.parse_args()
 
@@ -236,7 +243,12 @@ def run_native(a):
 
     with torch.inference_mode():
         # ---- tile configurations for this shape (timed candidates; every rank adopts rank 0's choice)
+        cache = a.tune_cache and f"{a.tune_cache}.tp{world}"
+        if cache and os.path.exists(cache):
+            dense_ops.load_tuned(cache)
         layers[0].tune(T)
+        if cache and rank == 0 and not os.path.exists(cache):
+            dense_ops.save_tuned(cache)
         barrier()
         # ---- device-resident value: K steps captured once in a CUDA graph, replayed for the timed region
         for i in range(a.warmup):
@@ -291,20 +303,66 @@ def run_native(a):
         ms_e2e = max_over_ranks((time.perf_counter() - t0) * 1e3 / e2e_steps)
         comm.check_status()
 
-        # ---- dominant kernel alone: gate_up GEMM + SiLU*mul
+        def graph_ms(fn, n, reps=5):
+            """Mean device time of one fn(i) call: n calls captured in a CUDA graph, replayed reps times."""
+            st = torch.cuda.Stream()
+            st.wait_stream(torch.cuda.current_stream())
+            with torch.cuda.stream(st):
+                for i in range(3):
+                    fn(i)
+                barrier()
+                g_ = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(g_, stream=st):
+                    for i in range(n):
+                        fn(i)
+                g_.replay()
+                barrier()
+                k0, k1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                k0.record(st)
+                for _ in range(reps):
+                    g_.replay()
+                k1.record(st)
+                barrier()
+            torch.cuda.current_stream().wait_stream(st)
+            return max_over_ranks(k0.elapsed_time(k1) / (n * reps))
+
+        # ---- dominant kernel alone: gate_up GEMM + SiLU*mul (weights cycled like in the layer steps)
         gu = [l.mlp.gate_up_proj for l in layers]
-        h_in = normed0
-        for i in range(5):
-            gu[i % n_layers].forward_silu_mul(h_in)
-        torch.cuda.synchronize()
-        reps = max(20, a.steps // 2)
-        k0, k1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        k0.record()
-        for i in range(reps):
-            gu[i % n_layers].forward_silu_mul(h_in)
-        k1.record()
-        torch.cuda.synchronize()
-        ms_kernel = k0.elapsed_time(k1) / reps
+        ms_kernel = graph_ms(lambda i: gu[i % n_layers].forward_silu_mul(normed0), 2 * n_layers)
+
+        # ---- the reference's GPU sequence on this box, for comparison: cuBLAS GEMMs (torch.matmul), the
+        # separate rotary / SiLU*mul / add+RMSNorm kernels and an NCCL all-reduce after each row-parallel GEMM
+        from sarathi_serve_b200 import activation_ops, layernorm_ops, pos_encoding_ops
+        sa0 = layers[0].self_attn
+        cache = sa0.rotary_emb.cos_sin_cache
+        d_loc = case.intermediate_size // world
+
+        def step_cublas(i):
+            l = layers[i % n_layers]
+            nxt = layers[(i + 1) % n_layers].input_layernorm
+            qkv = torch.matmul(normed0, l.self_attn.qkv_proj.weight.t())
+            q, k, v = qkv.split([sa0.q_size, sa0.kv_size, sa0.kv_size], dim=-1)
+            pos_encoding_ops.rotary_embedding(pos_dev, q, k, sa0.head_dim, cache, True)
+            o = torch.matmul(q, l.self_attn.o_proj.weight.t())
+            if world > 1:
+                dist.all_reduce(o)
+            h = torch.empty_like(o)
+            r = torch.empty_like(o)
+            layernorm_ops.fused_add_rms_norm(h, r, o, x_dev, l.post_attention_layernorm.weight.data, 1e-5)
+            gu_ = torch.matmul(h, l.mlp.gate_up_proj.weight.t())
+            act = torch.empty(T, d_loc, dtype=gu_.dtype, device=dev)
+            activation_ops.silu_and_mul(act, gu_)
+            dn = torch.matmul(act, l.mlp.down_proj.weight.t())
+            if world > 1:
+                dist.all_reduce(dn)
+            layernorm_ops.fused_add_rms_norm(h, o, dn, r, nxt.weight.data, 1e-5)
+            return h
+
+        try:
+            ms_cublas = graph_ms(step_cublas, 2 * n_layers)
+        except Exception as exc:  # the comparison is optional: say why it is missing
+            ms_cublas = None
+            cublas_err = f"{type(exc).__name__}: {exc}"
 
     peak_tf, peak_hbm, peak_src = peaks()
     d = case.intermediate_size // world
@@ -329,7 +387,15 @@ def run_native(a):
                 "tile_cfgs": {k[0] + f"[{k[2]}x{k[3]}]": v for k, v in dense_ops._tuned.items()},
                 "roofline": {"bound": "tensor", "kernel": "gemm_sm100_kernel<bf16, EPI_SILU_MUL> (gate_up + SiLU*mul)",
                              "achieved": achieved, "peak": peak_tf, "unit": "TFLOP/s", "frac": achieved / peak_tf,
-                             "peak_source": f"{peak_src} (burst bf16)", "ms_per_launch": ms_kernel, "traffic": None}}
+                             "peak_source": f"{peak_src} (burst bf16)", "ms_per_launch": ms_kernel,
+                             # DRAM bytes per launch from the committed ncu capture of this kernel (TP=1 workload)
+                             "traffic": GATE_UP_TP1_DRAM_BYTES if (world == 1 and a.workload == "config2") else None,
+                             "algorithmic_bytes": 2 * d * H * es + T * H * es + T * d * es},
+                "gpu_comparison": ({"what": "same step as cuBLAS GEMMs (torch.matmul) + separate rotary / SiLU*mul / "
+                                            "add+RMSNorm kernels" + (" + NCCL all-reduce" if world > 1 else "") +
+                                            ", one CUDA graph", "ms_per_step": ms_cublas,
+                                    "value": T / (ms_cublas * 1e-3), "unit": UNIT} if ms_cublas else
+                                   {"unavailable": cublas_err})}
         if not a.no_cpu_baseline and world == 1:
             v, cores, iters, med = time_cpu(case, a.cpu_baseline_seconds)
             line["cpu_baseline"] = {"value": v, "unit": UNIT, "cores": cores, "kind": "port",

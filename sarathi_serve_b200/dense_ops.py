@@ -151,6 +151,26 @@ def gemm_plan(epilogue: int, T: int, Nn: int, K: int, head_size: int = 128, tile
 _tuned: dict = {}
 
 
+def save_tuned(path: str) -> None:
+    """Write the tile configurations found so far to a JSON file (see ``load_tuned``)."""
+    import json
+    rows = [{"kind": k[0], "T": k[1], "N": k[2], "K": k[3], "dtype": str(k[4]).replace("torch.", ""), "cfg": v}
+            for k, v in _tuned.items()]
+    with open(path, "w") as fh:
+        json.dump(rows, fh, indent=1)
+
+
+def load_tuned(path: str) -> int:
+    """Adopt tile configurations saved by ``save_tuned``; ``autotune`` then returns them without timing
+    anything.  Returns the number of entries read."""
+    import json
+    with open(path) as fh:
+        rows = json.load(fh)
+    for r in rows:
+        _tuned[(r["kind"], int(r["T"]), int(r["N"]), int(r["K"]), getattr(torch, r["dtype"]))] = int(r["cfg"])
+    return len(rows)
+
+
 def tuned_cfg(kind: str, T: int, Nn: int, K: int, dtype: torch.dtype) -> int:
     """Tile configuration found by ``autotune`` for this problem, or 0 (library default)."""
     return _tuned.get((kind, T, Nn, K, dtype), 0)
