@@ -10,9 +10,13 @@ mixed chunk of 512 tokens (448 prefill + 64 decode), tensor-parallel over N
 GPUs, attention replaced by the stand-in attn_out = q (attention is outside
 the path).  Inputs are seeded synthetic tensors (sarathi_serve_b200.synthetic).
 
-`value`   : tokens/s of the device-resident layer (4 kernels per step: qkv GEMM+rotary,
+`value`   : tokens/s of the device-resident layer (4 kernels per step at N > 1: qkv GEMM+rotary,
             o_proj GEMM+all-reduce+residual+RMSNorm, gate_up GEMM+SiLU*mul,
-            down GEMM+all-reduce+residual+next RMSNorm), CUDA-event timed, max over ranks.
+            down GEMM+all-reduce+residual+next RMSNorm; at N = 1, where nothing is exchanged, the two
+            row-parallel GEMMs are each followed by the add+RMSNorm kernel: 6 kernels), all timed steps
+            in one CUDA graph, CUDA-event timed, max over ranks.
+`gpu_comparison`: the same step as the reference runs it on a GPU (cuBLAS GEMMs, separate rotary /
+            SiLU*mul / add+RMSNorm kernels, NCCL all-reduce), same graph timing.
 `e2e`     : tokens/s through the public layer API with HOST buffers: pinned H2D of the
             hidden states and positions, LlamaDecoderLayer.forward, D2H of the result, every step.
 `roofline`: the dominant kernel (gate_up GEMM + SiLU*mul), timed alone with CUDA events.
@@ -383,7 +387,7 @@ def run_native(a):
                 "clocks": clocks,
                 "e2e": {"value": T / (ms_e2e * 1e-3), "unit": UNIT, "ms_per_step": ms_e2e,
                         "h2d_bytes_per_step": T * H * es + T * 8, "d2h_bytes_per_step": T * H * es},
-                "gpu_launches": 4 * a.steps, "launch_mode": "one CUDA graph of all timed steps",
+                "gpu_launches": (4 if world > 1 else 6) * a.steps, "launch_mode": "one CUDA graph of all timed steps",
                 "tile_cfgs": {k[0] + f"[{k[2]}x{k[3]}]": v for k, v in dense_ops._tuned.items()},
                 "roofline": {"bound": "tensor", "kernel": "gemm_sm100_kernel<bf16, EPI_SILU_MUL> (gate_up + SiLU*mul)",
                              "achieved": achieved, "peak": peak_tf, "unit": "TFLOP/s", "frac": achieved / peak_tf,

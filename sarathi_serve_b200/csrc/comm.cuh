@@ -198,7 +198,7 @@ template <typename T, int VPL>
 __device__ __forceinline__ void reduce_rows(const CommView& c, const ReduceArgs& a, int gteam, int num_teams, int tw,
                                             int team, int wt, int lane, int warp, int nrows, float* s_ss) {
   constexpr int N = Vec16<T>::N;
-  constexpr int SB = 8 / VPL;  // source ranks whose loads are issued together (8 vectors in flight per lane)
+  constexpr int SB = VPL <= 2 ? 8 : 8 / VPL;  // source ranks whose loads are issued together (8-16 vectors in flight per lane)
   const int nvec = a.H / N;
   const int row0 = c.rank * a.rows_per_rank;
   const T* bias = (const T*)a.bias;
@@ -351,11 +351,11 @@ __device__ void reduce_phase(const CommView& c, const ReduceArgs& a, int cta, in
 
 // Bring the rows other ranks own into this rank's heap (and the caller's tensors).  The CTAs split
 // into one group per peer; a group waits for its peer's done flag only, then copies that peer's rows
-// with several loads in flight per thread.  Called by all threads of every CTA.
+// with up to 8 loads in flight per thread.  Called by all threads of every CTA.
 template <typename T>
 __device__ void gather_phase(const CommView& c, const ReduceArgs& a, int cta, int num_ctas) {
   constexpr int N = Vec16<T>::N;
-  constexpr int U = 4;
+  constexpr int U = 8;
   __shared__ int s_ok;
   const int others = c.world - 1;
   if (others == 0) return;

@@ -102,13 +102,13 @@ GemmPlan plan_gemm(int epi, int64_t M, int64_t N, int64_t K, int head_size, int 
       const int units_max = cta2 ? sms / 2 : sms;     // CTAs or CTA pairs that run at once
       const int64_t total = tiles * k_blocks;
       // per-k-block clocks of one SM (constants fitted to measurements on B200):
-      //   a tcgen05.mma of K=16 occupies the tensor pipe for at least ~137 clocks whatever its
-      //   shape, so a k-block (4 MMAs per accumulator) costs >= 548*MI clocks; its nominal time
-      //   is M*N*16*2 / 8192 flop/clk; the stage also has to cross L2 -> shared memory
-      //   (~50 B/clk/SM with every SM pulling) and shared memory itself (fill + operand reads).
+      //   one CTA: a tcgen05.mma of K=16 (M=128) occupies the tensor pipe ~154 clocks whatever N <= 256;
+      //   a CTA pair (M=256) runs at the nominal rate, N/2 clocks per MMA with a floor of ~65;
+      //   the stage also has to cross L2 -> shared memory (~50 B/clk/SM with every SM pulling, which
+      //   is what bounds 256x256 pair tiles) and shared memory itself (fill + operand reads).
       const double stage = gemm_stage_bytes(mi, bn, cta2);
-      const double mma_nominal = 2.0 * mi * bn * 1.08;
-      const double mma_floor = 548.0 * mi;
+      const double mma_nominal = cta2 ? 2.0 * mi * bn : 616.0 * mi;
+      const double mma_floor = cta2 ? 260.0 * mi : 616.0 * mi;
       const double b_rows = cta2 ? bn / 2.0 : bn;
       const double smem_rd = mi * (128 + b_rows) * kBK * 2;
       double per_kb = mma_nominal > mma_floor ? mma_nominal : mma_floor;
@@ -123,36 +123,36 @@ GemmPlan plan_gemm(int epi, int64_t M, int64_t N, int64_t K, int head_size, int 
       const int64_t G = tiles < units_max ? tiles : units_max;
       const int64_t tiles_full = (tiles / G) * G, rem = tiles - tiles_full;
       const double full_item = dbuf ? (k_blocks * per_kb > epi_c ? k_blocks * per_kb : epi_c) : k_blocks * per_kb + epi_c;
-      for (int sp = 1; sp <= 8; ++sp) {  // parts the tiles of the last partial round are cut into
+      for (int sp = 1; sp <= 8; ++sp) {  // about sp units share a tile of the last partial round
         if (f_s && sp != f_s) continue;
-        int64_t units = G;
-        int kbp = k_blocks;
-        double cost = 9000.0 + (dbuf ? epi_c : 0.0);
-        if (tiles >= units_max || sp == 1) cost += (tiles_full / G) * full_item;
+        const int64_t rem_t = rem ? rem : (tiles < units_max ? tiles : 0);  // fewer tiles than units: all are "the last round"
+        const int64_t full_rounds = tiles < units_max ? 0 : tiles_full / G;
+        int64_t units = G, gs = rem_t;
+        double cost = 9000.0 + (dbuf ? epi_c : 0.0) + full_rounds * full_item;
         if (sp == 1) {
-          if (rem) cost += full_item;
+          if (rem_t) cost += full_item;
         } else {
-          // cutting only pays (and is only allowed) when the parts fit into one extra round
-          const int64_t rem_t = rem ? rem : 0;
-          if (rem_t == 0 && tiles >= units_max) continue;
-          const int64_t cut_tiles = rem_t ? rem_t : tiles;  // fewer tiles than units: all of them are "the last round"
-          if (sp > k_blocks / 2) break;
-          if (tiles < units_max) units = (cut_tiles * sp < units_max) ? cut_tiles * sp : units_max;
-          const size_t need = kWsCounterBytes + (size_t)cut_tiles * sp * bm * bn * sizeof(float);
-          if (need > ws_bytes || (size_t)cut_tiles * 32 * sizeof(uint32_t) > kWsCounterBytes) continue;
-          if (cut_tiles * sp > units) continue;  // all parts of a tile must run at the same time (one round)
-          kbp = (k_blocks + sp - 1) / sp;
-          if ((int64_t)(sp - 1) * kbp >= k_blocks) continue;  // an empty part
-          const int64_t rounds = (cut_tiles * sp + units - 1) / units;
-          const double fix = epi_units * 700.0 + 4500.0;  // dump, wait for the other parts, summed re-read of 1/S of the tile
-          cost += rounds * (kbp * per_kb + (dbuf ? 300.0 : epi_c)) + fix;
+          if (rem_t == 0) continue;  // nothing to cut
+          const int64_t W = rem_t * k_blocks;
+          gs = rem_t * sp < units_max ? rem_t * sp : units_max;
+          if (gs > W / 2) gs = W / 2;          // at least two k-blocks per unit
+          if (gs <= rem_t) continue;           // degenerates to whole tiles
+          if (tiles < units_max) units = gs;
+          const size_t need = kWsCounterBytes + (size_t)(gs + rem_t) * bm * bn * sizeof(float);
+          if (need > ws_bytes || (size_t)rem_t * 32 * sizeof(uint32_t) > kWsCounterBytes) continue;
+          const double share = (double)((W + gs - 1) / gs);
+          // every range leaves an fp32 partial tile in L2 and reads one tile's worth back (measured ~20 B/clk/SM
+          // with all SMs at it); a unit whose range straddles two tiles does that twice
+          const double segs = (gs % rem_t == 0) ? 1.0 : 2.0;
+          const double fix = 1500.0 + segs * 51.0 * bn;
+          cost += share * per_kb + (dbuf ? 300.0 : epi_c) + fix;
         }
         if (cost < best_cost) {
           best_cost = cost;
           best.cta2 = cta2; best.mi = mi; best.bn = bn;
           best.units = (int)units;
-          best.tiles_full = (tiles >= units_max) ? (int)tiles_full : (sp > 1 ? 0 : (int)tiles_full);
-          best.rem_splits = sp; best.kb_per_part = kbp;
+          best.tiles_full = (tiles >= units_max) ? (int)tiles_full : 0;
+          best.rem_splits = sp; best.rem_units = (int)gs;
           best.stages = stages; best.m_tiles = m_tiles; best.n_tiles = n_tiles; best.k_blocks = k_blocks;
           best.est_clocks = cost;
         }
@@ -183,7 +183,11 @@ uint32_t gemm_push_increments(const GemmPlan& p, int64_t M, int64_t lo, int64_t 
     if (!groups) continue;
     // tiles mt, mt + m_tiles, ... : whole ones below tiles_full, cut ones from there on
     uint64_t weight = 0;
-    for (int64_t t = mt; t < tiles; t += p.m_tiles) weight += (t < p.tiles_full) ? 1 : (uint64_t)p.rem_splits;
+    for (int64_t t = mt; t < tiles; t += p.m_tiles) {
+      int first = 0, parts = 1;
+      if (t >= p.tiles_full) sk_tile_parts(p.k_blocks, (int)(tiles - p.tiles_full), p.rem_units, (int)(t - p.tiles_full), &first, &parts);
+      weight += (uint64_t)parts;
+    }
     total += (uint64_t)groups * slots_per_group * weight;
   }
   return (uint32_t)total;
@@ -257,12 +261,12 @@ int run_gemm_sm100(int dtype, int epi, const GemmPlan& plan, const void* x, int6
   SB_CHECK_ARG(plan.bn != 0, "no GEMM tile shape fits epilogue %d (head_size=%d)", epi, g.head_size);
   g.cta2 = plan.cta2;
   g.mi = plan.mi; g.bn = plan.bn; g.units = plan.units; g.tiles_full = plan.tiles_full;
-  g.rem_splits = plan.rem_splits; g.kb_per_part = plan.kb_per_part;
+  g.rem_units = plan.rem_units;
   g.l2_prefetch = l2_prefetch_distance();
   { const char* e = getenv("SB200_DEBUG"); g.debug = e ? atoi(e) : 0; }
   g.stages = plan.stages; g.m_tiles = plan.m_tiles; g.n_tiles = plan.n_tiles; g.k_blocks = plan.k_blocks;
-  if (plan.rem_splits > 1) {
-    SB_CHECK_ARG(workspace && aligned16(workspace), "stream-K scheduling needs an aligned workspace");
+  if (plan.rem_units > (int)((int64_t)plan.m_tiles * plan.n_tiles - plan.tiles_full)) {
+    SB_CHECK_ARG(workspace && aligned16(workspace), "cutting tiles along K needs an aligned workspace");
     g.ws_counters = reinterpret_cast<uint32_t*>(workspace);
     g.ws = reinterpret_cast<float*>(reinterpret_cast<char*>(workspace) + kWsCounterBytes);
   }
@@ -372,14 +376,14 @@ extern "C" int sb200_gemm_colpar(void* out, int64_t ldo, const void* x, int64_t 
 }
 
 // The tile shape and schedule sb200_gemm_colpar / sb200_gemm_rowpar would use (for tuning and tests).
-// out[0..10] = cta2, mi, bn, units, tiles_full, rem_splits, kb_per_part, stages, m_tiles, n_tiles, k_blocks.
+// out[0..10] = cta2, mi, bn, units, tiles_full, rem_splits, rem_units, stages, m_tiles, n_tiles, k_blocks.
 extern "C" int sb200_gemm_plan(int epilogue, int64_t T, int64_t N, int64_t K, int head_size, int tile_cfg,
                                int64_t workspace_bytes, int* out) {
   SB_CHECK_ARG(out != nullptr && T > 0 && N > 0 && K > 0, "gemm_plan: bad arguments");
   const int epi = epilogue == SB200_EPI_ROTARY ? EPI_ROTARY : epilogue == SB200_EPI_SILU_MUL ? EPI_SILU_MUL
                   : epilogue == 3 ? EPI_PUSH : EPI_STORE;
   const GemmPlan p = plan_gemm(epi, T, N, K, head_size ? head_size : 128, tile_cfg, (size_t)workspace_bytes);
-  const int v[11] = {p.cta2, p.mi, p.bn, p.units, p.tiles_full, p.rem_splits, p.kb_per_part, p.stages, p.m_tiles,
+  const int v[11] = {p.cta2, p.mi, p.bn, p.units, p.tiles_full, p.rem_splits, p.rem_units, p.stages, p.m_tiles,
                      p.n_tiles, p.k_blocks};
   for (int i = 0; i < 11; ++i) out[i] = v[i];
   return p.bn ? SB200_OK : SB200_ERR_UNSUPPORTED;

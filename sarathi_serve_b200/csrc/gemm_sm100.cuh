@@ -70,8 +70,7 @@ struct GemmArgs {
   int bn;                  // tile columns
   int units;               // G: scheduling units launched (CTAs, or CTA pairs)
   int tiles_full;          // tiles handed out whole, round-robin (a multiple of units)
-  int rem_splits;          // S: parts each remaining tile is cut into along K (1 = not cut)
-  int kb_per_part;         // k-blocks per part
+  int rem_units;           // units that share the k-blocks of the remaining tiles (= their number: tiles not cut)
   int stages;              // shared-memory ring depth
   int l2_prefetch;         // k-blocks ahead at which the B boxes are prefetched into L2 (0 = off)
   int debug;               // profiling switches (0 in production)
@@ -156,21 +155,37 @@ struct TmemSource {
 //   * the first `tiles_full` tiles (a multiple of G) are handed out round-robin, whole: unit p
 //     computes tiles p, p+G, ...  Neighbouring units then work on the M-tiles of the same
 //     weight tile at the same time, so a weight tile comes from HBM once and hits in L2 after;
-//   * each of the remaining `rem_tiles` tiles is cut along K into S parts of `kbp` k-blocks
-//     (S = 1: not cut), and the rem_tiles*S parts are handed out round-robin as well.  A part
-//     leaves an fp32 partial tile in workspace slot `part index`; the last part of a tile to
-//     arrive (per 32-row slot) sums all S in part order and runs the epilogue.
+//   * the k-blocks of the remaining R = `rem_tiles` tiles (R < G) form one sequence of
+//     W = R * k_blocks items that is cut into Gs >= R equal ranges, one per unit p < Gs:
+//     unit p gets [p*W/Gs, (p+1)*W/Gs), which touches one or two tiles.  A tile touched by
+//     S > 1 units is "cut": each of them leaves an fp32 partial tile in a workspace slot, and
+//     once all S have arrived every one of them sums the slots (in part order) and finishes
+//     its share of the tile.  Gs = R: whole tiles, nothing is cut.
+// A unit stores the partials of all its ranges before it waits for anybody else's, so the waits
+// cannot form a cycle.
 struct Sched {
-  int G, tiles_full, rem_tiles, S, kbp, k_blocks;
+  int G, tiles_full, rem_tiles, Gs, k_blocks;
 };
 struct Segment {
   int tile, kb0, kb1;
-  int parts;       // parts this tile is cut into (1: whole)
+  int parts;       // units this tile is shared by (1: whole)
   int part_slot;   // workspace slot of this part; the tile's parts are slots first_slot .. first_slot+parts-1
   int first_slot;
-  int rem_index;   // index of the tile among the cut tiles (selects its arrival counters)
+  int rem_index;   // index of the tile among the remaining tiles (selects its arrival counters)
   bool valid;
 };
+// Unit whose range holds item x of the W remaining k-blocks: the p with floor(p*W/Gs) <= x < floor((p+1)*W/Gs).
+__host__ __device__ inline int sk_unit_of(long long W, int Gs, long long x) {
+  return (int)(((x + 1) * Gs - 1) / W);
+}
+// First unit and number of units that share remaining tile rt.
+__host__ __device__ inline void sk_tile_parts(int k_blocks, int rem_tiles, int Gs, int rt, int* first_unit, int* parts) {
+  const long long W = (long long)rem_tiles * k_blocks;
+  const int pf = sk_unit_of(W, Gs, (long long)rt * k_blocks);
+  const int pl = sk_unit_of(W, Gs, (long long)(rt + 1) * k_blocks - 1);
+  *first_unit = pf;
+  *parts = pl - pf + 1;
+}
 // it-th work item of unit p.
 __device__ __forceinline__ Segment segment_of(const Sched& sc, int p, int it) {
   Segment sg;
@@ -181,15 +196,24 @@ __device__ __forceinline__ Segment segment_of(const Sched& sc, int p, int it) {
     sg.kb0 = 0; sg.kb1 = sc.k_blocks; sg.parts = 1; sg.part_slot = 0; sg.first_slot = 0; sg.rem_index = 0;
     return sg;
   }
-  const long long j = (long long)p + (long long)(it - nA) * sc.G;
-  if (j >= (long long)sc.rem_tiles * sc.S) { sg.valid = false; return sg; }
-  const int rt = (int)(j / sc.S), sp = (int)(j - (long long)rt * sc.S);
+  sg.valid = false;
+  if (p >= sc.Gs || sc.rem_tiles == 0) return sg;
+  const long long W = (long long)sc.rem_tiles * sc.k_blocks;
+  const long long b0 = (long long)p * W / sc.Gs, b1 = (long long)(p + 1) * W / sc.Gs;
+  const int rt = (int)(b0 / sc.k_blocks) + (it - nA);
+  if (rt >= sc.rem_tiles) return sg;
+  const long long t0 = (long long)rt * sc.k_blocks;
+  const long long lo = b0 > t0 ? b0 : t0, hi = b1 < t0 + sc.k_blocks ? b1 : t0 + sc.k_blocks;
+  if (lo >= hi) return sg;
+  int pf, S;
+  sk_tile_parts(sc.k_blocks, sc.rem_tiles, sc.Gs, rt, &pf, &S);
+  sg.valid = true;
   sg.tile = sc.tiles_full + rt;
-  sg.kb0 = sp * sc.kbp;
-  sg.kb1 = min(sc.k_blocks, sg.kb0 + sc.kbp);
-  sg.parts = sc.S;
-  sg.part_slot = (int)j;
-  sg.first_slot = rt * sc.S;
+  sg.kb0 = (int)(lo - t0);
+  sg.kb1 = (int)(hi - t0);
+  sg.parts = S;
+  sg.first_slot = pf + rt;
+  sg.part_slot = p + rt;
   sg.rem_index = rt;
   return sg;
 }
@@ -384,6 +408,14 @@ __device__ __forceinline__ RowCtx<T> make_row_ctx(const GemmArgs& g, const CommV
   return rc;
 }
 
+// Row-parallel projection: the 32 rows starting at r_lo of some tile are final in this rank's partial
+// region (called by one lane after a __syncwarp of the storing warp): one arrival per owner of those rows.
+__device__ __forceinline__ void push_rows_done(const CommView& comm, const ReduceArgs& red, const GemmArgs& g, int r_lo) {
+  const int r_hi = min(g.M, r_lo + 32) - 1;
+  if (r_hi >= r_lo)
+    for (int o = r_lo / red.rows_per_rank; o <= r_hi / red.rows_per_rank; ++o) signal_push(comm, red, o);
+}
+
 // ---------------------------------------------------------------------------
 // The kernel.  `comm` / `red` are used only by EPI_PUSH.
 //   CTA2 = false: one CTA per tile of 128*MI x BN.
@@ -427,8 +459,7 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
   sc.G = num_units_grid;
   sc.tiles_full = g.tiles_full;
   sc.rem_tiles = g.m_tiles * g.n_tiles - g.tiles_full;
-  sc.S = g.rem_splits;
-  sc.kbp = g.kb_per_part;
+  sc.Gs = g.rem_units;
   sc.k_blocks = g.k_blocks;
   // grouped mode: rows of A in use (a device value written by moe_align_block_size earlier in the stream)
   const int rows_in_use = g.expert_ids ? min(g.M, *g.num_post_pad) : g.M;
@@ -616,57 +647,54 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
       if (lane == 0) {
         if (CTA2) ptx::mbar_arrive_cluster(empty_remote + (uint32_t)(buf * 8));
         else ptx::mbar_arrive(&tmem_empty[buf]);
+        // a part of a cut tile: tell the tile's other parts that these 32 rows of it are in the workspace
+        // (release increment after the __syncwarp: covers the stores of all lanes)
+        if (S > 1) arrive_acq_rel(g.ws_counters + (size_t)sg.rem_index * 32 + slot);
       }
+      if constexpr (EPI == EPI_PUSH) {
+        if (S == 1 && lane == 0) push_rows_done(comm, red, g, mt * BM + row_in_tile - lane);
+      }
+    }
 
-      bool finished_here = (S == 1);  // did this warp produce final (stored / pushed) values for its rows?
-      if (S > 1) {
-        // ... and, once every part of the tile has left its share for these 32 rows, finish 1/S of
-        // the units: all S parts work on the fix-up at once instead of one of them doing it alone.
-        // (The parts of a tile are the LAST work item of S different, co-resident units, so the
-        // wait below cannot depend on anything that has not been scheduled; it is bounded anyway.)
-        if (!(g.debug & 4)) __threadfence();
-        __syncwarp();
-        uint32_t* ctr_arrive = g.ws_counters + (size_t)sg.rem_index * 32 + slot;
-        uint32_t* ctr_done = ctr_arrive + 16;
-        int arrived = 1;
-        if (lane == 0) {
-          atomicAdd(ctr_arrive, 1u);
-          const long long t0 = clock64();
-          while (ld_acquire_gpu(ctr_arrive) < (uint32_t)S) {
-            __nanosleep(32);
-            if (*abort_flag || clock64() - t0 > ptx::kWaitLimitCycles) { arrived = 0; *abort_flag = 1; break; }
-          }
+    // Second pass over the cut tiles this unit has a part of: once every part of a tile has left its
+    // share for these 32 rows, finish 1/S of the tile's units -- all S parts work on the fix-up at
+    // once instead of one of them doing it alone.
+    for (int it = sc.tiles_full / sc.G; ok; ++it) {
+      const Segment sg = segment_of(sc, unit_id, it);
+      if (!sg.valid) break;
+      const int S = sg.parts;
+      if (S == 1) continue;
+      const int mt = sg.tile % g.m_tiles, nt = sg.tile / g.m_tiles;
+      if (g.expert_ids && mt * BM >= rows_in_use) continue;
+      uint32_t* ctr_arrive = g.ws_counters + (size_t)sg.rem_index * 32 + slot;
+      uint32_t* ctr_done = ctr_arrive + 16;
+      int arrived = 1;
+      if (lane == 0) {
+        const long long t0 = clock64();
+        while (ld_acquire_gpu(ctr_arrive) < (uint32_t)S) {
+          __nanosleep(32);
+          if (*abort_flag || clock64() - t0 > ptx::kWaitLimitCycles) { arrived = 0; *abort_flag = 1; break; }
         }
-        arrived = __shfl_sync(0xffffffffu, arrived, 0);
-        if (!arrived) { ok = false; break; }
-        if (!(g.debug & 2)) {
-          const int my_part = sg.part_slot - sg.first_slot;
-          const WorkspaceSource wsrc{g.ws + (size_t)sg.first_slot * BM * BN + row_in_tile, (size_t)BM * BN, BM, S};
-          int k = 0;
-          for (int u = u_first; u < U; u += u_step, ++k)
-            if (k % S == my_part) finish_unit<T, EPI>(g, rc, wsrc, u);
-        }
-        finished_here = true;
-        __syncwarp();
-        if (lane == 0 && atomicAdd(ctr_done, 1u) == (uint32_t)(S - 1)) {  // last reader: ready for the next launch
+      }
+      arrived = __shfl_sync(0xffffffffu, arrived, 0);
+      if (!arrived) { ok = false; break; }
+      const int n0 = nt * (EPI == EPI_SILU_MUL ? BN / 2 : BN);
+      const RowCtx<T> rc = make_row_ctx<T, EPI>(g, comm, red, mt * BM + row_in_tile, n0);
+      if (!(g.debug & 2)) {
+        const int my_part = sg.part_slot - sg.first_slot;
+        const WorkspaceSource wsrc{g.ws + (size_t)sg.first_slot * BM * BN + row_in_tile, (size_t)BM * BN, BM, S};
+        int k = 0;
+        for (int u = u_first; u < U; u += u_step, ++k)
+          if (k % S == my_part) finish_unit<T, EPI>(g, rc, wsrc, u);
+      }
+      __syncwarp();
+      if (lane == 0) {
+        if (atomicAdd(ctr_done, 1u) == (uint32_t)(S - 1)) {  // last reader: ready for the next launch
           *ctr_arrive = 0;
           *ctr_done = 0;
         }
-      }
-
-      if constexpr (EPI == EPI_PUSH) {
-        // Publish this warp's rows to their owner(s): the stores of all lanes first, then one
-        // arrival per owner (the arrival that completes an owner's count sends the flag).  Exactly one epilogue warp per (tile, slot) gets here with
-        // finished_here set for a whole tile and S of them (one per part) for a tile cut along K, so
-        // the host can count the increments per (tile, slot, owner of the slot's rows).
-        if (finished_here) {
-          __syncwarp();
-          if (lane == 0) {
-            const int r_lo = mt * BM + row_in_tile - lane, r_hi = min(g.M, r_lo + 32) - 1;
-            if (r_hi >= r_lo)
-              for (int o = r_lo / red.rows_per_rank; o <= r_hi / red.rows_per_rank; ++o) signal_push(comm, red, o);
-          }
-        }
+        // every part reports its share of these rows: S arrivals per (cut tile, 32-row slot)
+        if (EPI == EPI_PUSH) push_rows_done(comm, red, g, mt * BM + row_in_tile - lane);
       }
     }
   }

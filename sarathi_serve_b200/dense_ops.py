@@ -142,7 +142,7 @@ def gemm_plan(epilogue: int, T: int, Nn: int, K: int, head_size: int = 128, tile
     """The tile shape / schedule the library would use for a [T, K] x [Nn, K]^T projection."""
     out = (ctypes.c_int * 11)()
     N.check(N.lib().sb200_gemm_plan(epilogue, T, Nn, K, head_size, tile_cfg, workspace_bytes, out), "gemm_plan")
-    keys = ("cta_pairs", "accumulators", "bn", "units", "tiles_full", "k_parts", "kb_per_part", "stages", "m_tiles",
+    keys = ("cta_pairs", "accumulators", "bn", "units", "tiles_full", "k_parts", "rem_units", "stages", "m_tiles",
             "n_tiles", "k_blocks")
     return dict(zip(keys, out))
 

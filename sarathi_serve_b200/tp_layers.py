@@ -144,6 +144,9 @@ class RowParallelLinear(torch.nn.Module):
         """Pick the fastest tile configuration of the fused GEMM for [num_tokens, in/tp] inputs; every rank of
         the tensor-parallel group must call this together (rank 0's choice is shared)."""
         group = ps.get_tensor_model_parallel_group() if self.world_size > 1 else None
+        if self.world_size == 1:  # forward_fused runs the plain GEMM there
+            dense_ops.autotune("store", num_tokens, self.weight.shape[0], self.weight.shape[1], self.weight.dtype,
+                               self.weight.device)
         return dense_ops.autotune("push", num_tokens, self.weight.shape[0], self.weight.shape[1], self.weight.dtype,
                                   self.weight.device, group=group)
 
@@ -182,6 +185,17 @@ class RowParallelLinear(torch.nn.Module):
         context (valid until the second-next collective)."""
         assert self.input_is_parallel and self.reduce_results
         add_bias = self.bias if (self.bias is not None and not self.skip_bias_add) else None
+        if self.world_size == 1 and residual is not None and norm_weight is not None:
+            # Nothing to exchange: the plain GEMM followed by the one-pass add + RMSNorm kernel is faster
+            # than the in-kernel tail, whose rows have to wait for every column tile of the GEMM.
+            from . import layernorm_ops
+            prod = dense_ops.linear(input_, self.weight, add_bias,
+                                    tile_n=dense_ops.tuned_cfg("store", input_.shape[0], self.weight.shape[0],
+                                                               self.weight.shape[1], input_.dtype))
+            y = out if out is not None else torch.empty_like(prod)
+            z = resid_out if resid_out is not None else torch.empty_like(prod)
+            layernorm_ops.fused_add_rms_norm(y, z, prod, residual, norm_weight, eps)
+            return y, z
         return self._comm(input_.shape[0]).rowpar_linear(input_, self.weight, bias=add_bias, residual=residual,
                                                          norm_weight=norm_weight, eps=eps,
                                                          resid_everywhere=resid_everywhere, out=out,

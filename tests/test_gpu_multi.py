@@ -60,8 +60,11 @@ def _run(fn_name, port, world):
         if p.is_alive():
             p.terminate()
             pytest.fail(f"{fn_name}: a rank did not finish within the time limit")
-    for r in range(world):
-        assert ret.get(r) == "ok", f"rank {r}: {ret.get(r)}"
+    bad = {r: ret.get(r) for r in range(world) if ret.get(r) != "ok"}
+    if bad:  # the children's tracebacks, in full, on stdout as well (the assertion message gets truncated)
+        for r, text in bad.items():
+            print(f"---- {fn_name} world={world} rank {r} ----\n{text}", flush=True)
+    assert not bad, f"{fn_name} world={world}: ranks {sorted(bad)} failed; first: {next(iter(bad.values()))}"
 
 
 # ------------------------------------------------------------------ bodies
@@ -69,6 +72,8 @@ def _body_all_reduce(rank, world):
     from sarathi_serve_b200 import parallel_state as ps
     comm = ps.get_tensor_model_parallel_comm(64 << 20)
     for dtype, tol in ((torch.bfloat16, 1e-2), (torch.float32, 1e-5), (torch.float16, 2e-3)):
+        if world > 2 and dtype == torch.float16:
+            continue  # larger groups: a reduced set keeps the multi-GPU run short
         for T, H in ((512, 4096), (288, 1024), (7, 256), (1, 64), (65, 8192)):
             g = torch.Generator().manual_seed(T * 7 + H)
             parts = [torch.randn(T, H, generator=g).to(dtype) for _ in range(world)]
@@ -108,6 +113,8 @@ def _body_rowpar(rank, world):
             for tile_n in (0, 128, 2256, 302128, 3256, 203128, 4256, 204128):
                 if dtype == torch.float32 and tile_n != 0:
                     continue
+                if world > 2 and (dtype == torch.float16 or tile_n not in (0, 302128, 3256, 203128)):
+                    continue  # larger groups: a reduced set keeps the multi-GPU run short
                 if tile_n // 100000 > (K + 63) // 64:
                     continue
                 g = torch.Generator().manual_seed(T + H + K)
@@ -156,7 +163,7 @@ def _body_layer(rank, world):
             out = layer(t.positions.cuda(), x.clone(), 0, QAttention())
             out_u = layer.forward_unfused(t.positions.cuda(), x.clone(), 0, QAttention())
         ps.get_tensor_model_parallel_comm().check_status()
-        if rank == 0 or case_name != "config2":
+        if rank == 0 or (case_name != "config2" and world == 2):
             cache = O.cos_sin_cache(case.head_dim, case.head_dim, case.max_position, case.rope_theta, case.dtype)
             ref = O.decoder_layer([S.shard(t, r, world) for r in range(world)], t.x.to(case.dtype), t.positions,
                                   num_heads=case.num_heads, num_kv_heads=case.num_kv_heads, head_dim=case.head_dim,

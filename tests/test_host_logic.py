@@ -215,3 +215,51 @@ def test_flag_protocol_reports_a_lost_rank_instead_of_hanging():
     st = _run_protocol(4, 6, absent=(2, 3), workers=1)
     assert st[2] == 0  # the absent rank just stops
     assert all(s_ in (2, 3) for i, s_ in enumerate(st) if i != 2), st
+
+
+# ------------------------------------- host model of the K-range partition of the GEMM scheduler
+def _sk_unit_of(W, Gs, x):
+    return ((x + 1) * Gs - 1) // W
+
+
+def _sk_segments(R, KB, Gs, p):
+    """Mirror of segment_of() in csrc/gemm_sm100.cuh for the remaining tiles: (tile, kb0, kb1, parts, part, slot)."""
+    W = R * KB
+    b0, b1 = p * W // Gs, (p + 1) * W // Gs
+    out = []
+    e = 0
+    while True:
+        rt = b0 // KB + e
+        if rt >= R:
+            break
+        t0 = rt * KB
+        lo, hi = max(b0, t0), min(b1, t0 + KB)
+        if lo >= hi:
+            break
+        pf = _sk_unit_of(W, Gs, rt * KB)
+        pl = _sk_unit_of(W, Gs, (rt + 1) * KB - 1)
+        out.append((rt, lo - t0, hi - t0, pl - pf + 1, p - pf, p + rt, pf + rt))
+        e += 1
+    return out
+
+
+@pytest.mark.parametrize("R,KB,Gs", [(96, 64, 148), (4, 64, 32), (4, 64, 148), (1, 8, 4), (147, 7, 148), (12, 64, 148),
+                                     (64, 28, 148), (56, 64, 74), (5, 3, 7), (3, 224, 74), (10, 10, 10)])
+def test_k_range_partition_covers_every_k_block_once(R, KB, Gs):
+    cover = {}
+    slots = set()
+    for p in range(Gs):
+        segs = _sk_segments(R, KB, Gs, p)
+        assert 1 <= len(segs) <= 2
+        for rt, k0, k1, parts, part, slot, first_slot in segs:
+            assert 0 <= part < parts and slot == first_slot + part
+            assert slot not in slots and slot < Gs + R
+            slots.add(slot)
+            for k in range(k0, k1):
+                assert (rt, k) not in cover
+                cover[(rt, k)] = (p, parts)
+    assert len(cover) == R * KB
+    for rt in range(R):  # the units of a tile are consecutive and agree on how many they are
+        units = sorted({cover[(rt, k)][0] for k in range(KB)})
+        assert units == list(range(units[0], units[0] + len(units)))
+        assert {cover[(rt, k)][1] for k in range(KB)} == {len(units)}
