@@ -100,3 +100,27 @@ def test_layer_config2_full_size(tp1):
     tp1.get_tensor_model_parallel_comm().check_status()
     ref = oracle_out(case, t)
     assert rel_err(out, ref["out"]) <= TOL[case.dtype]
+
+
+def test_layer_graph_replay_equals_eager(tp1):
+    """A layer captured in a CUDA graph (graph_runner.LayerGraph) and fed from pinned host buffers returns
+    exactly what the eager call returns, for two different inputs in a row."""
+    from sarathi_serve_b200.graph_runner import LayerGraph
+
+    class Q:
+        def forward(self, q, k, v, layer_cache_idx, softmax_scale=1.0, layer_id=None):
+            return q
+
+    case = S.CASES["mini_bf16"]
+    layer, t = build_layer(case)
+    runner = LayerGraph(layer, case.num_tokens, Q())
+    pos_host = t.positions.pin_memory()
+    for scale in (1.0, -0.5):
+        x_host = (t.x * scale).to(case.dtype).pin_memory()
+        out = runner(pos_host, x_host).clone()
+        with torch.inference_mode():
+            eager = layer(t.positions.cuda(), x_host.cuda(), 0, Q())
+        assert torch.equal(out, eager)
+    with pytest.raises(RuntimeError, match="captured for"):
+        runner(pos_host[:3], x_host[:3])
+    tp1.get_tensor_model_parallel_comm().check_status()
