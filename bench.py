@@ -48,6 +48,11 @@ L2_BYTES = 126 << 20
 GATE_UP_TP1_DRAM_BYTES = 254.2e6
 
 
+def workload_text(name: str, world: int) -> str:
+    return (f"{name}: Llama-3-8B-shaped decoder layer (hidden 4096, 32q/8kv heads, head_dim 128, intermediate 14336), "
+            f"512-token mixed chunk (448 prefill + 64 decode), TP={world}, attention stand-in attn_out=q")
+
+
 def parse():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -173,9 +178,10 @@ def run_reference_arm(a):
     line = {"metric": METRIC, "value": v, "unit": UNIT, "n_gpus": a.gpus, "steps": steps, "warmup": warm,
             "ms_per_step": dt * 1e3, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
             "dtype": "bf16", "data": "synthetic", "impl": "reference",
-            "config": {"workload": f"{a.workload}: Llama-3-8B-shaped decoder layer, 512-token mixed chunk "
-                                   "(448 prefill + 64 decode), oracle port of the reference layer path on CPU, TP=1",
-                       "tokens_per_step": tokens},
+            "config": {"workload": workload_text(a.workload, a.gpus), "tokens_per_step": tokens,
+                       "parallelism": f"tp{a.gpus}",
+                       "how": "oracle port of the reference layer path, one process on the host cores (the whole "
+                              "layer, all shards)"},
             "cpu_baseline": {"value": v, "unit": UNIT, "cores": threads, "kind": "port",
                              "sample": f"{steps} full layer passes of the workload (steps capped at 20)"},
             "e2e": {"value": v, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
@@ -380,9 +386,7 @@ def run_native(a):
         line = {"metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": a.steps, "warmup": a.warmup,
                 "ms_per_step": ms_resident, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
                 "dtype": "bf16", "data": "synthetic",
-                "config": {"workload": f"{a.workload}: Llama-3-8B-shaped decoder layer (hidden 4096, 32q/8kv heads, "
-                                       f"head_dim 128, intermediate 14336), 512-token mixed chunk (448 prefill + 64 "
-                                       f"decode), TP={world}, attention stand-in attn_out=q",
+                "config": {"workload": workload_text(a.workload, world),
                            "tokens_per_step": T, "parallelism": f"tp{world}",
                            "l2": f"{n_layers} distinct weight sets ({n_layers * per_layer_bytes >> 20} MiB/GPU) cycled: "
                                  "operands of consecutive steps exceed the 126 MB L2"},

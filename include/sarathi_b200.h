@@ -170,10 +170,11 @@ typedef struct sb200_rotary_args {
  * tile_cfg: 0 = let the library choose the tile shape, else
  *   BN + 1000*MODE + 100000*S  (BN = tile columns 32..256 step 32; MODE = 1|2: one CTA
  *   with 1|2 accumulators of 128 rows; MODE = 3|4: CTA pairs (tcgen05 cta_group::2) with
- *   1|2 accumulators of 256 rows; S >= 2 cuts tiles along K so that about S units share
- *   one; a bare BN means MODE = 1, whole tiles per CTA).
+ *   1|2 accumulators of 256 rows; S >= 2 spreads the k-blocks of the tiles that do not fill
+ *   a last round over about S units per tile, in equal ranges; a bare BN means MODE = 1,
+ *   whole tiles per CTA).
  * workspace: optional device buffer (zero-filled once by the caller, at least 64 KiB +
- *   room for the fp32 partial tiles) that allows tiles to be cut along K ("stream-K");
+ *   room for the fp32 partial tiles) that allows tiles to be cut along K;
  *   the library leaves its first 64 KiB zero again after every launch.  NULL / 0: whole
  *   tiles per CTA only.
  * Replaces: ColumnParallelLinear.apply_weights / ReplicatedLinear.apply_weights
@@ -187,16 +188,17 @@ int sb200_gemm_colpar(void* out, int64_t ldo, const void* x, int64_t ldx, const 
 
 /* The tile shape and schedule the two GEMM entry points would pick (epilogue 3 = the
  * row-parallel kernel): out[0..10] = cta_pairs, accumulators, BN, scheduling units,
- * tiles handed out whole, K-parts of the remaining tiles, k-blocks per part, pipeline
- * stages, M tiles, N tiles, k-blocks.  Host-only; no counterpart in the reference. */
+ * tiles handed out whole, S of the configuration, units that share the k-blocks of the
+ * remaining tiles (= their number when nothing is cut), pipeline stages, M tiles, N tiles,
+ * k-blocks.  Host-only; no counterpart in the reference. */
 int sb200_gemm_plan(int epilogue, int64_t T, int64_t N, int64_t K, int head_size, int tile_cfg,
                     int64_t workspace_bytes, int* out);
 
 /* ------------------------------------------- tensor-parallel communication */
 
 /* One context per (process, GPU, TP group).  It owns a "symmetric heap" on the
- * current device; after the handle exchange every rank's kernels can store
- * into every other rank's heap over NVLink.  All ranks must issue the same
+ * current device; after the handle exchange every rank's kernels can load from
+ * every other rank's heap over NVLink (and store one flag word per peer and phase).  All ranks must issue the same
  * sequence of sb200_all_reduce / sb200_gemm_rowpar calls with the same shapes.
  * Replaces the NCCL communicator behind get_tensor_model_parallel_group()
  * (sarathi/model_executor/parallel_utils/parallel_state.py:147-158,235-240) for
@@ -229,8 +231,8 @@ int sb200_comm_set_wait_limit(sb200_comm* comm, int64_t cycles);
 int sb200_comm_status(sb200_comm* comm, sb200_stream_t stream, uint32_t* host_status);
 int sb200_comm_clear_status(sb200_comm* comm, sb200_stream_t stream);
 /* Profiling aid: with a device buffer of 148 * 8 uint64, thread 0 of every CTA of the collective
- * kernels records %globaltimer (ns) at: 0 start, 1 tiles/push issued, 2 reduce entered, 3 every
- * rank's push flag seen, 4 rows reduced, 5 every rank's done flag seen, 6 exit.  NULL switches it off (default). */
+ * kernels records %globaltimer (ns) at: 0 start, 1 own partial rows stored, 2 reduce entered, 3 every
+ * rank's "partials stored" flag seen, 4 owned rows reduced, 5 other ranks' rows gathered, 6 exit.  NULL switches it off (default). */
 int sb200_comm_set_trace(sb200_comm* comm, void* device_buffer);
 
 /* Sum `in` [T, H] over the ranks; then, on the summed rows,
@@ -249,10 +251,11 @@ int sb200_all_reduce(sb200_comm* comm, const void* in, int64_t T, int64_t H, int
                      void* out_copy, void* resid_copy, sb200_stream_t stream, void** out_ptr, void** resid_ptr);
 
 /* Row-parallel projection fused with its all-reduce and the element-wise tail:
- *   partial = x[T, K/tp] * w[N, K/tp]^T  (tcgen05, partial rows stored straight
- *   into the owner rank's heap by the GEMM epilogue), then the reduce /
- *   bias / residual / RMSNorm / broadcast phases of sb200_all_reduce in the same kernel.
- * Arguments and results as sb200_all_reduce (H = N).
+ *   partial = x[T, K/tp] * w[N, K/tp]^T  (tcgen05; the GEMM epilogue stores the partial
+ *   rows into this rank's own heap and flags their owners), then the reduce (owners load
+ *   the partial rows of every rank over NVLink) / bias / residual / RMSNorm / gather phases
+ *   of sb200_all_reduce in the same kernel.
+ * Arguments and results as sb200_all_reduce (H = N; rows of at most 16 KiB here, 32 KiB there).
  * Replaces: RowParallelLinear.forward (F.linear -> cuBLAS, then NCCL all-reduce),
  * tensor_parallel/layers.py:421-454, with the same element-wise tail. */
 int sb200_gemm_rowpar(sb200_comm* comm, const void* x, int64_t ldx, const void* w, int64_t ldw, int64_t T,
@@ -285,7 +288,7 @@ int sb200_moe_gemm2(void* out3, const void* act, const void* w2, const int32_t* 
                     uint32_t* status, int tile_cfg, sb200_stream_t stream);
 /* out[t, :] = sum_j in3[t * top_k + j, :] (fp32 sum rounded once; fused_moe.py:539-543). */
 int sb200_moe_sum(void* out, const void* in3, int64_t T, int top_k, int64_t H, int dtype, sb200_stream_t stream);
-/* The same sum fused into the push phase of the all-reduce over the tensor-parallel ranks
+/* The same sum fused into the copy-in phase of the all-reduce over the tensor-parallel ranks
  * (fused_moe/layer.py:128-132); results as sb200_all_reduce without bias / residual / norm. */
 int sb200_moe_sum_all_reduce(sb200_comm* comm, const void* in3, int64_t T, int top_k, int64_t H, int dtype,
                              void* out_copy, sb200_stream_t stream, void** out_ptr);

@@ -263,3 +263,35 @@ def test_k_range_partition_covers_every_k_block_once(R, KB, Gs):
         units = sorted({cover[(rt, k)][0] for k in range(KB)})
         assert units == list(range(units[0], units[0] + len(units)))
         assert {cover[(rt, k)][1] for k in range(KB)} == {len(units)}
+
+
+# --------------------------------------------------------- tile planner (host-only entry point)
+@pytest.mark.parametrize("tp", [1, 2, 4, 8])
+def test_planner_gives_valid_schedules_for_the_layer_shapes(tp):
+    """sb200_gemm_plan needs no GPU (148 SMs assumed): the schedules it returns for the four projections of
+    the headline layer are self-consistent."""
+    from sarathi_serve_b200 import dense_ops as D
+    H, I, T = 4096, 14336, 512
+    shapes = (("qkv", 1, 6144 // tp, H), ("o_proj", 3, H, 4096 // tp), ("gate_up", 2, 2 * I // tp, H),
+              ("down", 3, H, I // tp))
+    for name, epi, N, K in shapes:
+        for cfg in (0, 3256, 203256, 1128, 301128):
+            try:
+                p = D.gemm_plan(epi, T, N, K, tile_cfg=cfg)
+            except RuntimeError:
+                continue  # a forced configuration may not exist for a shape
+            bm = (256 if p["cta_pairs"] else 128) * p["accumulators"]
+            cols = p["bn"] // 2 if epi == 2 else p["bn"]
+            out_cols = N // 2 if epi == 2 else N
+            assert p["m_tiles"] == -(-T // bm) and p["n_tiles"] == -(-out_cols // cols), (name, cfg, p)
+            assert p["k_blocks"] == -(-K // 64)
+            tiles = p["m_tiles"] * p["n_tiles"]
+            units_max = 74 if p["cta_pairs"] else 148
+            assert 1 <= p["units"] <= units_max
+            assert p["tiles_full"] % p["units"] == 0 and p["tiles_full"] <= tiles
+            rem = tiles - p["tiles_full"]
+            assert rem < units_max or p["tiles_full"] == 0
+            if rem:
+                assert rem <= p["rem_units"] <= p["units"], (name, cfg, p)
+                assert p["rem_units"] <= rem * p["k_blocks"]  # at least one k-block per unit
+            assert 2 <= p["stages"] <= 8
