@@ -276,13 +276,21 @@ def run_native(a):
         torch.cuda.current_stream().wait_stream(side)
         graph.replay()  # untimed: first replay of a fresh graph
         barrier()
+        # Clocks are sampled under the same load: the sampler is started, the graph is replayed untimed
+        # (every rank the same number of times) until nvidia-smi has had time to report, and the timed
+        # replay of exactly `steps` steps follows without a gap.
         sampler = ClockSampler(local)
         if rank == 0:
             sampler.start()
+        lead_in = max(2, int(0.3 / max(1e-4, a.steps * 2.5e-4)))
+        for _ in range(lead_in):
+            graph.replay()
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         e0.record()
         graph.replay()
         e1.record()
+        for _ in range(2):  # keeps the load up while the last samples are taken; outside the timed region
+            graph.replay()
         barrier()
         ms_resident = max_over_ranks(e0.elapsed_time(e1) / a.steps)
         clocks = sampler.stop() if rank == 0 else None
@@ -304,8 +312,8 @@ def run_native(a):
             out_host.copy_(out, non_blocking=True)
             torch.cuda.current_stream().synchronize()
 
-        e2e_steps = max(10, a.steps // 4)
-        for i in range(max(3, a.warmup // 4)):
+        e2e_steps = max(50, a.steps)
+        for i in range(max(10, a.warmup)):
             step_e2e(i)
         barrier()
         t0 = time.perf_counter()
@@ -327,9 +335,16 @@ def run_native(a):
                 with torch.cuda.graph(g_, stream=st):
                     for i in range(n):
                         fn(i)
-                g_.replay()
-                barrier()
                 k0, k1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                k0.record(st)
+                g_.replay()
+                k1.record(st)
+                barrier()
+                # same thermal / power state as the layer steps: about 0.3 s of load before the timed replays
+                # (the same count on every rank: the replayed graphs may hold collectives)
+                est_ms = max_over_ranks(k0.elapsed_time(k1))
+                for _ in range(min(2000, max(1, int(300.0 / max(1e-3, est_ms))))):
+                    g_.replay()
                 k0.record(st)
                 for _ in range(reps):
                     g_.replay()
