@@ -226,6 +226,12 @@ void* sb200_comm_scratch(sb200_comm* comm);
 int64_t sb200_comm_region_bytes(sb200_comm* comm);
 /* Limit of every device-side wait on a peer, in SM clock cycles (default ~2 s). */
 int sb200_comm_set_wait_limit(sb200_comm* comm, int64_t cycles);
+/* Collectives whose (world - 1) * T * H * sizeof(dtype) is at most `bytes` run "one-shot": every rank
+ * loads all partial rows and finishes all T rows itself (one wait and one trip over the links);
+ * larger ones have each row reduced by its owner and gathered afterwards.  Default 4 MiB
+ * (environment override SB200_ONE_SHOT_BYTES at creation); 0 = never.  Every rank must use the
+ * same value.  No counterpart in the reference (NCCL picks its algorithm internally). */
+int sb200_comm_set_one_shot_bytes(sb200_comm* comm, int64_t bytes);
 /* Synchronises `stream`, reads the context's device status word into *host_status and returns
  * SB200_ERR_PEER_TIMEOUT if a bounded wait ran out since the last clear. */
 int sb200_comm_status(sb200_comm* comm, sb200_stream_t stream, uint32_t* host_status);

@@ -57,6 +57,7 @@ _GEMM_SIGS: dict = {
     "sb200_comm_scratch": (_P, [_P]),
     "sb200_comm_region_bytes": (_L, [_P]),
     "sb200_comm_set_wait_limit": (_I, [_P, _L]),
+    "sb200_comm_set_one_shot_bytes": (_I, [_P, _L]),
     "sb200_comm_set_trace": (_I, [_P, _P]),
     "sb200_comm_status": (_I, [_P, _P, ctypes.POINTER(ctypes.c_uint32)]),
     "sb200_comm_clear_status": (_I, [_P, _P]),

@@ -74,6 +74,12 @@ class TPComm:
     def set_wait_limit_cycles(self, cycles: int) -> None:
         N.check(N.lib().sb200_comm_set_wait_limit(self._h, int(cycles)), "comm_set_wait_limit")
 
+    def set_one_shot_bytes(self, nbytes: int) -> None:
+        """Collectives with (world - 1) * T * H * itemsize <= nbytes run one-shot (every rank loads all
+        partial rows and finishes all rows itself); larger ones reduce rows at their owners and gather
+        them.  Every rank must set the same value."""
+        N.check(N.lib().sb200_comm_set_one_shot_bytes(self._h, int(nbytes)), "comm_set_one_shot_bytes")
+
     def set_trace(self, buffer: Optional[torch.Tensor]) -> None:
         """Profiling aid: int64 tensor [>=148*8] on this device receives per-CTA phase time stamps (ns)."""
         N.check(N.lib().sb200_comm_set_trace(self._h, N.ptr(buffer)), "comm_set_trace")

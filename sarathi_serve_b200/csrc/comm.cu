@@ -22,6 +22,7 @@ struct sb200_comm {
   uint64_t seq;
   long long wait_cycles;
   unsigned long long* trace;
+  size_t one_shot_bytes;
 };
 
 namespace sb200 {
@@ -83,7 +84,9 @@ all_reduce_kernel(const __grid_constant__ CommView c, const __grid_constant__ Re
   }
   trace_mark(a, 1);
   __syncthreads();
-  if (threadIdx.x < c.world) signal_push(c, a, threadIdx.x);  // this CTA's rows for every owner are stored
+  // this CTA's share of the rows is stored: one arrival per owner (or one in all for a one-shot call)
+  if (a.one_shot) { if (threadIdx.x == 0) signal_push_all(c, a); }
+  else if (threadIdx.x < c.world) signal_push(c, a, threadIdx.x);
   reduce_phase<T, kMaxVecPerLaneAllReduce>(c, a, blockIdx.x, gridDim.x);
   trace_mark(a, 4);
   gather_phase<T>(c, a, blockIdx.x, gridDim.x);
@@ -132,6 +135,9 @@ static int plan_call(sb200_comm* c, int64_t T_, int64_t H, int dtype, const void
   a = ReduceArgs{};
   a.T = (int)T_; a.H = (int)H; a.rows_per_rank = rpr;
   a.set = (int)(c->seq & 1);
+  // one-shot while the rows every rank would have to load stay below ~4 MB (always with two ranks,
+  // where both schemes move the same bytes); the owner-reduce + gather scheme above that
+  a.one_shot = (c->world == 1 || (size_t)(c->world - 1) * T_ * H * es <= c->one_shot_bytes) ? 1 : 0;
   a.bias = bias; a.residual = residual; a.norm_w = norm_w; a.eps = eps;
   a.write_resid_all = write_resid_all;
   a.out_copy = out_copy; a.resid_copy = resid_copy;
@@ -163,7 +169,7 @@ static int do_all_reduce(sb200_comm* c, const void* in, int64_t T_, int64_t H, i
   if (rc) return rc;
   SB_CHECK_ARG(in && aligned16(in), "all_reduce: input must be a 16-byte aligned device pointer");
   const int grid = all_reduce_grid(T_, H, dtype, p.ra.rows_per_rank);
-  for (int o = 0; o < c->world; ++o) p.ra.push_expected[o] = (uint32_t)grid;  // every CTA reports once per owner
+  for (int o = 0; o < c->world; ++o) p.ra.push_expected[o] = (uint32_t)grid;  // every CTA reports once (per owner)
   commit_call(c, &p, out_ptr, resid_ptr);
   SB_DISPATCH_FLOAT(dtype, return (launch_all_reduce<scalar_t>(p, in, rows_per_token, grid, s)));
   return SB200_OK;
@@ -189,6 +195,8 @@ static int comm_new(sb200_comm** out, int rank, int world, int64_t region_bytes)
   c->region_bytes = round_up((size_t)region_bytes, 1024);
   c->heap_bytes = kCounterBytes + kRegions * c->region_bytes;
   c->wait_cycles = ptx::kWaitLimitCycles;
+  c->one_shot_bytes = 4u << 20;
+  if (const char* e = getenv("SB200_ONE_SHOT_BYTES")) c->one_shot_bytes = (size_t)atoll(e);
   if (cudaGetDevice(&c->device) != cudaSuccess) { delete c; set_error("comm_create: no current CUDA device"); return SB200_ERR_CUDA; }
   *out = c;
   return SB200_OK;
@@ -265,6 +273,12 @@ extern "C" int64_t sb200_comm_region_bytes(sb200_comm* c) { return c ? (int64_t)
 extern "C" int sb200_comm_set_wait_limit(sb200_comm* c, int64_t cycles) {
   SB_CHECK_ARG(c && cycles > 0, "comm_set_wait_limit: bad arguments");
   c->wait_cycles = cycles;
+  return SB200_OK;
+}
+
+extern "C" int sb200_comm_set_one_shot_bytes(sb200_comm* c, int64_t bytes) {
+  SB_CHECK_ARG(c && bytes >= 0, "comm_set_one_shot_bytes: bad arguments");
+  c->one_shot_bytes = (size_t)bytes;
   return SB200_OK;
 }
 
@@ -346,6 +360,7 @@ extern "C" int sb200_gemm_rowpar(sb200_comm* comm, const void* x, int64_t ldx, c
     const int64_t lo = (int64_t)o * rpr, hi = (lo + rpr < T ? lo + rpr : T);
     p.ra.push_expected[o] = gemm_push_increments(plan, T, lo, hi);
   }
+  if (p.ra.one_shot) p.ra.push_expected[0] = gemm_push_increments(plan, T, 0, T);  // one arrival per finished (tile, 32-row slot)
   GemmArgs g = {};
   g.M = (int)T; g.N = (int)N; g.K = (int)K;
   g.head_size = 128;

@@ -129,6 +129,9 @@ struct ReduceArgs {
   int T, H;               // rows of the whole batch, row length
   int rows_per_rank;      // ownership granule: owner(t) = t / rows_per_rank
   int set;                // call parity
+  int one_shot;           // 1: every rank loads ALL partial rows and finishes all T rows itself (one flag wait and one
+                          // trip over the links instead of two; pays off while (world-1)*T*H bytes is small); 0: rows
+                          // are reduced by their owners and gathered afterwards
   uint32_t push_expected[kMaxRanks];  // arrivals this rank's own kernel reports per destination owner
                                       // (epilogue warp-tiles of the GEMM, or CTAs of the all-reduce)
   const void* bias;       // [H] or null, added after the sum (reference: layers.py:448-453)
@@ -166,6 +169,17 @@ __device__ __forceinline__ void signal_push(const CommView& c, const ReduceArgs&
   if (n == a.push_expected[owner])
     st_release(comm_counter(c, owner, (a.set ? CC_PUSH_FLAG1 : CC_PUSH_FLAG0) + c.rank), call_epoch(c, a), c.world > 1);
 }
+// One-shot calls: every rank needs all rows, so the arrivals are counted in one counter
+// (push_expected[0] = all arrivals of this rank's kernel) and the last one flags every rank.
+__device__ __forceinline__ void signal_push_all(const CommView& c, const ReduceArgs& a) {
+  const uint32_t n = arrive_acq_rel(comm_counter(c, c.rank, CC_LOCAL_PUSH)) + 1u;
+  if (n == a.push_expected[0]) {
+    const uint32_t epoch = call_epoch(c, a);
+    const int flag = (a.set ? CC_PUSH_FLAG1 : CC_PUSH_FLAG0) + c.rank;
+    for (int d = 1; d < c.world; ++d) st_release(comm_counter(c, (c.rank + d) % c.world, flag), epoch, true);
+    st_release(comm_counter(c, c.rank, flag), epoch, false);
+  }
+}
 
 // Primary result = rms_norm(z)*w when norm_w is set, else z, kept in the `out` region; z is
 // additionally kept in the `resid` region when a norm is applied (so the caller gets both the
@@ -196,15 +210,32 @@ __device__ __forceinline__ void team_barrier(int id, int threads) {
 
 template <typename T, int VPL>
 __device__ __forceinline__ void reduce_rows(const CommView& c, const ReduceArgs& a, int gteam, int num_teams, int tw,
-                                            int team, int wt, int lane, int warp, int nrows, float* s_ss) {
+                                            int team, int wt, int lane, int warp, int row0, int nrows, float* s_ss) {
   constexpr int N = Vec16<T>::N;
   constexpr int SB = VPL <= 2 ? 8 : 8 / VPL;  // source ranks whose loads are issued together (8-16 vectors in flight per lane)
   const int nvec = a.H / N;
-  const int row0 = c.rank * a.rows_per_rank;
   const T* bias = (const T*)a.bias;
   const T* resid = (const T*)a.residual;
   const T* nw = (const T*)a.norm_w;
   const int vstep = 32 * tw, vbase = wt * 32 + lane;
+  // When all source ranks fit in one batch of loads, the partials of a team's NEXT row are requested
+  // while the current row is normalised and stored, so a team with several rows pays the trip over
+  // the links once.
+  const bool prefetch = c.world <= SB;
+  Vec16<T> x[SB][VPL];
+  auto load_batch = [&](int s0, size_t row_off) {
+#pragma unroll
+    for (int i = 0; i < SB; ++i)
+      if (s0 + i < c.world) {
+        const T* p = (const T*)(c.heap[s0 + i] + c.partial_off[a.set]) + row_off;
+#pragma unroll
+        for (int b = 0; b < VPL; ++b) {
+          const int v = vbase + vstep * b;
+          if (v < nvec) x[i][b] = ldcg16(p + (size_t)v * N);
+        }
+      }
+  };
+  if (prefetch && gteam < nrows) load_batch(0, (size_t)(row0 + gteam) * a.H);
   for (int lr = gteam; lr < nrows; lr += num_teams) {
     const size_t row_off = (size_t)(row0 + lr) * a.H;
     float acc[VPL][N];
@@ -217,17 +248,7 @@ __device__ __forceinline__ void reduce_rows(const CommView& c, const ReduceArgs&
       if (resid && v < nvec) rv[b] = ld16(resid + row_off + (size_t)v * N);
     }
     for (int s0 = 0; s0 < c.world; s0 += SB) {
-      Vec16<T> x[SB][VPL];
-#pragma unroll
-      for (int i = 0; i < SB; ++i)
-        if (s0 + i < c.world) {
-          const T* p = (const T*)(c.heap[s0 + i] + c.partial_off[a.set]) + row_off;
-#pragma unroll
-          for (int b = 0; b < VPL; ++b) {
-            const int v = vbase + vstep * b;
-            if (v < nvec) x[i][b] = ldcg16(p + (size_t)v * N);
-          }
-        }
+      if (!prefetch) load_batch(s0, row_off);
 #pragma unroll
       for (int i = 0; i < SB; ++i)
         if (s0 + i < c.world) {
@@ -239,6 +260,7 @@ __device__ __forceinline__ void reduce_rows(const CommView& c, const ReduceArgs&
             }
         }
     }
+    if (prefetch && lr + num_teams < nrows) load_batch(0, (size_t)(row0 + lr + num_teams) * a.H);
     // z = round(round(sum + bias) + residual)
     Vec16<T> z[VPL];
     float ss = 0.f;
@@ -301,8 +323,8 @@ __device__ void reduce_phase(const CommView& c, const ReduceArgs& a, int cta, in
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   if (warp >= kReduceWarps) return;
   const bool sys = c.world > 1;
-  const int row0 = c.rank * a.rows_per_rank;
-  const int nrows = max(0, min(a.rows_per_rank, a.T - row0));
+  const int row0 = a.one_shot ? 0 : c.rank * a.rows_per_rank;
+  const int nrows = a.one_shot ? a.T : max(0, min(a.rows_per_rank, a.T - row0));
   if (nrows == 0) return;  // owns nothing: nobody waits for this rank's done flag
   const int nvec = a.H / N;
   // team width: what the row needs to fit in registers, then as many warps as the grid can spare
@@ -332,10 +354,11 @@ __device__ void reduce_phase(const CommView& c, const ReduceArgs& a, int cta, in
     //  results are not to be used -- so that every rank keeps counting the same arrivals)
   }
   if (gteam >= nrows) return;
-  if (vpl <= 1) reduce_rows<T, 1>(c, a, gteam, num_teams, tw, team, wt, lane, warp, nrows, s_ss);
-  else if (vpl <= 2) reduce_rows<T, 2>(c, a, gteam, num_teams, tw, team, wt, lane, warp, nrows, s_ss);
-  else if (vpl <= 4 || MAXVPL <= 4) reduce_rows<T, 4>(c, a, gteam, num_teams, tw, team, wt, lane, warp, nrows, s_ss);
-  else reduce_rows<T, (MAXVPL > 4 ? 8 : 4)>(c, a, gteam, num_teams, tw, team, wt, lane, warp, nrows, s_ss);
+  if (vpl <= 1) reduce_rows<T, 1>(c, a, gteam, num_teams, tw, team, wt, lane, warp, row0, nrows, s_ss);
+  else if (vpl <= 2) reduce_rows<T, 2>(c, a, gteam, num_teams, tw, team, wt, lane, warp, row0, nrows, s_ss);
+  else if (vpl <= 4 || MAXVPL <= 4) reduce_rows<T, 4>(c, a, gteam, num_teams, tw, team, wt, lane, warp, row0, nrows, s_ss);
+  else reduce_rows<T, (MAXVPL > 4 ? 8 : 4)>(c, a, gteam, num_teams, tw, team, wt, lane, warp, row0, nrows, s_ss);
+  if (a.one_shot) return;  // every rank has finished all rows itself: nothing to tell, nothing to gather
   // publish: the team is counted locally (a release increment after the team's barrier covers the
   // stores of all its warps), and the team that completes the count tells every peer, with one remote
   // release store each, that this rank's rows are done
@@ -358,7 +381,7 @@ __device__ void gather_phase(const CommView& c, const ReduceArgs& a, int cta, in
   constexpr int U = 8;
   __shared__ int s_ok;
   const int others = c.world - 1;
-  if (others == 0) return;
+  if (others == 0 || a.one_shot) return;
   const int nvec = a.H / N;
   const uint32_t epoch = call_epoch(c, a);
   const int groups = min(others, num_ctas);

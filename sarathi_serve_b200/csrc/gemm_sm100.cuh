@@ -412,8 +412,9 @@ __device__ __forceinline__ RowCtx<T> make_row_ctx(const GemmArgs& g, const CommV
 // region (called by one lane after a __syncwarp of the storing warp): one arrival per owner of those rows.
 __device__ __forceinline__ void push_rows_done(const CommView& comm, const ReduceArgs& red, const GemmArgs& g, int r_lo) {
   const int r_hi = min(g.M, r_lo + 32) - 1;
-  if (r_hi >= r_lo)
-    for (int o = r_lo / red.rows_per_rank; o <= r_hi / red.rows_per_rank; ++o) signal_push(comm, red, o);
+  if (r_hi < r_lo) return;
+  if (red.one_shot) { signal_push_all(comm, red); return; }
+  for (int o = r_lo / red.rows_per_rank; o <= r_hi / red.rows_per_rank; ++o) signal_push(comm, red, o);
 }
 
 // ---------------------------------------------------------------------------

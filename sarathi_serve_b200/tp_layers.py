@@ -185,13 +185,15 @@ class RowParallelLinear(torch.nn.Module):
         context (valid until the second-next collective)."""
         assert self.input_is_parallel and self.reduce_results
         add_bias = self.bias if (self.bias is not None and not self.skip_bias_add) else None
-        if self.world_size == 1 and residual is not None and norm_weight is not None:
-            # Nothing to exchange: the plain GEMM followed by the one-pass add + RMSNorm kernel is faster
+        if self.world_size == 1 and residual is not None:
+            # Nothing to exchange: the plain GEMM followed by the one-pass add (+ RMSNorm) kernel is faster
             # than the in-kernel tail, whose rows have to wait for every column tile of the GEMM.
             from . import layernorm_ops
             prod = dense_ops.linear(input_, self.weight, add_bias,
                                     tile_n=dense_ops.tuned_cfg("store", input_.shape[0], self.weight.shape[0],
                                                                self.weight.shape[1], input_.dtype))
+            if norm_weight is None:
+                return torch.add(residual, prod, out=out), None
             y = out if out is not None else torch.empty_like(prod)
             z = resid_out if resid_out is not None else torch.empty_like(prod)
             layernorm_ops.fused_add_rms_norm(y, z, prod, residual, norm_weight, eps)

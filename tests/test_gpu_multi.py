@@ -71,9 +71,12 @@ def _run(fn_name, port, world):
 def _body_all_reduce(rank, world):
     from sarathi_serve_b200 import parallel_state as ps
     comm = ps.get_tensor_model_parallel_comm(64 << 20)
-    for dtype, tol in ((torch.bfloat16, 1e-2), (torch.float32, 1e-5), (torch.float16, 2e-3)):
+    for dtype, tol, one_shot in ((torch.bfloat16, 1e-2, None), (torch.bfloat16, 1e-2, 0), (torch.float32, 1e-5, None),
+                                 (torch.float16, 2e-3, None), (torch.float16, 2e-3, 1 << 30)):
         if world > 2 and dtype == torch.float16:
             continue  # larger groups: a reduced set keeps the multi-GPU run short
+        # both schemes whatever the size: None = the library's threshold, 0 = never one-shot, 1 GiB = always
+        comm.set_one_shot_bytes((4 << 20) if one_shot is None else one_shot)
         for T, H in ((512, 4096), (288, 1024), (7, 256), (1, 64), (65, 8192)):
             g = torch.Generator().manual_seed(T * 7 + H)
             parts = [torch.randn(T, H, generator=g).to(dtype) for _ in range(world)]
@@ -108,7 +111,9 @@ def _body_all_reduce(rank, world):
 def _body_rowpar(rank, world):
     from sarathi_serve_b200 import parallel_state as ps
     comm = ps.get_tensor_model_parallel_comm(64 << 20)
-    for dtype, tol in ((torch.bfloat16, 1e-2), (torch.float16, 2e-3), (torch.float32, 2e-5)):
+    for dtype, tol, one_shot in ((torch.bfloat16, 1e-2, 4 << 20), (torch.bfloat16, 1e-2, 0), (torch.float16, 2e-3, 1 << 30),
+                                 (torch.float32, 2e-5, 4 << 20)):
+        comm.set_one_shot_bytes(one_shot)  # the library's threshold / never one-shot / always one-shot
         for T, H, K in ((512, 4096, 1024), (288, 1024, 704), (65, 256, 64), (1, 128, 512), (130, 4096, 7168)):
             for tile_n in (0, 128, 2256, 302128, 3256, 203128, 4256, 204128):
                 if dtype == torch.float32 and tile_n != 0:
