@@ -53,6 +53,26 @@ def workload_text(name: str, world: int) -> str:
             f"512-token mixed chunk (448 prefill + 64 decode), TP={world}, attention stand-in attn_out=q")
 
 
+NVLINK_GBS = 770.0  # measured peer-copy bandwidth per direction on this pool's B200s (nominal 900)
+
+
+def layer_roofline(case, T: int, world: int, peak_tf: float, peak_hbm: float) -> dict:
+    """Lower bound of one layer step per GPU: the slowest of dense FLOPs at the bf16 peak, bytes at the HBM
+    copy bandwidth (each tensor crossing HBM once) and all-reduce bytes at the NVLink bandwidth
+    (2 all-reduces x 2 (tp-1)/tp T H s per direction)."""
+    H, I, hd = case.hidden_size, case.intermediate_size, case.head_dim
+    nq, nkv, s = case.num_heads, case.num_kv_heads, 2
+    flops = 2.0 * T * H * ((nq + 2 * nkv) * hd + nq * hd + 3 * I) / world
+    hbm = s * H * ((nq + 2 * nkv) * hd + nq * hd + 3 * I) / world + s * T * (
+        2 * H + (nq + 2 * nkv) * hd / world + nq * hd / world + 2 * I / world + 2 * H + 4 * H)
+    nvl = 2 * 2.0 * (world - 1) / world * T * H * s
+    t = {"compute_us": flops / (peak_tf * 1e12) * 1e6, "hbm_us": hbm / (peak_hbm * 1e9) * 1e6,
+         "nvlink_us": nvl / (NVLINK_GBS * 1e9) * 1e6}
+    t["t_roof_us"] = max(t.values())
+    t["flops"], t["hbm_bytes"], t["nvlink_bytes_per_direction"] = flops, hbm, nvl
+    return t
+
+
 def parse():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -61,6 +81,9 @@ def parse():
     ap.add_argument("--impl", default="native", choices=["native", "reference"])
     ap.add_argument("--workload", default="config2")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--parts", action="store_true",
+                    help="instead of the step benchmark: time every kernel of the path on its own (CUDA graphs) and "
+                         "print one JSON line of per-kernel times with achieved TFLOP/s, HBM GB/s and NVLink GB/s")
     ap.add_argument("--tune-cache", default=None,
                     help="JSON file of tile configurations: read if present (no tuning launches), else written")
     ap.add_argument("--cpu-baseline-seconds", type=float, default=15.0)
@@ -323,8 +346,9 @@ def run_native(a):
         ms_e2e = max_over_ranks((time.perf_counter() - t0) * 1e3 / e2e_steps)
         comm.check_status()
 
-        def graph_ms(fn, n, reps=5):
-            """Mean device time of one fn(i) call: n calls captured in a CUDA graph, replayed reps times."""
+        def graph_ms(fn, n, reps=5, lead_in=True):
+            """Mean device time of one fn(i) call: n calls captured in a CUDA graph, replayed reps times;
+            lead_in: about 0.3 s of the same load first (the power / clock state of a long run)."""
             st = torch.cuda.Stream()
             st.wait_stream(torch.cuda.current_stream())
             with torch.cuda.stream(st):
@@ -343,7 +367,7 @@ def run_native(a):
                 # same thermal / power state as the layer steps: about 0.3 s of load before the timed replays
                 # (the same count on every rank: the replayed graphs may hold collectives)
                 est_ms = max_over_ranks(k0.elapsed_time(k1))
-                for _ in range(min(2000, max(1, int(300.0 / max(1e-3, est_ms))))):
+                for _ in range(min(2000, max(1, int(300.0 / max(1e-3, est_ms)))) if lead_in else 0):
                     g_.replay()
                 k0.record(st)
                 for _ in range(reps):
@@ -355,7 +379,8 @@ def run_native(a):
 
         # ---- dominant kernel alone: gate_up GEMM + SiLU*mul (weights cycled like in the layer steps)
         gu = [l.mlp.gate_up_proj for l in layers]
-        ms_kernel = graph_ms(lambda i: gu[i % n_layers].forward_silu_mul(normed0), 2 * n_layers)
+        # timed alone, without the lead-in: the figure that goes against the burst peak
+        ms_kernel = graph_ms(lambda i: gu[i % n_layers].forward_silu_mul(normed0), 2 * n_layers, lead_in=False)
 
         # ---- the reference's GPU sequence on this box, for comparison: cuBLAS GEMMs (torch.matmul), the
         # separate rotary / SiLU*mul / add+RMSNorm kernels and an NCCL all-reduce after each row-parallel GEMM
@@ -416,6 +441,10 @@ def run_native(a):
                              # DRAM bytes per launch from the committed ncu capture of this kernel (TP=1 workload)
                              "traffic": GATE_UP_TP1_DRAM_BYTES if (world == 1 and a.workload == "config2") else None,
                              "algorithmic_bytes": 2 * d * H * es + T * H * es + T * d * es},
+                "layer_roofline": dict(layer_roofline(case, T, world, peak_tf, peak_hbm),
+                                       frac=layer_roofline(case, T, world, peak_tf, peak_hbm)["t_roof_us"] / (ms_resident * 1e3),
+                                       peaks=f"{peak_src}: {peak_tf} TFLOP/s bf16 burst, {peak_hbm} GB/s HBM; NVLink "
+                                             f"{NVLINK_GBS} GB/s per direction (measured peer copy)"),
                 "gpu_comparison": ({"what": "same step as cuBLAS GEMMs (torch.matmul) + separate rotary / SiLU*mul / "
                                             "add+RMSNorm kernels" + (" + NCCL all-reduce" if world > 1 else "") +
                                             ", one CUDA graph", "ms_per_step": ms_cublas,
@@ -433,10 +462,171 @@ def run_native(a):
         dist.destroy_process_group()
 
 
+def run_parts(a):
+    """Per-kernel device times of the path (each kernel alone, back-to-back launches in one CUDA graph with
+    the weights of several layers cycled), with the achieved rate against the roofline that bounds it."""
+    import torch
+    import torch.distributed as dist
+    from sarathi_serve_b200 import (activation_ops, dense_ops, layernorm_ops, moe_ops, parallel_state as ps,
+                                    pos_encoding_ops, synthetic as S)
+    from sarathi_serve_b200.decoder_layer import LlamaDecoderLayer
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("cpu:gloo,cuda:nccl", rank=rank, world_size=world, device_id=dev)
+    ps.initialize_model_parallel(world)
+    case = S.CASES[a.workload]
+    T, H, es = case.num_tokens, case.hidden_size, 2
+    comm = ps.get_tensor_model_parallel_comm(max(64 << 20, -(-T // world) * world * H * es))
+    torch.set_default_dtype(case.dtype)
+    t = S.generate(case)
+    params = S.shard(t, rank, world)
+    per_layer_bytes = sum(v.numel() for k, v in params.items() if "proj" in k) * es
+    nl = max(2, -(-2 * L2_BYTES // per_layer_bytes))
+    layers = []
+    for i in range(nl):
+        layer = LlamaDecoderLayer(case.hf_config(), layer_id=i)
+        S.load_layer(layer, params)
+        layers.append(layer)
+    x = t.x.to(case.dtype).to(dev)
+    pos = t.positions.to(dev)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def graph_us(fn, n=None, reps=5):
+        n = n or 2 * nl
+        st = torch.cuda.Stream()
+        st.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(st):
+            for i in range(3):
+                fn(i)
+            barrier()
+            g_ = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g_, stream=st):
+                for i in range(n):
+                    fn(i)
+            g_.replay()
+            barrier()
+            k0, k1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            k0.record(st)
+            for _ in range(reps):
+                g_.replay()
+            k1.record(st)
+            barrier()
+        torch.cuda.current_stream().wait_stream(st)
+        v = torch.tensor([k0.elapsed_time(k1) / (n * reps) * 1e3], dtype=torch.float64, device=dev)
+        if world > 1:
+            dist.all_reduce(v, op=dist.ReduceOp.MAX)
+        return float(v.item())
+
+    peak_tf, peak_hbm, peak_src = peaks()
+    nq, nkv, hd, I = case.num_heads, case.num_kv_heads, case.head_dim, case.intermediate_size
+    qkv_n, d = (nq + 2 * nkv) * hd // world, I // world
+    out = {}
+
+    def gemm_entry(name, us, flops, extra=None):
+        e = {"us": us, "tflops": flops / us / 1e6, "frac_of_bf16_peak": flops / us / 1e6 / peak_tf}
+        e.update(extra or {})
+        out[name] = e
+
+    def hbm_entry(name, us, nbytes):
+        out[name] = {"us": us, "bytes": nbytes, "hbm_gbs": nbytes / us / 1e3, "frac_of_hbm_peak": nbytes / us / 1e3 / peak_hbm}
+
+    with torch.inference_mode():
+        cache = a.tune_cache and f"{a.tune_cache}.tp{world}"
+        if cache and os.path.exists(cache):
+            dense_ops.load_tuned(cache)
+        layers[0].tune(T)
+        if cache and rank == 0 and not os.path.exists(cache):
+            dense_ops.save_tuned(cache)
+        barrier()
+        l0 = layers[0]
+        sa = l0.self_attn
+        normed = l0.input_layernorm(x)
+        q, k, v = sa.qkv_rotary(pos, normed)
+        nw = l0.post_attention_layernorm.weight.data
+        h, resid = sa.o_proj.forward_fused(q, x, nw, 1e-5)
+        h, resid = h.clone(), resid.clone()
+        act = l0.mlp.gate_up_proj.forward_silu_mul(h)
+        ar_bytes = 2.0 * (world - 1) / world * T * H * es  # per direction, per GPU
+        gemm_entry("qkv_gemm+rotary", graph_us(lambda i: layers[i % nl].self_attn.qkv_rotary(pos, normed)), 2.0 * T * H * qkv_n)
+        us = graph_us(lambda i: layers[i % nl].self_attn.o_proj.forward_fused(q, x, nw, 1e-5))
+        gemm_entry("o_proj_gemm+allreduce+add+rmsnorm", us, 2.0 * T * H * nq * hd / world,
+                   {"nvlink_gbs_per_direction": ar_bytes / us / 1e3 if world > 1 else None})
+        gemm_entry("gate_up_gemm+silu_mul", graph_us(lambda i: layers[i % nl].mlp.gate_up_proj.forward_silu_mul(h)), 2.0 * T * H * 2 * d)
+        us = graph_us(lambda i: layers[i % nl].mlp.down_proj.forward_fused(act, resid, nw, 1e-5))
+        gemm_entry("down_gemm+allreduce+add+rmsnorm", us, 2.0 * T * H * d,
+                   {"nvlink_gbs_per_direction": ar_bytes / us / 1e3 if world > 1 else None})
+        gemm_entry("o_proj_gemm_alone", graph_us(lambda i: dense_ops.linear(q, layers[i % nl].self_attn.o_proj.weight)), 2.0 * T * H * nq * hd / world)
+        gemm_entry("down_gemm_alone", graph_us(lambda i: dense_ops.linear(act, layers[i % nl].mlp.down_proj.weight)), 2.0 * T * H * d)
+        if world > 1:
+            us = graph_us(lambda i: comm.all_reduce(h, residual=x, norm_weight=nw, eps=1e-5))
+            out["allreduce+add+rmsnorm_alone"] = {"us": us, "nvlink_bytes_per_direction": ar_bytes,
+                                                   "nvlink_gbs_per_direction": ar_bytes / us / 1e3,
+                                                   "frac_of_nvlink": ar_bytes / us / 1e3 / NVLINK_GBS}
+            buf = h.clone()
+            us = graph_us(lambda i: dist.all_reduce(buf))
+            out["nccl_allreduce_alone"] = {"us": us, "nvlink_gbs_per_direction": ar_bytes / us / 1e3}
+
+            def ref_tail(xin, wt, res_in):
+                y = torch.matmul(xin, wt.t())
+                dist.all_reduce(y)
+                r_, o_ = torch.empty_like(y), torch.empty_like(y)
+                layernorm_ops.fused_add_rms_norm(o_, r_, y, res_in, nw, 1e-5)
+                return o_
+            out["cublas_o_proj+nccl+add_rmsnorm"] = {"us": graph_us(lambda i: ref_tail(q, layers[i % nl].self_attn.o_proj.weight, x))}
+            out["cublas_down+nccl+add_rmsnorm"] = {"us": graph_us(lambda i: ref_tail(act, layers[i % nl].mlp.down_proj.weight, resid))}
+        # the element-wise kernels on their own (HBM-bound); inputs of a few MB sit in L2, so they can read above the HBM figure
+        o1, o2 = torch.empty_like(x), torch.empty_like(x)
+        hbm_entry("rms_norm", graph_us(lambda i: layernorm_ops.rms_norm(o1, x, nw, 1e-5), n=8), (2 * T * H + H) * es)
+        hbm_entry("fused_add_rms_norm", graph_us(lambda i: layernorm_ops.fused_add_rms_norm(o1, o2, h, x, nw, 1e-5), n=8), (4 * T * H + H) * es)
+        gu = torch.randn(T, 2 * d, device=dev, dtype=torch.float32).to(case.dtype)
+        ao = torch.empty(T, d, device=dev, dtype=case.dtype)
+        hbm_entry("silu_and_mul", graph_us(lambda i: activation_ops.silu_and_mul(ao, gu), n=8), 3 * T * d * es)
+        qkv = torch.randn(T, qkv_n, device=dev, dtype=torch.float32).to(case.dtype)
+        qs, ks, _ = qkv.split([sa.q_size, sa.kv_size, sa.kv_size], dim=-1)
+        cache = sa.rotary_emb.cos_sin_cache
+        hbm_entry("rotary_embedding", graph_us(lambda i: pos_encoding_ops.rotary_embedding(pos, qs, ks, hd, cache, True), n=8),
+                  2 * T * (sa.q_size + sa.kv_size) * es + 8 * T + T * hd * es)
+        E, topk, Tm = 8, 2, 1024
+        logits = torch.randn(Tm, E, device=dev, dtype=torch.float32)
+        tw = torch.empty(Tm, topk, dtype=torch.float32, device=dev)
+        ti = torch.empty(Tm, topk, dtype=torch.int32, device=dev)
+        hbm_entry("topk_softmax", graph_us(lambda i: moe_ops.topk_softmax(tw, ti, None, logits, renormalize=True), n=8), Tm * E * 4 + Tm * topk * 12)
+        blk = 64
+        cap = Tm * topk + E * (blk - 1)
+        sids = torch.empty(cap, dtype=torch.int32, device=dev)
+        eids = torch.empty(-(-cap // blk), dtype=torch.int32, device=dev)
+        npp = torch.empty(1, dtype=torch.int32, device=dev)
+        moe_ops.topk_softmax(tw, ti, None, logits, renormalize=True)
+        hbm_entry("moe_align_block_size", graph_us(lambda i: moe_ops.moe_align_block_size(ti, E, blk, sids, eids, npp), n=8),
+                  4 * Tm * topk + 4 * (cap + cap // blk + 1))
+    comm.check_status()
+    if rank == 0:
+        print(json.dumps({"parts": out, "n_gpus": world, "workload": workload_text(a.workload, world),
+                          "peaks": {"bf16_tflops": peak_tf, "hbm_gbs": peak_hbm, "nvlink_gbs_per_direction": NVLINK_GBS,
+                                    "source": peak_src},
+                          "tile_cfgs": {k_[0] + f"[{k_[2]}x{k_[3]}]": v_ for k_, v_ in dense_ops._tuned.items()}}), flush=True)
+    barrier()
+    ps.destroy_model_parallel()
+    if world > 1:
+        dist.destroy_process_group()
+
+
 def main():
     a = parse()
     if a.impl == "reference":
         run_reference_arm(a)
+    elif a.parts:
+        run_parts(a)
     else:
         run_native(a)
 
