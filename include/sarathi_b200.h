@@ -224,7 +224,7 @@ int sb200_comm_destroy(sb200_comm* comm);
 void* sb200_comm_local_heap(sb200_comm* comm);
 void* sb200_comm_scratch(sb200_comm* comm);
 int64_t sb200_comm_region_bytes(sb200_comm* comm);
-/* Limit of every device-side wait on a peer, in SM clock cycles (default ~2 s). */
+/* Limit of every device-side wait on a peer, in SM clock cycles (default 2e10, about 10 s). */
 int sb200_comm_set_wait_limit(sb200_comm* comm, int64_t cycles);
 /* Collectives whose (world - 1) * T * H * sizeof(dtype) is at most `bytes` run "one-shot": every rank
  * loads all partial rows and finishes all T rows itself (one wait and one trip over the links);

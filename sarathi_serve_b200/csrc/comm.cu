@@ -194,7 +194,7 @@ static int comm_new(sb200_comm** out, int rank, int world, int64_t region_bytes)
   c->rank = rank; c->world = world;
   c->region_bytes = round_up((size_t)region_bytes, 1024);
   c->heap_bytes = kCounterBytes + kRegions * c->region_bytes;
-  c->wait_cycles = ptx::kWaitLimitCycles;
+  c->wait_cycles = 5 * ptx::kWaitLimitCycles;  // ~10 s: ranks of a serving engine can be seconds apart on the host (first steps, GC)
   c->one_shot_bytes = 4u << 20;
   if (const char* e = getenv("SB200_ONE_SHOT_BYTES")) c->one_shot_bytes = (size_t)atoll(e);
   if (cudaGetDevice(&c->device) != cudaSuccess) { delete c; set_error("comm_create: no current CUDA device"); return SB200_ERR_CUDA; }

@@ -26,6 +26,14 @@ def _rel(a, ref):
     return float((a.double().cpu() - ref.double().cpu()).abs().max()) / (d if d > 0 else 1.0)
 
 
+def _host_barrier():
+    """The ranks prepare their inputs on the host at different speeds (seconds apart for the large cases); the
+    device-side waits are bounded, so the ranks meet here before they launch collectives."""
+    import torch.distributed as dist
+    torch.cuda.synchronize()
+    dist.barrier()
+
+
 def _entry(rank, world, port, fn_name, ret):
     try:
         os.environ["MASTER_ADDR"] = "127.0.0.1"
@@ -85,6 +93,7 @@ def _body_all_reduce(rank, world):
             w = (1 + 0.1 * torch.randn(H, generator=g)).to(dtype)
             x = parts[rank].cuda()
             total = sum(p.float() for p in parts)
+            _host_barrier()
             # plain sum, result in a heap view
             y, z = comm.all_reduce(x)
             assert z is None and _rel(y, total) <= tol, ("sum", dtype, T, H)
@@ -131,6 +140,7 @@ def _body_rowpar(rank, world):
                 w = W[:, rank * K:(rank + 1) * K].contiguous().cuda()
                 ref = sum((X[:, r * K:(r + 1) * K].float().cuda() @ W[:, r * K:(r + 1) * K].float().cuda().t())
                           for r in range(world)).cpu()
+                _host_barrier()
                 y, _ = comm.rowpar_linear(x, w, tile_n=tile_n)
                 assert _rel(y, ref) <= tol, ("plain", dtype, T, H, K, tile_n)
                 y, z = comm.rowpar_linear(x, w, residual=resid.cuda(), norm_weight=nw.cuda(), eps=1e-5, tile_n=tile_n)
@@ -164,6 +174,7 @@ def _body_layer(rank, world):
         t = S.generate(case)
         S.load_layer(layer, S.shard(t, rank, world))
         x = t.x.to(case.dtype).cuda()
+        _host_barrier()
         with torch.inference_mode():
             out = layer(t.positions.cuda(), x.clone(), 0, QAttention())
             out_u = layer.forward_unfused(t.positions.cuda(), x.clone(), 0, QAttention())
@@ -209,6 +220,7 @@ def _body_moe(rank, world):
             sd["experts.w13_weight"].copy_(shards[rank]["w13"])
             sd["experts.w2_weight"].copy_(shards[rank]["w2"])
         x = shards[0]["x"]
+        _host_barrier()
         out = moe(x.cuda().clone())
         ps.get_tensor_model_parallel_comm().check_status()
         if rank == 0:
