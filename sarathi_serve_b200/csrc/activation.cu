@@ -34,15 +34,34 @@ silu_and_mul_kernel(T* __restrict__ out, const T* __restrict__ in, int64_t T_, i
   constexpr int N = Vec16<T>::N;
   const int64_t stride = (int64_t)gridDim.x * blockDim.x;
   if constexpr (VEC) {
+    // four vectors per thread and step, all eight loads issued before the first use: the kernel is a pure
+    // stream, so what matters is the number of bytes in flight per SM
+    constexpr int U = 4;
     const int64_t vpr = d / N, total = T_ * vpr;
-    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += stride) {
-      const int64_t t = i / vpr, c = (i - t * vpr) * N;
-      const Vec16<T> g = ld16(in + t * 2 * d + c), u = ld16(in + t * 2 * d + d + c);
-      Vec16<T> o;
+    for (int64_t i0 = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i0 < total; i0 += stride * U) {
+      Vec16<T> g[U], u[U];
+      int64_t off_in[U], off_out[U];
 #pragma unroll
-      for (int j = 0; j < N; ++j)
-        o.v[j] = DT<T>::from_f(silu_mul_op<T>(DT<T>::to_f(g.v[j]), DT<T>::to_f(u.v[j])));
-      st16(out + t * d + c, o);
+      for (int k = 0; k < U; ++k) {
+        const int64_t i = i0 + stride * k;
+        if (i < total) {
+          const int64_t t = i / vpr, c = (i - t * vpr) * N;
+          off_in[k] = t * 2 * d + c;
+          off_out[k] = t * d + c;
+          g[k] = ld16(in + off_in[k]);
+          u[k] = ld16(in + off_in[k] + d);
+        }
+      }
+#pragma unroll
+      for (int k = 0; k < U; ++k) {
+        if (i0 + stride * k < total) {
+          Vec16<T> o;
+#pragma unroll
+          for (int j = 0; j < N; ++j)
+            o.v[j] = DT<T>::from_f(silu_mul_op<T>(DT<T>::to_f(g[k].v[j]), DT<T>::to_f(u[k].v[j])));
+          st16(out + off_out[k], o);
+        }
+      }
     }
   } else {
     const int64_t total = T_ * d;

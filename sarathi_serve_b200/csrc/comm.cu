@@ -1,7 +1,7 @@
 // Tensor-parallel communication context (symmetric heaps mapped between the
-// ranks of one node), the standalone all-reduce built on the push / reduce /
-// finish phases of comm.cuh, and the row-parallel projection entry point that
-// runs the same phases inside the GEMM kernel.
+// ranks of one node), the standalone all-reduce built on the reduce / gather
+// phases of comm.cuh, and the row-parallel projection entry point that runs
+// the same phases inside the GEMM kernel.
 //
 // Replaces the all-reduce call site of the reference,
 // tensor_parallel/mappings.py:16-26 (torch.distributed.all_reduce over NCCL),
@@ -110,8 +110,7 @@ struct CallPlan {
   CommView cv;
 };
 
-// Common argument checks + per-call bookkeeping.  `pushes_to_me` is what every
-// rank adds to this rank's push counter during the call.
+// Common argument checks + per-call bookkeeping.
 static int plan_call(sb200_comm* c, int64_t T_, int64_t H, int dtype, const void* bias, const void* residual,
                      const void* norm_w, float eps, int write_resid_all, void* out_copy, void* resid_copy,
                      CallPlan* p, int max_vec_per_lane = kMaxVecPerLaneAllReduce) {

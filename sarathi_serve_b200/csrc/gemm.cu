@@ -164,7 +164,7 @@ GemmPlan plan_gemm(int epi, int64_t M, int64_t N, int64_t K, int head_size, int 
   return best;
 }
 
-// Increments the row-parallel kernel of every rank adds to the push counter of the rank that owns
+// Arrivals the row-parallel kernel of a rank counts for the rank that owns
 // rows [lo, hi): one per (tile, epilogue slot whose 32 rows overlap the range), times the number of
 // K-parts for tiles that are cut (every part finishes a share of such a tile and reports it).
 uint32_t gemm_push_increments(const GemmPlan& p, int64_t M, int64_t lo, int64_t hi) {
@@ -263,7 +263,6 @@ int run_gemm_sm100(int dtype, int epi, const GemmPlan& plan, const void* x, int6
   g.mi = plan.mi; g.bn = plan.bn; g.units = plan.units; g.tiles_full = plan.tiles_full;
   g.rem_units = plan.rem_units;
   g.l2_prefetch = l2_prefetch_distance();
-  { const char* e = getenv("SB200_DEBUG"); g.debug = e ? atoi(e) : 0; }
   g.stages = plan.stages; g.m_tiles = plan.m_tiles; g.n_tiles = plan.n_tiles; g.k_blocks = plan.k_blocks;
   if (plan.rem_units > (int)((int64_t)plan.m_tiles * plan.n_tiles - plan.tiles_full)) {
     SB_CHECK_ARG(workspace && aligned16(workspace), "cutting tiles along K needs an aligned workspace");

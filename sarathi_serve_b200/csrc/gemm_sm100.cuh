@@ -73,7 +73,6 @@ struct GemmArgs {
   int rem_units;           // units that share the k-blocks of the remaining tiles (= their number: tiles not cut)
   int stages;              // shared-memory ring depth
   int l2_prefetch;         // k-blocks ahead at which the B boxes are prefetched into L2 (0 = off)
-  int debug;               // profiling switches (0 in production)
   int m_tiles, n_tiles, k_blocks;
   // grouped (MoE) mode
   const int32_t* expert_ids;    // [m_tiles] expert of each row block, or null
@@ -532,8 +531,6 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
               ptx::tma_load_2d_pair(sb, &tmap_b, bar, kb * kBK, b_row0 + (int)cta_rank * (g.N / 2) + nt * (BN / 2));
             else
               ptx::tma_load_2d_pair(sb, &tmap_b, bar, kb * kBK, b_row0 + nt * BN + (int)cta_rank * (BN / 2));
-          } else if (g.debug & 8) {
-            ptx::mbar_arrive(&full_bar[stage]);  // profiling: no loads, the MMAs run on whatever the stage holds
           } else {
             ptx::mbar_expect_tx(&full_bar[stage], (uint32_t)stage_bytes);
 #pragma unroll
@@ -582,7 +579,6 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
             for (int a = 0; a < MI; ++a) {
               const uint64_t da = ptx::make_smem_desc_sw128(sa + a * (128 * kBK * 2));
               if (CTA2) ptx::umma_f16_pair(d_tmem + (uint32_t)(a * BN), da + (uint64_t)(k * 2), db + (uint64_t)(k * 2), idesc, acc);
-              else if (g.debug & 16) {}  // profiling: loads only
               else ptx::umma_f16(d_tmem + (uint32_t)(a * BN), da + (uint64_t)(k * 2), db + (uint64_t)(k * 2), idesc, acc);
             }
           }
@@ -634,7 +630,6 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
           for (int c = 0; c < nch; ++c) {
             float f[32];
             tsrc.load32(cols[c], f);
-            if (g.debug & 1) continue;
             float* p = ws_row + (size_t)cols[c] * BM;
 #pragma unroll
             for (int j = 0; j < 32; ++j) __stcg(p + (size_t)j * BM, f[j]);
@@ -681,7 +676,7 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
       if (!arrived) { ok = false; break; }
       const int n0 = nt * (EPI == EPI_SILU_MUL ? BN / 2 : BN);
       const RowCtx<T> rc = make_row_ctx<T, EPI>(g, comm, red, mt * BM + row_in_tile, n0);
-      if (!(g.debug & 2)) {
+      {
         const int my_part = sg.part_slot - sg.first_slot;
         const WorkspaceSource wsrc{g.ws + (size_t)sg.first_slot * BM * BN + row_in_tile, (size_t)BM * BN, BM, S};
         int k = 0;

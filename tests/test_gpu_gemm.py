@@ -17,6 +17,39 @@ def _rand(shape, dtype, seed, scale=1.0):
     return (torch.randn(*shape, generator=g) * scale).to(dtype)
 
 
+# Per-rank shapes of the 70B-shaped layer at TP=8 (hidden 8192, 64 q / 8 kv heads, intermediate 28672;
+# T = 512): qkv N=1280, o_proj K=1024, gate_up N=7168 (d=3584), down K=3584.
+def test_70b_shaped_tp8_shard_projections():
+    T, H = 512, 8192
+    dtype = torch.bfloat16
+    x = _rand((T, H), dtype, 11)
+    # qkv + rotary: 8 q heads + 1 k head rotated, 1 v head untouched
+    wqkv = _rand((1280, H), dtype, 12, 0.02)
+    pos = torch.arange(T, dtype=torch.int64) * 5 % 4096
+    cache = O.cos_sin_cache(128, 128, 8192, 500000.0, dtype)
+    ref = (x.float() @ wqkv.float().t()).to(dtype)
+    q, k = ref[:, :1024].clone(), ref[:, 1024:1152].clone()
+    O.rotary_embedding(pos, q, k, 128, cache, True)
+    out = dense_ops.linear_rotary(x.cuda(), wqkv.cuda(), pos.cuda(), cache.cuda(), 128, 1152, True)
+    _check_status()
+    assert rel_err(out[:, :1024].float().cpu(), q.float()) <= 2e-2
+    assert rel_err(out[:, 1024:1152].float().cpu(), k.float()) <= 2e-2
+    assert rel_err(out[:, 1152:].float().cpu(), ref[:, 1152:].float()) <= 2e-2
+    # gate_up + SiLU*mul
+    wgu = _rand((7168, H), dtype, 13, 0.02)
+    gu = (x.float() @ wgu.float().t()).to(dtype)
+    act_ref = O.silu_and_mul(gu)
+    act = dense_ops.linear_silu_mul(x.cuda(), wgu.cuda())
+    _check_status()
+    assert rel_err(act.float().cpu(), act_ref.float()) <= 2e-2
+    # o_proj / down shards (K = 1024, 3584), output rows of 16 KiB
+    for K, seed in ((1024, 14), (3584, 15)):
+        a, w = _rand((T, K), dtype, seed), _rand((H, K), dtype, seed + 10, 0.02)
+        y = dense_ops.linear(a.cuda(), w.cuda())
+        _check_status()
+        assert rel_err(y.float().cpu(), a.float() @ w.float().t()) <= 2e-2
+
+
 def _check_status():
     from sarathi_serve_b200 import dense_ops
     dense_ops.check_status(torch.device("cuda", torch.cuda.current_device()))

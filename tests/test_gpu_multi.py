@@ -123,7 +123,7 @@ def _body_rowpar(rank, world):
     for dtype, tol, one_shot in ((torch.bfloat16, 1e-2, 4 << 20), (torch.bfloat16, 1e-2, 0), (torch.float16, 2e-3, 1 << 30),
                                  (torch.float32, 2e-5, 4 << 20)):
         comm.set_one_shot_bytes(one_shot)  # the library's threshold / never one-shot / always one-shot
-        for T, H, K in ((512, 4096, 1024), (288, 1024, 704), (65, 256, 64), (1, 128, 512), (130, 4096, 7168)):
+        for T, H, K in ((512, 4096, 1024), (288, 1024, 704), (65, 256, 64), (1, 128, 512), (130, 4096, 7168), (96, 8192, 256)):
             for tile_n in (0, 128, 2256, 302128, 3256, 203128, 4256, 204128):
                 if dtype == torch.float32 and tile_n != 0:
                     continue
