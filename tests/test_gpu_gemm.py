@@ -20,6 +20,7 @@ def _rand(shape, dtype, seed, scale=1.0):
 # Per-rank shapes of the 70B-shaped layer at TP=8 (hidden 8192, 64 q / 8 kv heads, intermediate 28672;
 # T = 512): qkv N=1280, o_proj K=1024, gate_up N=7168 (d=3584), down K=3584.
 def test_70b_shaped_tp8_shard_projections():
+    from sarathi_serve_b200 import dense_ops
     T, H = 512, 8192
     dtype = torch.bfloat16
     x = _rand((T, H), dtype, 11)
