@@ -85,7 +85,7 @@ all_reduce_kernel(const __grid_constant__ CommView c, const __grid_constant__ Re
   trace_mark(a, 1);
   __syncthreads();
   // this CTA's share of the rows is stored: one arrival per owner (or one in all for a one-shot call)
-  if (a.one_shot) { if (threadIdx.x == 0) signal_push_all(c, a); }
+  if (a.one_shot) { if (threadIdx.x < 32) signal_push_all(c, a); }
   else if (threadIdx.x < c.world) signal_push(c, a, threadIdx.x);
   reduce_phase<T, kMaxVecPerLaneAllReduce>(c, a, blockIdx.x, gridDim.x);
   trace_mark(a, 4);

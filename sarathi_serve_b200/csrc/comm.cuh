@@ -171,14 +171,18 @@ __device__ __forceinline__ void signal_push(const CommView& c, const ReduceArgs&
 }
 // One-shot calls: every rank needs all rows, so the arrivals are counted in one counter
 // (push_expected[0] = all arrivals of this rank's kernel) and the last one flags every rank.
+// Called by ALL lanes of a converged warp after its stores (and, for a CTA-wide share, a
+// __syncthreads): lane 0 counts the arrival; when it completes the count, lanes 0..world-1 store one
+// rank's flag each, so the fan-out costs one release, not world of them in a row.
 __device__ __forceinline__ void signal_push_all(const CommView& c, const ReduceArgs& a) {
-  const uint32_t n = arrive_acq_rel(comm_counter(c, c.rank, CC_LOCAL_PUSH)) + 1u;
-  if (n == a.push_expected[0]) {
-    const uint32_t epoch = call_epoch(c, a);
-    const int flag = (a.set ? CC_PUSH_FLAG1 : CC_PUSH_FLAG0) + c.rank;
-    for (int d = 1; d < c.world; ++d) st_release(comm_counter(c, (c.rank + d) % c.world, flag), epoch, true);
-    st_release(comm_counter(c, c.rank, flag), epoch, false);
-  }
+  const int lane = threadIdx.x & 31;
+  __syncwarp();
+  uint32_t n = 0;
+  if (lane == 0) n = arrive_acq_rel(comm_counter(c, c.rank, CC_LOCAL_PUSH)) + 1u;
+  n = __shfl_sync(0xffffffffu, n, 0);  // (also orders lane 0's acquire before the other lanes' stores)
+  if (n == a.push_expected[0] && lane < c.world)
+    st_release(comm_counter(c, lane, (a.set ? CC_PUSH_FLAG1 : CC_PUSH_FLAG0) + c.rank), call_epoch(c, a),
+               lane != c.rank);
 }
 
 // Primary result = rms_norm(z)*w when norm_w is set, else z, kept in the `out` region; z is

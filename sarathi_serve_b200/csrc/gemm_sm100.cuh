@@ -408,12 +408,14 @@ __device__ __forceinline__ RowCtx<T> make_row_ctx(const GemmArgs& g, const CommV
 }
 
 // Row-parallel projection: the 32 rows starting at r_lo of some tile are final in this rank's partial
-// region (called by one lane after a __syncwarp of the storing warp): one arrival per owner of those rows.
+// region.  Called by all lanes of the storing warp: one arrival per owner of those rows.
 __device__ __forceinline__ void push_rows_done(const CommView& comm, const ReduceArgs& red, const GemmArgs& g, int r_lo) {
   const int r_hi = min(g.M, r_lo + 32) - 1;
-  if (r_hi < r_lo) return;
+  if (r_hi < r_lo) return;  // warp-uniform
   if (red.one_shot) { signal_push_all(comm, red); return; }
-  for (int o = r_lo / red.rows_per_rank; o <= r_hi / red.rows_per_rank; ++o) signal_push(comm, red, o);
+  __syncwarp();
+  if ((threadIdx.x & 31) == 0)
+    for (int o = r_lo / red.rows_per_rank; o <= r_hi / red.rows_per_rank; ++o) signal_push(comm, red, o);
 }
 
 // ---------------------------------------------------------------------------
@@ -648,7 +650,7 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
         if (S > 1) arrive_acq_rel(g.ws_counters + (size_t)sg.rem_index * 32 + slot);
       }
       if constexpr (EPI == EPI_PUSH) {
-        if (S == 1 && lane == 0) push_rows_done(comm, red, g, mt * BM + row_in_tile - lane);
+        if (S == 1) push_rows_done(comm, red, g, mt * BM + row_in_tile - lane);
       }
     }
 
@@ -689,9 +691,9 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
           *ctr_arrive = 0;
           *ctr_done = 0;
         }
-        // every part reports its share of these rows: S arrivals per (cut tile, 32-row slot)
-        if (EPI == EPI_PUSH) push_rows_done(comm, red, g, mt * BM + row_in_tile - lane);
       }
+      // every part reports its share of these rows: S arrivals per (cut tile, 32-row slot)
+      if constexpr (EPI == EPI_PUSH) push_rows_done(comm, red, g, mt * BM + row_in_tile - lane);
     }
   }
 

@@ -201,6 +201,8 @@ def _body_moe(rank, world):
         case = S.MOE_CASES[case_name]
         if case.intermediate_size % world:
             continue
+        if case_name == "config5" and world > 2:
+            continue  # the CPU oracle of the full-size block takes minutes; its shard shapes run at world 2
         if case_name == "config5":  # a slice of the 8-way sharded experts keeps the CPU oracle affordable
             shards = [S.generate_moe(case, world=8, rank=r) for r in range(world)]
         else:
