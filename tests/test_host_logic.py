@@ -155,7 +155,7 @@ def _wait(get, limit_s):
     return True
 
 
-def _run_protocol(world, calls, absent=None, limit_s=0.3, workers=3):
+def _run_protocol(world, calls, absent=None, limit_s=0.3, workers=3, one_shot=False):
     """Each rank = `workers` threads (its CTAs) running `calls` collectives with the device protocol:
     a worker counts its arrival per owner locally, the arrival that completes the count stores the
     epoch into the owner's flag; the owner waits for every source's flag, 'reduces', and the last of
@@ -172,7 +172,14 @@ def _run_protocol(world, calls, absent=None, limit_s=0.3, workers=3):
             if absent == (r, c):
                 return
             epoch = me.epoch[s] + 1
-            for o in range(world):  # push phase: this worker's share for every owner
+            if one_shot:  # one counter; the arrival that completes it flags every rank
+                with me.lock:
+                    me.local_push[0] += 1
+                    last = me.local_push[0] == workers
+                if last:
+                    for o in range(world):
+                        ranks[o].push_flag[s][r] = epoch
+            for o in range(world if not one_shot else 0):  # this worker's share for every owner
                 with me.lock:
                     me.local_push[o] += 1
                     last = me.local_push[o] == workers
@@ -184,10 +191,10 @@ def _run_protocol(world, calls, absent=None, limit_s=0.3, workers=3):
             with me.lock:  # reduce done: count locally, last worker tells everyone
                 me.local_done += 1
                 last = me.local_done == workers
-            if last:
+            if last and not one_shot:
                 for o in range(world):
                     ranks[o].done_flag[s][r] = epoch
-            if ok and not _wait(lambda: all(f == epoch for f in me.done_flag[s]), limit_s):
+            if ok and not one_shot and not _wait(lambda: all(f == epoch for f in me.done_flag[s]), limit_s):
                 status[r] = 3
             try:
                 if barriers[r].wait(timeout=5) == 0:  # "last CTA": close the call
@@ -209,6 +216,12 @@ def _run_protocol(world, calls, absent=None, limit_s=0.3, workers=3):
 def test_flag_protocol_completes_with_skewed_ranks():
     assert _run_protocol(4, 25) == [0, 0, 0, 0]
     assert _run_protocol(2, 40) == [0, 0]
+
+
+def test_one_shot_protocol_completes_and_reports_a_lost_rank():
+    assert _run_protocol(4, 25, one_shot=True) == [0, 0, 0, 0]
+    st = _run_protocol(2, 6, absent=(1, 2), workers=1, one_shot=True)
+    assert st[1] == 0 and st[0] == 2
 
 
 def test_flag_protocol_reports_a_lost_rank_instead_of_hanging():
