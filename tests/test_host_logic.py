@@ -308,3 +308,22 @@ def test_planner_gives_valid_schedules_for_the_layer_shapes(tp):
                 assert rem <= p["rem_units"] <= p["units"], (name, cfg, p)
                 assert p["rem_units"] <= rem * p["k_blocks"]  # at least one k-block per unit
             assert 2 <= p["stages"] <= 8
+
+
+def test_tuned_configuration_cache_round_trip(tmp_path):
+    from sarathi_serve_b200 import dense_ops as D
+    saved = dict(D._tuned)
+    try:
+        D._tuned.clear()
+        D._tuned[("silu", 512, 28672, 4096, torch.bfloat16)] = 303256
+        D._tuned[("push", 512, 4096, 2048, torch.float16)] = 101128
+        path = str(tmp_path / "tuned.json")
+        D.save_tuned(path)
+        D._tuned.clear()
+        assert D.load_tuned(path) == 2
+        assert D.tuned_cfg("silu", 512, 28672, 4096, torch.bfloat16) == 303256
+        assert D.tuned_cfg("push", 512, 4096, 2048, torch.float16) == 101128
+        assert D.tuned_cfg("push", 512, 4096, 2048, torch.bfloat16) == 0  # unknown problem: library default
+    finally:
+        D._tuned.clear()
+        D._tuned.update(saved)
