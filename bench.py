@@ -18,8 +18,9 @@ the path).  Inputs are seeded synthetic tensors (sarathi_serve_b200.synthetic).
 `gpu_comparison`: the same step as the reference runs it on a GPU (cuBLAS GEMMs, separate rotary /
             SiLU*mul / add+RMSNorm kernels, NCCL all-reduce), same graph timing.
 `e2e`     : tokens/s through the public layer API with HOST buffers: pinned H2D of the
-            hidden states and positions, LlamaDecoderLayer.forward captured once per layer in a CUDA
-            graph (graph_runner.LayerGraph) and replayed, D2H of the result, a host sync, every step.
+            hidden states and positions, LlamaDecoderLayer.forward and the D2H of the result, all captured
+            once per layer in a CUDA graph (graph_runner.LayerGraph with host_io) and replayed, then a host
+            sync, every step.
 `roofline`: the dominant kernel (gate_up GEMM + SiLU*mul), timed alone with CUDA events.
 Weights of several distinct layers are cycled so that each step's operands exceed the L2.
 One JSON line is printed by rank 0.
@@ -323,16 +324,19 @@ def run_native(a):
         # ---- end to end through the layer API with host buffers
         x_host = t.x.to(case.dtype).pin_memory()
         pos_host = t.positions.pin_memory()
-        out_host = torch.empty(T, H, dtype=case.dtype).pin_memory()
 
         # the public call for a fixed batch shape: a captured layer (LayerGraph) fed from host buffers
         from sarathi_serve_b200.graph_runner import LayerGraph
-        runners = [LayerGraph(l, T, attn) for l in layers]
+        # (host_io: the H2D copies of the step's inputs and the D2H copy of its result are nodes of the graph,
+        #  so a step is one launch and one host synchronisation)
+        runners = [LayerGraph(l, T, attn, host_io=True) for l in layers]
+        for r_ in runners:
+            r_.host_positions.copy_(pos_host)
+            r_.host_hidden_states.copy_(x_host)
         barrier()
 
         def step_e2e(i):
-            out = runners[i % n_layers](pos_host, x_host)
-            out_host.copy_(out, non_blocking=True)
+            runners[i % n_layers].replay_host_io()
             torch.cuda.current_stream().synchronize()
 
         e2e_steps = max(50, a.steps)

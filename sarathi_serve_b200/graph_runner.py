@@ -21,10 +21,16 @@ class LayerGraph:
 
     ``__call__(positions, hidden_states)`` accepts device or (pinned) host tensors, copies them into
     the graph's static inputs, replays, and returns the static output tensor (overwritten by the
-    next call).  Shapes other than the captured one are rejected."""
+    next call).  Shapes other than the captured one are rejected.
+
+    With ``host_io=True`` the graph also owns pinned host buffers (``host_positions``,
+    ``host_hidden_states``, ``host_output``) and the copies between them and the device are nodes of
+    the graph: a step is then ONE graph launch -- fill the host inputs, ``replay_host_io()``,
+    synchronise, read ``host_output`` -- which matters when several ranks have to stay in step."""
 
     def __init__(self, layer: torch.nn.Module, num_tokens: int, attention_backend_wrapper, *, layer_cache_idx: int = 0,
-                 dtype: Optional[torch.dtype] = None, device: Optional[torch.device] = None, warmup: int = 2):
+                 dtype: Optional[torch.dtype] = None, device: Optional[torch.device] = None, warmup: int = 2,
+                 host_io: bool = False):
         p = next(layer.parameters())
         self.device = device or p.device
         self.dtype = dtype or p.dtype
@@ -35,6 +41,11 @@ class LayerGraph:
         hidden = layer.hidden_size
         self.positions = torch.zeros(self.num_tokens, dtype=torch.int64, device=self.device)
         self.hidden_states = torch.zeros(self.num_tokens, hidden, dtype=self.dtype, device=self.device)
+        self.host_io = bool(host_io)
+        if self.host_io:
+            self.host_positions = torch.zeros(self.num_tokens, dtype=torch.int64).pin_memory()
+            self.host_hidden_states = torch.zeros(self.num_tokens, hidden, dtype=self.dtype).pin_memory()
+            self.host_output = torch.zeros(self.num_tokens, hidden, dtype=self.dtype).pin_memory()
         self.stream = torch.cuda.Stream(device=self.device)
         self.stream.wait_stream(torch.cuda.current_stream(self.device))
         with torch.cuda.stream(self.stream), torch.inference_mode():
@@ -43,10 +54,26 @@ class LayerGraph:
             self.stream.synchronize()
             self.graph = torch.cuda.CUDAGraph()
             with torch.cuda.graph(self.graph, stream=self.stream):
+                if self.host_io:
+                    self.positions.copy_(self.host_positions, non_blocking=True)
+                    self.hidden_states.copy_(self.host_hidden_states, non_blocking=True)
                 self.output = layer(self.positions, self.hidden_states, layer_cache_idx, attention_backend_wrapper)
+                if self.host_io:
+                    self.host_output.copy_(self.output, non_blocking=True)
         torch.cuda.current_stream(self.device).wait_stream(self.stream)
 
+    def replay_host_io(self) -> torch.Tensor:
+        """One launch: host inputs -> device, the layer, output -> ``host_output`` (valid after the
+        current stream has been synchronised)."""
+        if not self.host_io:
+            raise RuntimeError("LayerGraph: built without host_io=True")
+        self.graph.replay()
+        return self.host_output
+
     def __call__(self, positions: torch.Tensor, hidden_states: torch.Tensor) -> torch.Tensor:
+        if self.host_io:
+            raise RuntimeError("LayerGraph: built with host_io=True -- fill host_positions / host_hidden_states and "
+                               "call replay_host_io()")
         if hidden_states.shape != self.hidden_states.shape or positions.shape != self.positions.shape:
             raise RuntimeError(f"LayerGraph: captured for {tuple(self.hidden_states.shape)} hidden states, "
                                f"got {tuple(hidden_states.shape)}")

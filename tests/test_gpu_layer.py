@@ -123,4 +123,14 @@ def test_layer_graph_replay_equals_eager(tp1):
         assert torch.equal(out, eager)
     with pytest.raises(RuntimeError, match="captured for"):
         runner(pos_host[:3], x_host[:3])
+    # host buffers owned by the graph: the copies are graph nodes, a step is one launch
+    io = LayerGraph(layer, case.num_tokens, Q(), host_io=True)
+    io.host_positions.copy_(t.positions)
+    for scale in (1.0, 0.25):
+        io.host_hidden_states.copy_((t.x * scale).to(case.dtype))
+        out = io.replay_host_io()
+        torch.cuda.synchronize()
+        with torch.inference_mode():
+            eager = layer(t.positions.cuda(), (t.x * scale).to(case.dtype).cuda(), 0, Q())
+        assert torch.equal(out, eager.cpu())
     tp1.get_tensor_model_parallel_comm().check_status()
