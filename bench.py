@@ -46,7 +46,7 @@ L2_BYTES = 126 << 20
 
 # dram__bytes_read.sum + dram__bytes_write.sum of one gate_up launch at TP=1 (ncu --set full capture,
 # summarised in profiles/gemm_gate_up_silu_tp1_ncu_full.md)
-GATE_UP_TP1_DRAM_BYTES = 254.2e6
+GATE_UP_TP1_DRAM_BYTES = 256.7e6
 
 
 def workload_text(name: str, world: int) -> str:
