@@ -262,7 +262,8 @@ def run_native(a):
     def step_resident(i):
         layer = layers[i % n_layers]
         nxt = layers[(i + 1) % n_layers].input_layernorm
-        return layer.forward_carry(pos_dev, normed0, x_dev, 0, attn, nxt)
+        # as in a stack of layers: normed hidden states + residual stream (kept sharded by rows) go to the next layer
+        return layer.forward_carry(pos_dev, normed0, x_dev, 0, attn, nxt, shard_residual=True)
 
     def barrier():
         if world > 1:

@@ -119,7 +119,8 @@ class LlamaDecoderLayer(nn.Module):
         return residual + hidden_states
 
     # --------------------------------------------------------------- fused
-    def _attn_mlp(self, positions, normed, residual, layer_cache_idx, attn, next_norm_weight, next_eps, out=None):
+    def _attn_mlp(self, positions, normed, residual, layer_cache_idx, attn, next_norm_weight, next_eps, out=None,
+                  resid_everywhere=True):
         sa = self.self_attn
         q, k, v = sa.qkv_rotary(positions, normed)
         attn_out = attn.forward(q, k, v, layer_cache_idx, sa.scaling, sa.layer_id)
@@ -128,7 +129,8 @@ class LlamaDecoderLayer(nn.Module):
         h, resid = sa.o_proj.forward_fused(attn_out, residual, self.post_attention_layernorm.weight.data,
                                            self.post_attention_layernorm.variance_epsilon, resid_everywhere=False)
         act = self.mlp.gate_up_proj.forward_silu_mul(h)
-        return self.mlp.down_proj.forward_fused(act, resid, next_norm_weight, next_eps, out=out)
+        return self.mlp.down_proj.forward_fused(act, resid, next_norm_weight, next_eps, out=out,
+                                                resid_everywhere=resid_everywhere)
 
     def tune(self, num_tokens: int) -> None:
         """Autotune the four projections for batches of ``num_tokens`` tokens (all tensor-parallel ranks together)."""
@@ -148,12 +150,19 @@ class LlamaDecoderLayer(nn.Module):
         return out
 
     def forward_carry(self, positions: torch.Tensor, normed: torch.Tensor, residual: torch.Tensor,
-                      layer_cache_idx: int, attention_backend_wrapper, next_norm: RMSNorm
-                      ) -> Tuple[torch.Tensor, torch.Tensor]:
+                      layer_cache_idx: int, attention_backend_wrapper, next_norm: RMSNorm,
+                      shard_residual: bool = False) -> Tuple[torch.Tensor, torch.Tensor]:
         """(normed_l, residual_l) -> (normed_{l+1}, residual_{l+1}); ``next_norm`` is the following
-        layer's input_layernorm (or the model's final norm)."""
+        layer's input_layernorm (or the model's final norm).
+
+        ``shard_residual``: the residual stream is only ever read by the tail of the next row-parallel
+        projection, which touches the rows this rank owns (rows [rank * ceil(T/tp), ...)); with this flag
+        the returned residual is guaranteed for those rows only (the other ranks' rows are not gathered),
+        and the ``residual`` passed in needs to be valid for those rows only -- what a stack of layers
+        calling each other through ``forward_carry`` needs.  The normed hidden states are always complete."""
         return self._attn_mlp(positions, normed, residual, layer_cache_idx, attention_backend_wrapper,
-                              next_norm.weight.data, next_norm.variance_epsilon)
+                              next_norm.weight.data, next_norm.variance_epsilon,
+                              resid_everywhere=not shard_residual)
 
 
 class MixtralMoE(nn.Module):

@@ -191,6 +191,52 @@ def _body_layer(rank, world):
             assert _rel(out[::step], gold["out"]) <= TOL[case.dtype], (case_name, "fixture")
 
 
+def _body_carry(rank, world):
+    """Two layers chained through forward_carry with the residual stream kept sharded by rows, under both
+    all-reduce schemes, against two oracle layers."""
+    from oracle import tp_layer_oracle as O
+    from sarathi_serve_b200 import parallel_state as ps, synthetic as S
+    from sarathi_serve_b200.decoder_layer import LlamaDecoderLayer
+    from helpers import TOL
+
+    class QAttention:
+        def forward(self, q, k, v, idx, scale=1.0, layer_id=None):
+            return q
+
+    case = S.CASES["mini_bf16"]
+    old = torch.get_default_dtype()
+    torch.set_default_dtype(case.dtype)
+    try:
+        layers = [LlamaDecoderLayer(case.hf_config(), layer_id=i) for i in range(2)]
+    finally:
+        torch.set_default_dtype(old)
+    t = S.generate(case)
+    for l in layers:
+        S.load_layer(l, S.shard(t, rank, world))
+    x = t.x.to(case.dtype).cuda()
+    pos = t.positions.cuda()
+    shards = [S.shard(t, r, world) for r in range(world)]
+    cache = O.cos_sin_cache(case.head_dim, case.head_dim, case.max_position, case.rope_theta, case.dtype)
+    kw = dict(num_heads=case.num_heads, num_kv_heads=case.num_kv_heads, head_dim=case.head_dim, eps=case.rms_norm_eps,
+              cache=cache)
+    ref1 = O.decoder_layer(shards, t.x.to(case.dtype), t.positions, **kw)
+    ref2 = O.decoder_layer(shards, ref1["out"], t.positions, next_norm_weight=t.ln1.to(case.dtype), **kw)
+    comm = ps.get_tensor_model_parallel_comm()
+    T = case.num_tokens
+    rpr = -(-T // world)
+    lo, hi = rank * rpr, min(T, rank * rpr + rpr)
+    for one_shot in (4 << 20, 0):
+        comm.set_one_shot_bytes(one_shot)
+        _host_barrier()
+        with torch.inference_mode():
+            normed = layers[0].input_layernorm(x)
+            y1, z1 = layers[0].forward_carry(pos, normed, x, 0, QAttention(), layers[1].input_layernorm, shard_residual=True)
+            y2, z2 = layers[1].forward_carry(pos, y1, z1, 0, QAttention(), layers[0].input_layernorm, shard_residual=True)
+        comm.check_status()
+        assert _rel(y2, ref2["out_normed"]) <= TOL[case.dtype] * 1.5, ("normed", one_shot)
+        assert _rel(z2[lo:hi], ref2["out"][lo:hi]) <= TOL[case.dtype] * 1.5, ("own rows of the residual", one_shot)
+
+
 def _body_moe(rank, world):
     """Tensor-parallel MoE block: experts sharded along the intermediate dimension, k-slot sum fused
     into the all-reduce."""
@@ -263,6 +309,11 @@ def test_rowpar_linear_multi_gpu(world):
 @pytest.mark.parametrize("world", WORLDS)
 def test_decoder_layer_multi_gpu(world):
     _run("_body_layer", 29803, world)
+
+
+@pytest.mark.parametrize("world", WORLDS)
+def test_layer_stack_with_sharded_residual_multi_gpu(world):
+    _run("_body_carry", 29806, world)
 
 
 @pytest.mark.parametrize("world", WORLDS)
