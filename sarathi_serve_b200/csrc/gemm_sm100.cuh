@@ -463,8 +463,9 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
   sc.rem_tiles = g.m_tiles * g.n_tiles - g.tiles_full;
   sc.Gs = g.rem_units;
   sc.k_blocks = g.k_blocks;
-  // grouped mode: rows of A in use (a device value written by moe_align_block_size earlier in the stream)
-  const int rows_in_use = g.expert_ids ? min(g.M, *g.num_post_pad) : g.M;
+  // Every CTA of this persistent grid is resident from the start, so the next kernel of the stream may be
+  // scheduled onto SMs as they become free (its prologue then overlaps this kernel's tail).
+  ptx::grid_launch_dependents();
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < kStages; ++s) {
@@ -491,6 +492,10 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
   if (CTA2) ptx::cluster_sync_all();  // the peer's barriers are initialised before anything signals them
   ptx::tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
+  // Nothing above touched global memory: from here on the kernel reads what earlier kernels of the stream wrote.
+  ptx::grid_dependency_wait();
+  // grouped mode: rows of A in use (a device value written by moe_align_block_size earlier in the stream)
+  const int rows_in_use = g.expert_ids ? min(g.M, *g.num_post_pad) : g.M;
 
   if (warp == 0) {
     // ------------------------------------------------------------ TMA producer
