@@ -1,6 +1,6 @@
 """Generate golden fixtures by running the REFERENCE's own Python modules on CPU/gloo.
 
-    python tests/golden/make_golden.py [--reference /root/reference]
+    python tests/golden/make_golden.py [--reference <checkout of microsoft/sarathi-serve>]
 
 The unmodified reference package is imported from its checkout (never copied).
 What it needs to run without a GPU is shimmed here:
