@@ -194,6 +194,15 @@ int sb200_gemm_colpar(void* out, int64_t ldo, const void* x, int64_t ldx, const 
 int sb200_gemm_plan(int epilogue, int64_t T, int64_t N, int64_t K, int head_size, int tile_cfg,
                     int64_t workspace_bytes, int* out);
 
+/* Vocabulary-parallel embedding lookup: out[t, :] = weight[ids[t] - vocab_start, :] if
+ * vocab_start <= ids[t] < vocab_end, else zeros.  out: [T, H]; ids: [T] int64 (device); weight:
+ * this rank's rows [vocab_end - vocab_start, H] of the embedding table.  Followed by
+ * sb200_all_reduce over the tensor-parallel ranks it gives the full lookup.
+ * Replaces: VocabParallelEmbedding.forward (mask, F.embedding, masked fill),
+ * sarathi/model_executor/parallel_utils/tensor_parallel/layers.py:147-168. */
+int sb200_vocab_embedding(void* out, const int64_t* ids, const void* weight, int64_t T, int64_t H,
+                          int64_t vocab_start, int64_t vocab_end, int dtype, sb200_stream_t stream);
+
 /* ------------------------------------------- tensor-parallel communication */
 
 /* One context per (process, GPU, TP group).  It owns a "symmetric heap" on the

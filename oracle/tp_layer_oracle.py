@@ -212,6 +212,21 @@ def linear(x: torch.Tensor, w: torch.Tensor, b: Optional[torch.Tensor] = None) -
     return F.linear(x, w, b)
 
 
+def vocab_parallel_embedding(ids: torch.Tensor, weight_shards: Sequence[torch.Tensor]) -> torch.Tensor:
+    """tensor_parallel/layers.py:147-177 over len(weight_shards) simulated ranks: each rank looks up the ids of
+    its vocabulary slice (zeros elsewhere), then the SUM all-reduce."""
+    per = weight_shards[0].shape[0]
+    parts = []
+    for r, w in enumerate(weight_shards):
+        lo, hi = r * per, (r + 1) * per
+        mask = (ids < lo) | (ids >= hi)
+        local = (ids - lo).masked_fill(mask, 0)
+        o = w[local].clone()
+        o[mask] = 0
+        parts.append(o)
+    return sum_over_ranks(parts)
+
+
 def sum_over_ranks(parts: Sequence[torch.Tensor]) -> torch.Tensor:
     """tensor_parallel/mappings.py:16-26: element-wise SUM all-reduce in the tensor dtype,
     evaluated here in rank order."""

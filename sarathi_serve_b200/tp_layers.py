@@ -1,8 +1,8 @@
 """Tensor-parallel linear layers with the constructor signatures, attributes,
 parameter names / shapes and (output, output_bias) return convention of the
 reference (sarathi/model_executor/parallel_utils/tensor_parallel/layers.py:
-ColumnParallelLinear :180-308, RowParallelLinear :311-454, ReplicatedLinear
-:457-530), so model files and weight loaders work unchanged.
+VocabParallelEmbedding :72-177, ColumnParallelLinear :180-308, RowParallelLinear
+:311-454, ReplicatedLinear :457-530), so model files and weight loaders work unchanged.
 
 Differences that matter:
   * the local matmul is this library's tcgen05 GEMM, not F.linear;
@@ -29,6 +29,43 @@ from .mappings import (divide, gather_from_tensor_model_parallel_region, reduce_
 
 def _param_device():
     return torch.cuda.current_device() if torch.cuda.is_available() else "cpu"
+
+
+class VocabParallelEmbedding(torch.nn.Module):
+    """Embedding table split along the vocabulary: rank r holds rows [r*V/tp, (r+1)*V/tp).  ``forward`` looks the
+    ids of this rank's slice up (zeros for the others) in one kernel and sums over the ranks with this library's
+    all-reduce (the reference: mask, F.embedding, masked fill, NCCL all-reduce)."""
+
+    def __init__(self, num_embeddings: int, embedding_dim: int, *, params_dtype: Optional[torch.dtype] = None,
+                 use_cpu_initialization: bool = False, perform_initialization: bool = False,
+                 linear_metric_name: Optional[str] = None, communication_metric_name: Optional[str] = None,
+                 reduce_results: Optional[bool] = True, world_size: Optional[int] = None,
+                 rank: Optional[int] = None):
+        super().__init__()
+        assert not perform_initialization
+        assert not use_cpu_initialization
+        self.num_embeddings = num_embeddings
+        self.embedding_dim = embedding_dim
+        if params_dtype is None:
+            params_dtype = torch.get_default_dtype()
+        self.tensor_model_parallel_size = ps.get_tensor_model_parallel_world_size() if world_size is None else world_size
+        self.rank = ps.get_tensor_model_parallel_rank() if rank is None else rank
+        self.reduce_results = reduce_results
+        per_partition = divide(num_embeddings, self.tensor_model_parallel_size)
+        self.vocab_start_index = self.rank * per_partition
+        self.vocab_end_index = self.vocab_start_index + per_partition
+        self.num_embeddings_per_partition = per_partition
+        self.weight = Parameter(torch.empty(per_partition, embedding_dim, device=_param_device(), dtype=params_dtype),
+                                requires_grad=False)
+
+    def forward(self, input_: torch.Tensor) -> torch.Tensor:
+        from . import embedding_ops
+        ids = input_.reshape(-1).contiguous()
+        out = torch.empty(ids.numel(), self.embedding_dim, dtype=self.weight.dtype, device=self.weight.device)
+        embedding_ops.vocab_embedding(out, ids, self.weight, self.vocab_start_index, self.vocab_end_index)
+        if self.reduce_results and self.tensor_model_parallel_size > 1 and ids.numel() > 0:
+            out = reduce_from_tensor_model_parallel_region(out)
+        return out.view(*input_.shape, self.embedding_dim)
 
 
 class ColumnParallelLinear(torch.nn.Module):

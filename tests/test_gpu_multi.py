@@ -237,6 +237,22 @@ def _body_carry(rank, world):
         assert _rel(z2[lo:hi], ref2["out"][lo:hi]) <= TOL[case.dtype] * 1.5, ("own rows of the residual", one_shot)
 
 
+def _body_embedding(rank, world):
+    """VocabParallelEmbedding: each rank's masked lookup summed by the all-reduce = the full-table lookup."""
+    from sarathi_serve_b200.tp_layers import VocabParallelEmbedding
+    for dtype in (torch.bfloat16, torch.float32):
+        V, H = 1024, 512
+        g = torch.Generator().manual_seed(9)
+        table = torch.randn(V, H, generator=g).to(dtype)
+        emb = VocabParallelEmbedding(V, H, params_dtype=dtype)
+        emb.weight.data.copy_(table[emb.vocab_start_index:emb.vocab_end_index])
+        for shape in ((300,), (5, 13), (1,)):
+            ids = torch.randint(0, V, shape, generator=g)
+            _host_barrier()
+            out = emb(ids.cuda())
+            assert out.shape == (*shape, H) and torch.equal(out.cpu(), table[ids]), (dtype, shape)
+
+
 def _body_moe(rank, world):
     """Tensor-parallel MoE block: experts sharded along the intermediate dimension, k-slot sum fused
     into the all-reduce."""
@@ -314,6 +330,11 @@ def test_decoder_layer_multi_gpu(world):
 @pytest.mark.parametrize("world", WORLDS)
 def test_layer_stack_with_sharded_residual_multi_gpu(world):
     _run("_body_carry", 29806, world)
+
+
+@pytest.mark.parametrize("world", WORLDS)
+def test_vocab_parallel_embedding_multi_gpu(world):
+    _run("_body_embedding", 29807, world)
 
 
 @pytest.mark.parametrize("world", WORLDS)

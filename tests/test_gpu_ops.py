@@ -158,3 +158,44 @@ def test_cpu_tensors_are_rejected():
     x = torch.randn(4, 64)
     with pytest.raises(RuntimeError):
         layernorm_ops.rms_norm(torch.empty_like(x), x, torch.ones(64), 1e-5)
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16, torch.float32])
+@pytest.mark.parametrize("T,H,V", [(512, 4096, 1024), (7, 40, 96), (1, 8, 16), (300, 1000, 333), (0, 64, 32)])
+def test_vocab_embedding_slices(dtype, T, H, V):
+    """Every rank's masked lookup (any slice of the vocabulary) is bit-exact, and the slices add up to the
+    full-table lookup of the oracle."""
+    from sarathi_serve_b200 import embedding_ops
+    g = torch.Generator().manual_seed(T + H + V)
+    table = torch.randn(V, H, generator=g).to(dtype)
+    ids = torch.randint(0, V, (T,), generator=g)
+    total = torch.zeros(T, H, dtype=torch.float32)
+    bounds = [0, V // 3, V // 3, (2 * V) // 3, V]  # includes an empty slice
+    for lo, hi in zip(bounds[:-1], bounds[1:]):
+        out = torch.full((T, H), 7.0, dtype=dtype, device="cuda")
+        embedding_ops.vocab_embedding(out, ids.cuda(), table[lo:hi].contiguous().cuda(), lo, hi)
+        mask = (ids >= lo) & (ids < hi)
+        ref = torch.zeros(T, H, dtype=dtype)
+        ref[mask] = table[ids[mask]]
+        assert torch.equal(out.cpu(), ref)
+        total += out.float().cpu()
+    if T:
+        assert torch.equal(total.to(dtype), O.vocab_parallel_embedding(ids, [table]))
+
+
+def test_vocab_parallel_embedding_module_tp1():
+    from sarathi_serve_b200 import parallel_state as ps
+    from sarathi_serve_b200.tp_layers import VocabParallelEmbedding
+    ps.destroy_model_parallel()
+    ps.initialize_model_parallel(1)
+    try:
+        emb = VocabParallelEmbedding(1000, 256, params_dtype=torch.bfloat16)
+        assert emb.weight.shape == (1000, 256) and emb.vocab_start_index == 0 and emb.vocab_end_index == 1000
+        g = torch.Generator().manual_seed(0)
+        w = torch.randn(1000, 256, generator=g).to(torch.bfloat16)
+        emb.weight.data.copy_(w)
+        ids = torch.randint(0, 1000, (5, 13), generator=g)
+        out = emb(ids.cuda())
+        assert out.shape == (5, 13, 256) and torch.equal(out.cpu(), w[ids])
+    finally:
+        ps.destroy_model_parallel()

@@ -327,3 +327,17 @@ def test_tuned_configuration_cache_round_trip(tmp_path):
     finally:
         D._tuned.clear()
         D._tuned.update(saved)
+
+
+def test_vocab_parallel_embedding_api_surface_on_cpu():
+    """Constructor keywords, attributes and the weight shard shape of the reference (layers.py:72-145)."""
+    from sarathi_serve_b200.tp_layers import VocabParallelEmbedding
+    emb = VocabParallelEmbedding(128256, 64, params_dtype=torch.bfloat16, linear_metric_name="x",
+                                 communication_metric_name="y", reduce_results=True, world_size=8, rank=3)
+    assert emb.num_embeddings == 128256 and emb.embedding_dim == 64
+    assert emb.tensor_model_parallel_size == 8 and emb.rank == 3
+    assert (emb.vocab_start_index, emb.vocab_end_index) == (3 * 16032, 4 * 16032)
+    assert emb.num_embeddings_per_partition == 16032 and emb.weight.shape == (16032, 64)
+    assert emb.weight.dtype == torch.bfloat16 and not emb.weight.requires_grad
+    with pytest.raises(AssertionError):
+        VocabParallelEmbedding(100, 8, world_size=3, rank=0)  # the vocabulary must divide evenly

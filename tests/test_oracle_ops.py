@@ -97,3 +97,12 @@ def test_fused_experts_matches_dense_evaluation():
             a = torch.nn.functional.silu(gu[:I]) * gu[I:]
             ref[t] += w[t, j] * (w2[e] @ a)
     assert torch.allclose(out, ref, rtol=1e-4, atol=1e-5)
+
+
+def test_vocab_parallel_embedding_equals_the_full_table_lookup():
+    g = torch.Generator().manual_seed(3)
+    table = torch.randn(96, 40, generator=g).to(torch.bfloat16)
+    ids = torch.randint(0, 96, (57,), generator=g)
+    for tp in (1, 2, 4, 8):
+        shards = list(table.chunk(tp, dim=0))
+        assert torch.equal(O.vocab_parallel_embedding(ids, shards), table[ids])
