@@ -21,7 +21,8 @@ import torch.nn as nn
 from . import parallel_state as ps
 from .fused_moe import FusedMoE
 from .nn_layers import RMSNorm, SiluAndMul, get_rope
-from .tp_layers import ColumnParallelLinear, ReplicatedLinear, RowParallelLinear
+from .mappings import gather_from_tensor_model_parallel_region
+from .tp_layers import ColumnParallelLinear, ReplicatedLinear, RowParallelLinear, VocabParallelEmbedding
 
 
 class LlamaMLP(nn.Module):
@@ -163,6 +164,59 @@ class LlamaDecoderLayer(nn.Module):
         return self._attn_mlp(positions, normed, residual, layer_cache_idx, attention_backend_wrapper,
                               next_norm.weight.data, next_norm.variance_epsilon,
                               resid_everywhere=not shard_residual)
+
+
+class LlamaModel(nn.Module):
+    """Embedding, the stack of decoder layers and the final norm, with the reference's attribute names
+    (``embed_tokens``, ``layers``, ``norm``) and forward signature (models/llama.py:258-314; one pipeline stage).
+
+    The layers call each other through ``forward_carry``: the normed hidden states and the residual stream (kept
+    sharded by rows) go from layer to layer, every layer is four kernels, and the last one applies ``norm`` --
+    the reference's ``norm(hidden_states)`` after the loop -- in its down-projection kernel."""
+
+    def __init__(self, config) -> None:
+        super().__init__()
+        self.config = config
+        self.padding_idx = getattr(config, "pad_token_id", None)
+        self.vocab_size = config.vocab_size
+        vocab_size = ((config.vocab_size + 63) // 64) * 64
+        self.embed_tokens = VocabParallelEmbedding(vocab_size, config.hidden_size, perform_initialization=False)
+        self.layers = nn.ModuleList([LlamaDecoderLayer(config, layer_id=i) for i in range(config.num_hidden_layers)])
+        self.norm = RMSNorm(config.hidden_size, eps=config.rms_norm_eps)
+
+    def forward(self, hidden_states: torch.Tensor, positions: torch.Tensor, attention_backend_wrapper) -> torch.Tensor:
+        """``hidden_states``: token ids [T] (looked up in ``embed_tokens``); returns norm(last hidden states) [T, H]."""
+        residual = self.embed_tokens(hidden_states)
+        normed = self.layers[0].input_layernorm(residual)
+        n = len(self.layers)
+        for i, layer in enumerate(self.layers):
+            next_norm = self.layers[i + 1].input_layernorm if i + 1 < n else self.norm
+            normed, residual = layer.forward_carry(positions, normed, residual, i, attention_backend_wrapper, next_norm,
+                                                   shard_residual=True)
+        return normed
+
+
+class LlamaForCausalLM(nn.Module):
+    """``model`` + ``lm_head`` (vocabulary-sharded ColumnParallelLinear, no bias, output not gathered), as in
+    models/llama.py:317-345; ``compute_logits`` is the sampler's projection + gather (layers/sampler.py:89-97)."""
+
+    def __init__(self, config) -> None:
+        super().__init__()
+        self.config = config
+        self.model = LlamaModel(config)
+        vocab_size = ((config.vocab_size + 63) // 64) * 64
+        self.lm_head = ColumnParallelLinear(config.hidden_size, vocab_size, bias=False, gather_output=False,
+                                            perform_initialization=False)
+
+    def forward(self, hidden_states: torch.Tensor, positions: torch.Tensor, attention_backend_wrapper) -> torch.Tensor:
+        return self.model(hidden_states, positions, attention_backend_wrapper)
+
+    def compute_logits(self, hidden_states: torch.Tensor) -> torch.Tensor:
+        """[num_rows, H] -> [num_rows, vocab]: this rank's vocabulary slice of the logits, gathered over the ranks
+        and cut to the real vocabulary size."""
+        logits, _ = self.lm_head(hidden_states)
+        logits = gather_from_tensor_model_parallel_region(logits)
+        return logits[:, :self.config.vocab_size]
 
 
 class MixtralMoE(nn.Module):

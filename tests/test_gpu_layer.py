@@ -1,6 +1,8 @@
 """GPU parity of the decoder layer built from this package's modules (tensor
 parallel size 1: one GPU, the row-parallel kernel runs its reduce / residual /
 norm phases locally) against the CPU oracle and the reference fixtures."""
+import dataclasses
+
 import pytest
 import torch
 
@@ -134,3 +136,46 @@ def test_layer_graph_replay_equals_eager(tp1):
             eager = layer(t.positions.cuda(), (t.x * scale).to(case.dtype).cuda(), 0, Q())
         assert torch.equal(out, eager.cpu())
     tp1.get_tensor_model_parallel_comm().check_status()
+
+
+def test_model_stack_embedding_layers_norm_logits(tp1):
+    """Token ids -> VocabParallelEmbedding -> two decoder layers chained through forward_carry -> final norm
+    (applied by the last layer's kernel) -> lm_head logits, against the oracle's op-by-op chain."""
+    from sarathi_serve_b200.decoder_layer import LlamaForCausalLM
+
+    class Q:
+        def forward(self, q, k, v, layer_cache_idx, softmax_scale=1.0, layer_id=None):
+            return q
+
+    case = S.CASES["mini_bf16"]
+    cfg = case.hf_config()
+    cfg.num_hidden_layers, cfg.vocab_size = 2, 1000
+    old = torch.get_default_dtype()
+    torch.set_default_dtype(case.dtype)
+    try:
+        lm = LlamaForCausalLM(cfg)
+    finally:
+        torch.set_default_dtype(old)
+    t = S.generate(case)
+    for layer in lm.model.layers:
+        S.load_layer(layer, S.shard(t, 0, 1))
+    g = torch.Generator().manual_seed(21)
+    table = torch.randn(1024, case.hidden_size, generator=g).to(case.dtype)
+    final_w = (1 + 0.1 * torch.randn(case.hidden_size, generator=g)).to(case.dtype)
+    head = (torch.randn(1024, case.hidden_size, generator=g) * 0.05).to(case.dtype)
+    lm.model.embed_tokens.weight.data.copy_(table)
+    lm.model.norm.weight.data.copy_(final_w)
+    lm.lm_head.weight.data.copy_(head)
+    ids = torch.randint(0, 1000, (case.num_tokens,), generator=g)
+    with torch.inference_mode():
+        hidden = lm(ids.cuda(), t.positions.cuda(), Q())
+        logits = lm.compute_logits(hidden)
+    tp1.get_tensor_model_parallel_comm().check_status()
+    h = table[ids]
+    for _ in range(2):
+        h = oracle_out(case, dataclasses.replace(t, x=h.float()))["out"]
+    ref_hidden = O.rms_norm(h, final_w, case.rms_norm_eps)
+    assert hidden.shape == (case.num_tokens, case.hidden_size)
+    assert rel_err(hidden, ref_hidden) <= TOL[case.dtype] * 1.5
+    assert logits.shape == (case.num_tokens, 1000)
+    assert rel_err(logits, O.linear(ref_hidden, head)[:, :1000]) <= TOL[case.dtype] * 1.5
