@@ -203,6 +203,12 @@ int sb200_gemm_plan(int epilogue, int64_t T, int64_t N, int64_t K, int head_size
 int sb200_vocab_embedding(void* out, const int64_t* ids, const void* weight, int64_t T, int64_t H,
                           int64_t vocab_start, int64_t vocab_end, int dtype, sb200_stream_t stream);
 
+/* Arrivals the row-parallel kernel of one rank counts for the owner of rows [lo, hi) under the
+ * schedule sb200_gemm_plan(3, T, N, K, ., tile_cfg, workspace_bytes) reports (-1: no such schedule).
+ * Host-only, used by the tests of that bookkeeping; no counterpart in the reference. */
+int64_t sb200_gemm_rowpar_arrivals(int64_t T, int64_t N, int64_t K, int tile_cfg, int64_t workspace_bytes,
+                                   int64_t lo, int64_t hi);
+
 /* ------------------------------------------- tensor-parallel communication */
 
 /* One context per (process, GPU, TP group).  It owns a "symmetric heap" on the

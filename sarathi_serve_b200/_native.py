@@ -56,6 +56,7 @@ _GEMM_SIGS: dict = {
     "sb200_comm_local_heap": (_P, [_P]),
     "sb200_comm_scratch": (_P, [_P]),
     "sb200_comm_region_bytes": (_L, [_P]),
+    "sb200_gemm_rowpar_arrivals": (_L, [_L, _L, _L, _I, _L, _L, _L]),
     "sb200_vocab_embedding": (_I, [_P, _P, _P, _L, _L, _L, _L, _I, _P]),
     "sb200_comm_set_wait_limit": (_I, [_P, _L]),
     "sb200_comm_set_one_shot_bytes": (_I, [_P, _L]),

@@ -403,3 +403,14 @@ extern "C" int sb200_gemm_plan(int epilogue, int64_t T, int64_t N, int64_t K, in
   for (int i = 0; i < 11; ++i) out[i] = v[i];
   return p.bn ? SB200_OK : SB200_ERR_UNSUPPORTED;
 }
+
+// Arrivals the row-parallel kernel of one rank counts for the owner of rows [lo, hi) under the schedule
+// sb200_gemm_plan reports for (T, N, K, tile_cfg) -- what sb200_gemm_rowpar writes into the kernel's
+// expected counts.  Host-only, for tests of that bookkeeping; no counterpart in the reference.
+extern "C" int64_t sb200_gemm_rowpar_arrivals(int64_t T, int64_t N, int64_t K, int tile_cfg, int64_t workspace_bytes,
+                                              int64_t lo, int64_t hi) {
+  if (T <= 0 || N <= 0 || K <= 0) return -1;
+  const GemmPlan p = plan_gemm(EPI_PUSH, T, N, K, 128, tile_cfg, (size_t)workspace_bytes);
+  if (!p.bn) return -1;
+  return (int64_t)gemm_push_increments(p, T, lo, hi);
+}

@@ -341,3 +341,49 @@ def test_vocab_parallel_embedding_api_surface_on_cpu():
     assert emb.weight.dtype == torch.bfloat16 and not emb.weight.requires_grad
     with pytest.raises(AssertionError):
         VocabParallelEmbedding(100, 8, world_size=3, rank=0)  # the vocabulary must divide evenly
+
+
+# ------------------------- arrivals the row-parallel kernel reports vs what the host tells it to expect
+def _model_arrivals(p, T, lo, hi):
+    """What the device does (csrc/gemm_sm100.cuh, epilogue of EPI_PUSH): for every tile and every group of 32
+    rows of it that holds a valid row, the epilogue warps that drain those rows (two per group with one
+    accumulator, one with two) report once per owner whose rows the group overlaps -- once per part for a
+    tile that is cut along K, because every part finishes a share of it."""
+    bm = (256 if p["cta_pairs"] else 128) * p["accumulators"]
+    warps_per_group = 2 if p["accumulators"] == 1 else 1
+    tiles = p["m_tiles"] * p["n_tiles"]
+    rem = tiles - p["tiles_full"]
+    total = 0
+    for tile in range(tiles):
+        mt = tile % p["m_tiles"]
+        parts = 1
+        if tile >= p["tiles_full"]:
+            rt, KB, Gs = tile - p["tiles_full"], p["k_blocks"], p["rem_units"]
+            W = rem * KB
+            parts = _sk_unit_of(W, Gs, (rt + 1) * KB - 1) - _sk_unit_of(W, Gs, rt * KB) + 1
+        for g0 in range(mt * bm, min(T, mt * bm + bm), 32):
+            g1 = min(T, g0 + 32)
+            if g0 < hi and g1 > lo:
+                total += warps_per_group * parts
+    return total
+
+
+@pytest.mark.parametrize("T,N,K", [(512, 4096, 4096), (512, 4096, 1792), (65, 256, 64), (1, 128, 512), (130, 4096, 7168),
+                                   (300, 1024, 704), (96, 8192, 256)])
+@pytest.mark.parametrize("world", [1, 2, 3, 8])
+def test_expected_arrivals_match_the_kernels_reporting_rule(T, N, K, world):
+    from sarathi_serve_b200 import _native as N_, dense_ops as D
+    ws = 64 << 20
+    rpr = -(-T // world)
+    for cfg in (0, 128, 2256, 302128, 3256, 203256, 4256, 803128):
+        try:
+            p = D.gemm_plan(3, T, N, K, tile_cfg=cfg, workspace_bytes=ws)
+        except RuntimeError:
+            continue
+        for o in range(world):
+            lo, hi = o * rpr, min(T, o * rpr + rpr)
+            got = N_.lib().sb200_gemm_rowpar_arrivals(T, N, K, cfg, ws, lo, hi)
+            want = _model_arrivals(p, T, lo, hi) if hi > lo else 0
+            assert got == want, (cfg, o, p)
+        # one-shot calls count every finished (tile, 32-row group, part) once
+        assert N_.lib().sb200_gemm_rowpar_arrivals(T, N, K, cfg, ws, 0, T) == _model_arrivals(p, T, 0, T)
