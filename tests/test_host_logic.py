@@ -387,3 +387,28 @@ def test_expected_arrivals_match_the_kernels_reporting_rule(T, N, K, world):
             assert got == want, (cfg, o, p)
         # one-shot calls count every finished (tile, 32-row group, part) once
         assert N_.lib().sb200_gemm_rowpar_arrivals(T, N, K, cfg, ws, 0, T) == _model_arrivals(p, T, 0, T)
+
+
+def test_model_stack_api_surface_on_cpu():
+    """LlamaModel / LlamaForCausalLM keep the reference's module tree and parameter names
+    (models/llama.py:258-345), so its weight loader addresses the same state-dict keys."""
+    from types import SimpleNamespace
+    from sarathi_serve_b200 import parallel_state as ps
+    from sarathi_serve_b200.decoder_layer import LlamaForCausalLM
+    ps.destroy_model_parallel()
+    ps.initialize_model_parallel(1)
+    try:
+        cfg = SimpleNamespace(hidden_size=128, num_attention_heads=4, num_key_value_heads=2, intermediate_size=256,
+                              rms_norm_eps=1e-5, rope_theta=10000.0, rope_scaling=None, max_position_embeddings=64,
+                              hidden_act="silu", num_hidden_layers=2, vocab_size=1000, pad_token_id=None)
+        lm = LlamaForCausalLM(cfg)
+        keys = set(lm.state_dict().keys())
+        for k in ("model.embed_tokens.weight", "model.norm.weight", "lm_head.weight",
+                  "model.layers.0.self_attn.qkv_proj.weight", "model.layers.1.self_attn.o_proj.weight",
+                  "model.layers.0.mlp.gate_up_proj.weight", "model.layers.1.mlp.down_proj.weight",
+                  "model.layers.0.input_layernorm.weight", "model.layers.1.post_attention_layernorm.weight"):
+            assert k in keys, k
+        assert lm.model.embed_tokens.weight.shape == (1024, 128)  # vocabulary padded to a multiple of 64
+        assert lm.lm_head.weight.shape == (1024, 128) and lm.lm_head.bias is None
+    finally:
+        ps.destroy_model_parallel()
