@@ -6,7 +6,6 @@ from __future__ import annotations
 
 from typing import Optional
 
-import torch
 
 _TP_GROUP = None
 _TP_RANKS = None

@@ -12,9 +12,9 @@ harness: the path is token-wise, only shapes and value distributions matter.
 """
 from __future__ import annotations
 
-from dataclasses import dataclass, field
+from dataclasses import dataclass
 from types import SimpleNamespace
-from typing import Dict, List
+from typing import Dict
 
 import torch
 
