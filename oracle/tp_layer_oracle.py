@@ -14,7 +14,7 @@ of the model dtype.
 Pinning:
   * layer-level functions are checked against fixtures produced by running the
     reference's own Python modules (ColumnParallelLinear, RowParallelLinear,
-    LlamaDecoderLayer, RMSNorm, RotaryEmbedding, ... imported from the reference
+    LlamaDecoderLayer, RMSNorm, RotaryEmbedding, VocabParallelEmbedding, ... imported from the reference
     checkout, CPU/gloo) -- tests/golden/make_golden.py, tests/golden/*.npz;
   * op-level functions (rms_norm, silu_and_mul, gelu_*, rotary_embedding,
     topk_softmax, moe_align_block_size) are checked on the GPU against the

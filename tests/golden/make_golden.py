@@ -149,6 +149,34 @@ def _worker(rank: int, world: int, case_name: str, port: int, reference: str, ou
     dist.destroy_process_group()
 
 
+def _worker_embedding(rank: int, world: int, port: int, reference: str, out_path: str) -> None:
+    """The reference's VocabParallelEmbedding (tensor_parallel/layers.py:72-177) over gloo ranks."""
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    import torch.distributed as dist
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    _install_shims(reference)
+    from sarathi.config import MetricsConfig
+    from sarathi.metrics.metrics_store import MetricsStore
+    MetricsStore.get_or_create_instance(None, None, MetricsConfig(write_metrics=False))
+    from sarathi.model_executor.parallel_utils import parallel_state as ps
+    ps.initialize_model_parallel(world, 1)
+    from sarathi.model_executor.parallel_utils.tensor_parallel.layers import VocabParallelEmbedding
+    V, H = 256, 48
+    g = torch.Generator().manual_seed(17)
+    table = torch.randn(V, H, generator=g).to(torch.bfloat16)
+    ids = torch.cat([torch.tensor([0, V // world - 1, V // world, V - 1]), torch.randint(0, V, (60,), generator=g)])
+    emb = VocabParallelEmbedding(V, H, params_dtype=torch.bfloat16)
+    emb.weight.data.copy_(table[emb.vocab_start_index:emb.vocab_end_index])
+    with torch.inference_mode():
+        out = emb(ids)
+    if rank == 0:
+        np.savez_compressed(out_path, table=table.view(torch.int16).numpy(), ids=ids.numpy(),
+                            out=out.contiguous().view(torch.int16).numpy(), world=np.array([world]))
+        print(f"wrote {out_path} ({os.path.getsize(out_path) / 1024:.0f} KiB)")
+    dist.destroy_process_group()
+
+
 def main() -> None:
     ap = argparse.ArgumentParser()
     ap.add_argument("--reference", default="/root/reference")
@@ -162,6 +190,8 @@ def main() -> None:
         out_path = os.path.join(HERE, f"{case_name}_tp{world}.npz")
         mp.spawn(_worker, args=(world, case_name, port, a.reference, out_path), nprocs=world)
         port += 1
+    if not a.only or a.only == "vocab_embedding":
+        mp.spawn(_worker_embedding, args=(2, port, a.reference, os.path.join(HERE, "vocab_embedding_tp2.npz")), nprocs=2)
 
 
 if __name__ == "__main__":

@@ -57,3 +57,18 @@ def test_tp_invariance():
     _, o1, _ = run_oracle("mini_f32", 1)
     _, o2, _ = run_oracle("mini_f32", 2)
     assert rel_err(o2["out"], o1["out"]) < 1e-5
+
+
+def test_vocab_parallel_embedding_matches_the_reference_module():
+    """Fixture made by the reference's own VocabParallelEmbedding over two gloo ranks
+    (tests/golden/make_golden.py): the oracle's masked lookups + sum reproduce it bit for bit."""
+    import os
+    import numpy as np
+    g = np.load(os.path.join(os.path.dirname(__file__), "golden", "vocab_embedding_tp2.npz"))
+    table = torch.from_numpy(g["table"]).view(torch.bfloat16)
+    out = torch.from_numpy(g["out"]).view(torch.bfloat16)
+    ids = torch.from_numpy(g["ids"])
+    world = int(g["world"][0])
+    got = O.vocab_parallel_embedding(ids, list(table.chunk(world, dim=0)))
+    assert torch.equal(got, out)
+    assert torch.equal(out, table[ids])  # the sharded lookup is the full-table lookup
