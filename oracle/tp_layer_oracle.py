@@ -21,9 +21,10 @@ Pinning:
     reference's own CUDA kernels compiled into oracle/_ref/ (oracle/build_ref.py);
   * moe_align_block_size is also checked against the worked example in the
     reference's kernel comment (csrc/moe_align_block_size_kernels.cu:88-93);
-  * the grouped expert GEMM (a Triton kernel in the reference,
-    layers/fused_moe/fused_moe.py:15-148) cannot run on a CPU and is absent from
-    the GPU box: fused_experts() below is a restatement whose parity is UNPINNED.
+  * fused_experts() (the reference's Triton grouped GEMMs, layers/fused_moe/fused_moe.py:15-148,411-544) is
+    checked against a fixture made by running the reference's own kernel in the Triton interpreter on the CPU
+    (fp16 only -- the installed interpreter mishandles bf16; tests/golden/make_golden.py): equal except for
+    one-ulp differences where the order of the fp32 additions along K decides a rounding.
 """
 from __future__ import annotations
 
@@ -191,7 +192,7 @@ def fused_experts(x: torch.Tensor, w13: torch.Tensor, w2: torch.Tensor, topk_wei
                   topk_ids: torch.Tensor) -> torch.Tensor:
     """fused_moe.py:411-544 with the rounding points of the Triton kernel (:15-148):
     GEMM1 (fp32 accumulate) -> T, silu_and_mul -> T, GEMM2 * routed weight (fp32) -> T,
-    sum over the k slots -> T.  PARITY UNPINNED (see the module docstring)."""
+    sum over the k slots -> T.  Pinned for fp16 by tests/golden/fused_experts_f16.npz (see the module docstring)."""
     T_, H = x.shape
     k = topk_ids.shape[1]
     out3 = torch.zeros(T_, k, w2.shape[1], dtype=x.dtype)

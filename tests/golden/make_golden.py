@@ -177,6 +177,36 @@ def _worker_embedding(rank: int, world: int, port: int, reference: str, out_path
     dist.destroy_process_group()
 
 
+def _worker_fused_experts(rank: int, reference: str, out_path: str) -> None:
+    """The reference's fused_experts (layers/fused_moe/fused_moe.py:411-544) with its own Triton kernel
+    (:15-148) executed by the Triton interpreter on CPU tensors.  fp16 only: the interpreter of the installed
+    Triton mishandles bf16.  The CUDA ops it calls are shimmed with the oracle's restatements (they are pinned
+    separately against the reference's compiled kernels)."""
+    os.environ["TRITON_INTERPRET"] = "1"  # before triton is imported
+    _install_shims(reference)
+    from oracle import tp_layer_oracle as O
+    import importlib
+
+    def moe_align_block_size(topk_ids, num_experts, block_size, sorted_ids, experts, num_post_pad):
+        s_, e_, n_ = O.moe_align_block_size(topk_ids, block_size, num_experts)
+        sorted_ids.copy_(s_); experts.copy_(e_.clamp(min=0)); num_post_pad.copy_(n_)
+
+    sys.modules["sarathi.moe_ops"].moe_align_block_size = moe_align_block_size
+    torch.cuda.get_device_name = lambda *a, **k: "CPU"  # no tuned tile file: the reference's default tiles
+    FM = importlib.import_module("sarathi.model_executor.layers.fused_moe.fused_moe")
+    g = torch.Generator().manual_seed(23)
+    T, E, H, I, k = 40, 4, 96, 80, 2
+    x = torch.randn(T, H, generator=g).to(torch.float16)
+    w1 = (torch.randn(E, 2 * I, H, generator=g) * 0.1).to(torch.float16)
+    w2 = (torch.randn(E, H, I, generator=g) * 0.1).to(torch.float16)
+    tw, ti, _ = O.topk_softmax(torch.randn(T, E, generator=g), k, True)
+    out = FM.fused_experts(x, w1, w2, tw, ti.to(torch.int32), inplace=False)
+    np.savez_compressed(out_path, x=x.view(torch.int16).numpy(), w1=w1.view(torch.int16).numpy(),
+                        w2=w2.view(torch.int16).numpy(), topk_weights=tw.numpy(), topk_ids=ti.numpy().astype(np.int32),
+                        out=out.view(torch.int16).numpy())
+    print(f"wrote {out_path} ({os.path.getsize(out_path) / 1024:.0f} KiB)")
+
+
 def main() -> None:
     ap = argparse.ArgumentParser()
     ap.add_argument("--reference", default="/root/reference")
@@ -190,6 +220,8 @@ def main() -> None:
         out_path = os.path.join(HERE, f"{case_name}_tp{world}.npz")
         mp.spawn(_worker, args=(world, case_name, port, a.reference, out_path), nprocs=world)
         port += 1
+    if not a.only or a.only == "fused_experts":
+        mp.spawn(_worker_fused_experts, args=(a.reference, os.path.join(HERE, "fused_experts_f16.npz")), nprocs=1)
     if not a.only or a.only == "vocab_embedding":
         mp.spawn(_worker_embedding, args=(2, port, a.reference, os.path.join(HERE, "vocab_embedding_tp2.npz")), nprocs=2)
 
