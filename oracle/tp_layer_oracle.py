@@ -24,7 +24,8 @@ Pinning:
   * fused_experts() (the reference's Triton grouped GEMMs, layers/fused_moe/fused_moe.py:15-148,411-544) is
     checked against a fixture made by running the reference's own kernel in the Triton interpreter on the CPU
     (fp16 only -- the installed interpreter mishandles bf16; tests/golden/make_golden.py): equal except for
-    one-ulp differences where the order of the fp32 additions along K decides a rounding.
+    one-ulp differences where the order of the fp32 additions along K decides a rounding; moe_layer() likewise
+    against the reference's MixtralMoE block over two gloo ranks.
 """
 from __future__ import annotations
 

@@ -207,6 +207,59 @@ def _worker_fused_experts(rank: int, reference: str, out_path: str) -> None:
     print(f"wrote {out_path} ({os.path.getsize(out_path) / 1024:.0f} KiB)")
 
 
+def _worker_moe_block(rank: int, world: int, port: int, reference: str, out_path: str) -> None:
+    """The reference's MixtralMoE block (models/mixtral.py:58-108: replicated gate, FusedMoE with the experts
+    sharded along the intermediate dimension, SUM all-reduce) over gloo ranks, fp16, its Triton kernel run
+    by the Triton interpreter."""
+    os.environ["TRITON_INTERPRET"] = "1"
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    import torch.distributed as dist
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    _install_shims(reference)
+    from oracle import tp_layer_oracle as O
+
+    def moe_align_block_size(topk_ids, num_experts, block_size, sorted_ids, experts, num_post_pad):
+        s_, e_, n_ = O.moe_align_block_size(topk_ids, block_size, num_experts)
+        sorted_ids.copy_(s_); experts.copy_(e_.clamp(min=0)); num_post_pad.copy_(n_)
+
+    def topk_softmax(topk_weights, topk_ids, token_expert_indices, gating_output):
+        w_, i_, _ = O.topk_softmax(gating_output, topk_weights.shape[1], False)
+        topk_weights.copy_(w_); topk_ids.copy_(i_)
+
+    sys.modules["sarathi.moe_ops"].moe_align_block_size = moe_align_block_size
+    sys.modules["sarathi.moe_ops"].topk_softmax = topk_softmax
+    torch.cuda.get_device_name = lambda *a, **k: "CPU"
+    from sarathi.config import MetricsConfig
+    from sarathi.metrics.metrics_store import MetricsStore
+    MetricsStore.get_or_create_instance(None, None, MetricsConfig(write_metrics=False))
+    from sarathi.model_executor.parallel_utils import parallel_state as ps
+    ps.initialize_model_parallel(world, 1)
+    from sarathi.model_executor.models.mixtral import MixtralMoE
+    g = torch.Generator().manual_seed(29)
+    T, E, H, I, k = 40, 4, 96, 160, 2
+    x = torch.randn(T, H, generator=g).to(torch.float16)
+    gate_w = (torch.randn(E, H, generator=g) * 0.3).to(torch.float16)
+    w_gate = (torch.randn(E, I, H, generator=g) * 0.1).to(torch.float16)
+    w_up = (torch.randn(E, I, H, generator=g) * 0.1).to(torch.float16)
+    w_down = (torch.randn(E, H, I, generator=g) * 0.1).to(torch.float16)
+    moe = MixtralMoE(E, k, H, I, params_dtype=torch.float16)
+    Ish = I // world
+    sl = slice(rank * Ish, (rank + 1) * Ish)
+    with torch.no_grad():
+        moe.gate.weight.copy_(gate_w)
+        moe.experts.w13_weight.copy_(torch.cat([w_gate[:, sl], w_up[:, sl]], dim=1))
+        moe.experts.w2_weight.copy_(w_down[:, :, sl])
+    with torch.inference_mode():
+        out = moe(x.clone())
+    if rank == 0:
+        i16 = lambda t: t.contiguous().view(torch.int16).numpy()
+        np.savez_compressed(out_path, x=i16(x), gate_w=i16(gate_w), w_gate=i16(w_gate), w_up=i16(w_up), w_down=i16(w_down),
+                            out=i16(out), world=np.array([world]), top_k=np.array([k]))
+        print(f"wrote {out_path} ({os.path.getsize(out_path) / 1024:.0f} KiB)")
+    dist.destroy_process_group()
+
+
 def main() -> None:
     ap = argparse.ArgumentParser()
     ap.add_argument("--reference", default="/root/reference")
@@ -222,6 +275,8 @@ def main() -> None:
         port += 1
     if not a.only or a.only == "fused_experts":
         mp.spawn(_worker_fused_experts, args=(a.reference, os.path.join(HERE, "fused_experts_f16.npz")), nprocs=1)
+    if not a.only or a.only == "moe_block":
+        mp.spawn(_worker_moe_block, args=(2, port + 1, a.reference, os.path.join(HERE, "moe_block_f16_tp2.npz")), nprocs=2)
     if not a.only or a.only == "vocab_embedding":
         mp.spawn(_worker_embedding, args=(2, port, a.reference, os.path.join(HERE, "vocab_embedding_tp2.npz")), nprocs=2)
 
