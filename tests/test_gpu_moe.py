@@ -93,3 +93,17 @@ def test_mixtral_moe_block_tp1():
         assert rel_err(out, ref) <= 2e-2
     finally:
         ps.destroy_model_parallel()
+
+
+def test_fused_experts_against_the_reference_fixture_fp16():
+    """The committed output of the reference's own fused_experts (its Triton kernel, fp16,
+    tests/golden/fused_experts_f16.npz) -- ragged sizes: H=96, per-expert intermediate 80."""
+    import os
+    import numpy as np
+    from sarathi_serve_b200 import fused_moe as FM
+    g = np.load(os.path.join(os.path.dirname(__file__), "golden", "fused_experts_f16.npz"))
+    h = lambda name: torch.from_numpy(g[name]).view(torch.float16)
+    out = FM.fused_experts(h("x").cuda(), h("w1").cuda(), h("w2").cuda(), torch.from_numpy(g["topk_weights"]).cuda(),
+                           torch.from_numpy(g["topk_ids"]).cuda(), inplace=False)
+    _check_status()
+    assert rel_err(out, h("out")) <= 2e-3
