@@ -260,6 +260,33 @@ def _worker_moe_block(rank: int, world: int, port: int, reference: str, out_path
     dist.destroy_process_group()
 
 
+ROPE_VARIANTS = {
+    "plain": (64, 64, 128, 10000, None),
+    "partial": (64, 32, 128, 10000, None),
+    "linear": (64, 64, 128, 10000, {"type": "linear", "factor": 2.0}),
+    "dynamic": (64, 64, 128, 10000, {"type": "dynamic", "factor": 2.0}),
+    "yarn": (64, 64, 256, 10000, {"type": "yarn", "factor": 2.0, "original_max_position_embeddings": 128}),
+    "yarn_opts": (128, 128, 512, 500000, {"type": "yarn", "factor": 4.0, "original_max_position_embeddings": 128,
+                                          "beta_fast": 16, "beta_slow": 2, "attn_factor": 0.9}),
+}
+
+
+def _worker_rope(rank: int, reference: str, out_path: str) -> None:
+    """cos|sin tables of the reference's RotaryEmbedding variants (layers/rotary_embedding.py:33-345), fp32."""
+    _install_shims(reference)
+    from sarathi.model_executor.layers.rotary_embedding import get_rope
+    torch.set_default_dtype(torch.float32)
+    arrays = {}
+    for name, (hs, rot, max_pos, base, scaling) in ROPE_VARIANTS.items():
+        cache = get_rope(hs, rot, max_pos, base, True, scaling).cos_sin_cache.float()
+        rows = sorted(set(range(8)) | set(range(cache.shape[0] - 8, cache.shape[0])) | set(range(0, cache.shape[0], 9)))
+        arrays[name] = cache[rows].numpy()
+        arrays[name + "__rows"] = np.array(rows)
+        arrays[name + "__shape"] = np.array(cache.shape)
+    np.savez_compressed(out_path, **arrays)
+    print(f"wrote {out_path} ({os.path.getsize(out_path) / 1024:.0f} KiB)")
+
+
 def main() -> None:
     ap = argparse.ArgumentParser()
     ap.add_argument("--reference", default="/root/reference")
@@ -277,6 +304,8 @@ def main() -> None:
         mp.spawn(_worker_fused_experts, args=(a.reference, os.path.join(HERE, "fused_experts_f16.npz")), nprocs=1)
     if not a.only or a.only == "moe_block":
         mp.spawn(_worker_moe_block, args=(2, port + 1, a.reference, os.path.join(HERE, "moe_block_f16_tp2.npz")), nprocs=2)
+    if not a.only or a.only == "rope":
+        mp.spawn(_worker_rope, args=(a.reference, os.path.join(HERE, "rope_variants.npz")), nprocs=1)
     if not a.only or a.only == "vocab_embedding":
         mp.spawn(_worker_embedding, args=(2, port, a.reference, os.path.join(HERE, "vocab_embedding_tp2.npz")), nprocs=2)
 

@@ -111,3 +111,20 @@ def test_moe_block_matches_the_reference_mixtral_moe_over_two_ranks():
     ref = h("out")
     assert float((got != ref).float().mean()) <= 0.02
     assert rel_err(got, ref) <= 5e-4
+
+
+def test_rope_variant_tables_match_the_reference():
+    """cos|sin tables of the reference's RotaryEmbedding, LinearScaling, DynamicNTKScaling and YaRN variants
+    (layers/rotary_embedding.py:33-345; fixture rows from tests/golden/make_golden.py): this package's get_rope
+    builds the same tables bit for bit (fp32)."""
+    import os
+    import sys
+    import numpy as np
+    sys.path.insert(0, os.path.join(os.path.dirname(__file__), "golden"))
+    from make_golden import ROPE_VARIANTS
+    from sarathi_serve_b200.nn_layers import get_rope
+    g = np.load(os.path.join(os.path.dirname(__file__), "golden", "rope_variants.npz"))
+    for name, (hs, rot, max_pos, base, scaling) in ROPE_VARIANTS.items():
+        ours = get_rope(hs, rot, max_pos, base, True, scaling).cos_sin_cache.float().cpu()
+        assert tuple(ours.shape) == tuple(g[name + "__shape"]), name
+        assert torch.equal(ours[torch.from_numpy(g[name + "__rows"])], torch.from_numpy(g[name])), name
