@@ -329,6 +329,30 @@ def moe_layer(x: torch.Tensor, gate_w: torch.Tensor, w13: Sequence[torch.Tensor]
     return sum_over_ranks(parts)
 
 
+def mixtral_decoder_layer(attn_params: Sequence[Dict[str, torch.Tensor]], gate_w: torch.Tensor,
+                          w13: Sequence[torch.Tensor], w2: Sequence[torch.Tensor], x: torch.Tensor,
+                          positions: torch.Tensor, *, num_heads: int, num_kv_heads: int, head_dim: int, eps: float,
+                          cache: torch.Tensor, top_k: int) -> torch.Tensor:
+    """models/mixtral.py:235-258 (MixtralDecoderLayer.forward) over len(attn_params) simulated ranks: the
+    attention block of the Llama layer (qkv, rotary, stand-in attn_out = q, o_proj + SUM all-reduce, residual
+    add), post-attention norm, then the MoE block (moe_layer) and the second residual add.
+    attn_params[r]: rank r's "input_layernorm.weight", "post_attention_layernorm.weight",
+    "self_attn.qkv_proj.weight", "self_attn.o_proj.weight"."""
+    world = len(attn_params)
+    nq, nkv = num_heads // world, max(1, num_kv_heads // world)
+    q_size, kv_size = nq * head_dim, nkv * head_dim
+    o_parts = []
+    for p in attn_params:
+        h = rms_norm(x, p["input_layernorm.weight"], eps)
+        qkv = linear(h, p["self_attn.qkv_proj.weight"])
+        q, k, _v = qkv.split([q_size, kv_size, kv_size], dim=-1)
+        rotary_embedding(positions, q, k, head_dim, cache, True)
+        o_parts.append(linear(q.contiguous(), p["self_attn.o_proj.weight"]))
+    hidden = x + sum_over_ranks(o_parts)
+    h2 = rms_norm(hidden, attn_params[0]["post_attention_layernorm.weight"], eps)
+    return hidden + moe_layer(h2, gate_w, w13, w2, top_k)
+
+
 def rel_err(a: torch.Tensor, ref: torch.Tensor) -> float:
     """The parity measure used everywhere: max|a - ref| / max|ref| (element-wise relative
     error is meaningless near zero)."""

@@ -260,6 +260,84 @@ def _worker_moe_block(rank: int, world: int, port: int, reference: str, out_path
     dist.destroy_process_group()
 
 
+def mixtral_case(world: int, rank: int):
+    """Seeded tensors of the small Mixtral-shaped layer used by the fixture and by the tests (fp16): returns
+    (config namespace, full-size tensors, this rank's shards)."""
+    from types import SimpleNamespace
+    H, nq, nkv, hd, I, E, k, T = 128, 2, 2, 64, 160, 4, 2, 40
+    cfg = SimpleNamespace(hidden_size=H, num_attention_heads=nq, num_key_value_heads=nkv, intermediate_size=I,
+                          num_local_experts=E, num_experts_per_tok=k, rms_norm_eps=1e-5, rope_theta=10000.0,
+                          rope_scaling=None, max_position_embeddings=256)
+    g = torch.Generator().manual_seed(31)
+    r = lambda *shape, s=1.0: (torch.randn(*shape, generator=g) * s).to(torch.float16)
+    full = dict(x=r(T, H), positions=torch.randint(0, 256, (T,), generator=g), wq=r(nq * hd, H, s=0.1), wk=r(nkv * hd, H, s=0.1),
+                wv=r(nkv * hd, H, s=0.1), wo=r(H, nq * hd, s=0.1), gate=r(E, H, s=0.3), w_gate=r(E, I, H, s=0.1),
+                w_up=r(E, I, H, s=0.1), w_down=r(E, H, I, s=0.1), ln1=(1 + 0.05 * torch.randn(H, generator=g)).to(torch.float16),
+                ln2=(1 + 0.05 * torch.randn(H, generator=g)).to(torch.float16))
+    ch = lambda t_, dim: t_.chunk(world, dim=dim)[rank]
+    ish = slice(rank * (I // world), (rank + 1) * (I // world))
+    shard = {"input_layernorm.weight": full["ln1"], "post_attention_layernorm.weight": full["ln2"],
+             "self_attn.qkv_proj.weight": torch.cat([ch(full["wq"], 0), ch(full["wk"], 0), ch(full["wv"], 0)]).contiguous(),
+             "self_attn.o_proj.weight": ch(full["wo"], 1).contiguous(),
+             "block_sparse_moe.gate.weight": full["gate"],
+             "block_sparse_moe.experts.w13_weight": torch.cat([full["w_gate"][:, ish], full["w_up"][:, ish]], dim=1).contiguous(),
+             "block_sparse_moe.experts.w2_weight": full["w_down"][:, :, ish].contiguous()}
+    return cfg, full, shard
+
+
+def _worker_mixtral_layer(rank: int, world: int, port: int, reference: str, out_path: str) -> None:
+    """The reference's MixtralDecoderLayer (models/mixtral.py:194-258) over gloo ranks, fp16, Triton interpreter."""
+    os.environ["TRITON_INTERPRET"] = "1"
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    import torch.distributed as dist
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    _install_shims(reference)
+    from oracle import tp_layer_oracle as O
+
+    def moe_align_block_size(topk_ids, num_experts, block_size, sorted_ids, experts, num_post_pad):
+        s_, e_, n_ = O.moe_align_block_size(topk_ids, block_size, num_experts)
+        sorted_ids.copy_(s_); experts.copy_(e_.clamp(min=0)); num_post_pad.copy_(n_)
+
+    def topk_softmax(topk_weights, topk_ids, token_expert_indices, gating_output):
+        w_, i_, _ = O.topk_softmax(gating_output, topk_weights.shape[1], False)
+        topk_weights.copy_(w_); topk_ids.copy_(i_)
+
+    sys.modules["sarathi.moe_ops"].moe_align_block_size = moe_align_block_size
+    sys.modules["sarathi.moe_ops"].topk_softmax = topk_softmax
+    torch.cuda.get_device_name = lambda *a, **k: "CPU"
+    from sarathi.config import MetricsConfig
+    from sarathi.metrics.metrics_store import MetricsStore
+    MetricsStore.get_or_create_instance(None, None, MetricsConfig(write_metrics=False))
+    from sarathi.model_executor.parallel_utils import parallel_state as ps
+    ps.initialize_model_parallel(world, 1)
+    from sarathi.model_executor.attention.base_attention_wrapper import BaseAttentionWrapper
+    from sarathi.model_executor.models.mixtral import MixtralDecoderLayer
+    cfg, full, shard = mixtral_case(world, rank)
+    torch.set_default_dtype(torch.float16)
+    layer = MixtralDecoderLayer(cfg, layer_id=0)
+    sd = layer.state_dict()
+    with torch.no_grad():
+        for name, value in shard.items():
+            sd[name].copy_(value)
+
+    class Attn(BaseAttentionWrapper):
+        def __init__(self): pass
+        def init_gpu_cache(self, n): pass
+        def get_cache_block(self, n, **k): pass
+        def begin_forward(self, l): pass
+        def end_forward(self): pass
+        def forward(self, q, k, v, idx, softmax_scale=1.0, layer_id=None):
+            return q.contiguous()
+
+    with torch.inference_mode():
+        out = layer(full["positions"], full["x"].clone(), 0, Attn())
+    if rank == 0:
+        np.savez_compressed(out_path, out=out.contiguous().view(torch.int16).numpy(), world=np.array([world]))
+        print(f"wrote {out_path} ({os.path.getsize(out_path) / 1024:.0f} KiB)")
+    dist.destroy_process_group()
+
+
 ROPE_VARIANTS = {
     "plain": (64, 64, 128, 10000, None),
     "partial": (64, 32, 128, 10000, None),
@@ -304,6 +382,9 @@ def main() -> None:
         mp.spawn(_worker_fused_experts, args=(a.reference, os.path.join(HERE, "fused_experts_f16.npz")), nprocs=1)
     if not a.only or a.only == "moe_block":
         mp.spawn(_worker_moe_block, args=(2, port + 1, a.reference, os.path.join(HERE, "moe_block_f16_tp2.npz")), nprocs=2)
+    if not a.only or a.only == "mixtral_layer":
+        mp.spawn(_worker_mixtral_layer, args=(2, port + 2, a.reference, os.path.join(HERE, "mixtral_layer_f16_tp2.npz")),
+                 nprocs=2)
     if not a.only or a.only == "rope":
         mp.spawn(_worker_rope, args=(a.reference, os.path.join(HERE, "rope_variants.npz")), nprocs=1)
     if not a.only or a.only == "vocab_embedding":

@@ -107,3 +107,46 @@ def test_fused_experts_against_the_reference_fixture_fp16():
                            torch.from_numpy(g["topk_ids"]).cuda(), inplace=False)
     _check_status()
     assert rel_err(out, h("out")) <= 2e-3
+
+
+def test_mixtral_decoder_layer_tp1_against_oracle_and_reference_fixture():
+    """MixtralDecoderLayer (attention block with the fused o_proj tail + MoE block), fp16, one rank: against the
+    oracle's layer and against the output of the reference's own layer (tests/golden/mixtral_layer_f16_tp2.npz,
+    made over two ranks -- the layer output does not depend on the tensor-parallel size beyond rounding)."""
+    import os
+    import sys
+    import numpy as np
+    sys.path.insert(0, os.path.join(os.path.dirname(__file__), "golden"))
+    from make_golden import mixtral_case
+    from test_oracle_golden import _mixtral_oracle
+    from sarathi_serve_b200 import parallel_state as ps
+    from sarathi_serve_b200.decoder_layer import MixtralDecoderLayer
+
+    class Q:
+        def forward(self, q, k, v, layer_cache_idx, softmax_scale=1.0, layer_id=None):
+            return q
+
+    ps.destroy_model_parallel()
+    ps.initialize_model_parallel(1)
+    try:
+        cfg, full, shard = mixtral_case(1, 0)
+        old = torch.get_default_dtype()
+        torch.set_default_dtype(torch.float16)
+        try:
+            layer = MixtralDecoderLayer(cfg, layer_id=0)
+        finally:
+            torch.set_default_dtype(old)
+        sd = layer.state_dict()
+        with torch.no_grad():
+            for name, value in shard.items():
+                sd[name].copy_(value)
+        with torch.inference_mode():
+            out = layer(full["positions"].cuda(), full["x"].cuda(), 0, Q())
+        _check_status()
+        ps.get_tensor_model_parallel_comm().check_status()
+        _, _, ref = _mixtral_oracle(1)
+        assert rel_err(out, ref) <= 5e-3
+        g = np.load(os.path.join(os.path.dirname(__file__), "golden", "mixtral_layer_f16_tp2.npz"))
+        assert rel_err(out, torch.from_numpy(g["out"]).view(torch.float16)) <= 5e-3
+    finally:
+        ps.destroy_model_parallel()
