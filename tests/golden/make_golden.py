@@ -260,6 +260,65 @@ def _worker_moe_block(rank: int, world: int, port: int, reference: str, out_path
     dist.destroy_process_group()
 
 
+def model_stack_inputs(case):
+    """Seeded extra tensors of the two-layer model stack used by the fixture and the tests: embedding table
+    (vocabulary 1000 padded to 1024), final norm weight, lm_head, token ids."""
+    g = torch.Generator().manual_seed(21)
+    f32 = dict(generator=g, dtype=torch.float32)  # independent of the default dtype in force
+    table = torch.randn(1024, case.hidden_size, **f32).to(case.dtype)
+    final_w = (1 + 0.1 * torch.randn(case.hidden_size, **f32)).to(case.dtype)
+    head = (torch.randn(1024, case.hidden_size, **f32) * 0.05).to(case.dtype)
+    ids = torch.randint(0, 1000, (case.num_tokens,), generator=g)
+    return table, final_w, head, ids
+
+
+def _worker_model_stack(rank: int, world: int, port: int, reference: str, out_path: str) -> None:
+    """The reference's LlamaModel (models/llama.py:258-314: VocabParallelEmbedding, two LlamaDecoderLayers, final
+    RMSNorm) over gloo ranks, mini_bf16 shapes."""
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    import torch.distributed as dist
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    _install_shims(reference)
+    from sarathi_serve_b200 import synthetic as S
+    from sarathi.config import MetricsConfig
+    from sarathi.metrics.metrics_store import MetricsStore
+    MetricsStore.get_or_create_instance(None, None, MetricsConfig(write_metrics=False))
+    from sarathi.model_executor.parallel_utils import parallel_state as ps
+    ps.initialize_model_parallel(world, 1)
+    from sarathi.model_executor.attention.base_attention_wrapper import BaseAttentionWrapper
+    from sarathi.model_executor.models.llama import LlamaModel
+    case = S.CASES["mini_bf16"]
+    cfg = case.hf_config()
+    cfg.num_hidden_layers, cfg.vocab_size, cfg.pad_token_id = 2, 1000, None
+    torch.set_default_dtype(case.dtype)
+    model = LlamaModel(cfg)
+    tensors = S.generate(case)
+    for layer in model.layers:
+        S.load_layer(layer, S.shard(tensors, rank, world))
+    table, final_w, _head, ids = model_stack_inputs(case)
+    with torch.no_grad():
+        emb = model.embed_tokens
+        emb.weight.copy_(table[emb.vocab_start_index:emb.vocab_end_index])
+        model.norm.weight.copy_(final_w)
+
+    class Attn(BaseAttentionWrapper):
+        def __init__(self): pass
+        def init_gpu_cache(self, n): pass
+        def get_cache_block(self, n, **k): pass
+        def begin_forward(self, l): pass
+        def end_forward(self): pass
+        def forward(self, q, k, v, idx, softmax_scale=1.0, layer_id=None):
+            return q.contiguous()
+
+    with torch.inference_mode():
+        out = model(ids, tensors.positions, Attn())
+    if rank == 0:
+        np.savez_compressed(out_path, out=out.contiguous().view(torch.int16).numpy(), world=np.array([world]))
+        print(f"wrote {out_path} ({os.path.getsize(out_path) / 1024:.0f} KiB)")
+    dist.destroy_process_group()
+
+
 def mixtral_case(world: int, rank: int):
     """Seeded tensors of the small Mixtral-shaped layer used by the fixture and by the tests (fp16): returns
     (config namespace, full-size tensors, this rank's shards)."""
@@ -269,11 +328,11 @@ def mixtral_case(world: int, rank: int):
                           num_local_experts=E, num_experts_per_tok=k, rms_norm_eps=1e-5, rope_theta=10000.0,
                           rope_scaling=None, max_position_embeddings=256)
     g = torch.Generator().manual_seed(31)
-    r = lambda *shape, s=1.0: (torch.randn(*shape, generator=g) * s).to(torch.float16)
+    r = lambda *shape, s=1.0: (torch.randn(*shape, generator=g, dtype=torch.float32) * s).to(torch.float16)
     full = dict(x=r(T, H), positions=torch.randint(0, 256, (T,), generator=g), wq=r(nq * hd, H, s=0.1), wk=r(nkv * hd, H, s=0.1),
                 wv=r(nkv * hd, H, s=0.1), wo=r(H, nq * hd, s=0.1), gate=r(E, H, s=0.3), w_gate=r(E, I, H, s=0.1),
-                w_up=r(E, I, H, s=0.1), w_down=r(E, H, I, s=0.1), ln1=(1 + 0.05 * torch.randn(H, generator=g)).to(torch.float16),
-                ln2=(1 + 0.05 * torch.randn(H, generator=g)).to(torch.float16))
+                w_up=r(E, I, H, s=0.1), w_down=r(E, H, I, s=0.1), ln1=(1 + 0.05 * torch.randn(H, generator=g, dtype=torch.float32)).to(torch.float16),
+                ln2=(1 + 0.05 * torch.randn(H, generator=g, dtype=torch.float32)).to(torch.float16))
     ch = lambda t_, dim: t_.chunk(world, dim=dim)[rank]
     ish = slice(rank * (I // world), (rank + 1) * (I // world))
     shard = {"input_layernorm.weight": full["ln1"], "post_attention_layernorm.weight": full["ln2"],
@@ -382,6 +441,9 @@ def main() -> None:
         mp.spawn(_worker_fused_experts, args=(a.reference, os.path.join(HERE, "fused_experts_f16.npz")), nprocs=1)
     if not a.only or a.only == "moe_block":
         mp.spawn(_worker_moe_block, args=(2, port + 1, a.reference, os.path.join(HERE, "moe_block_f16_tp2.npz")), nprocs=2)
+    if not a.only or a.only == "model_stack":
+        mp.spawn(_worker_model_stack, args=(2, port + 3, a.reference, os.path.join(HERE, "llama_model_mini_bf16_tp2.npz")),
+                 nprocs=2)
     if not a.only or a.only == "mixtral_layer":
         mp.spawn(_worker_mixtral_layer, args=(2, port + 2, a.reference, os.path.join(HERE, "mixtral_layer_f16_tp2.npz")),
                  nprocs=2)

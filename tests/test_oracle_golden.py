@@ -157,3 +157,30 @@ def test_mixtral_decoder_layer_matches_the_reference_over_two_ranks():
     _, _, got = _mixtral_oracle(int(g["world"][0]))
     assert float((got != ref).float().mean()) <= 0.03
     assert rel_err(got, ref) <= 1e-3
+
+
+def test_model_stack_chain_matches_the_reference_llama_model():
+    """Fixture made by the reference's own LlamaModel (VocabParallelEmbedding, two decoder layers, final RMSNorm)
+    over two gloo ranks: the oracle's chain embedding -> decoder_layer x 2 -> rms_norm reproduces it (bf16; the
+    same chain is what the GPU model-stack test compares the fused stack with)."""
+    import dataclasses
+    import os
+    import sys
+    import numpy as np
+    sys.path.insert(0, os.path.join(os.path.dirname(__file__), "golden"))
+    from make_golden import model_stack_inputs
+    g = np.load(os.path.join(os.path.dirname(__file__), "golden", "llama_model_mini_bf16_tp2.npz"))
+    world = int(g["world"][0])
+    case = S.CASES["mini_bf16"]
+    t = S.generate(case)
+    table, final_w, _head, ids = model_stack_inputs(case)
+    h = O.vocab_parallel_embedding(ids, list(table.chunk(world, dim=0)))
+    cache = O.cos_sin_cache(case.head_dim, case.head_dim, case.max_position, case.rope_theta, case.dtype)
+    for _ in range(2):
+        tt = dataclasses.replace(t, x=h.float())
+        h = O.decoder_layer([S.shard(tt, r, world) for r in range(world)], h, t.positions, num_heads=case.num_heads,
+                            num_kv_heads=case.num_kv_heads, head_dim=case.head_dim, eps=case.rms_norm_eps,
+                            cache=cache)["out"]
+    got = O.rms_norm(h, final_w, case.rms_norm_eps)
+    ref = torch.from_numpy(g["out"]).view(torch.bfloat16)
+    assert torch.equal(got, ref)
