@@ -4,7 +4,7 @@
     python bench.py --gpus N --steps K --warmup W            # this library, TP = N
     python bench.py --impl reference --gpus N --steps K ...  # CPU arm (oracle port of the reference path)
 
-A step = one Llama-3-8B-shaped decoder layer (BASELINE config 2: hidden 4096,
+A step = one Llama-3-8B-shaped decoder layer (hidden 4096,
 32 q / 8 kv heads, head_dim 128, intermediate 14336, bf16) over one Sarathi
 mixed chunk of 512 tokens (448 prefill + 64 decode), tensor-parallel over N
 GPUs, attention replaced by the stand-in attn_out = q (attention is outside
@@ -180,9 +180,16 @@ def time_cpu(case, budget_s: float, warmup: int = 1, max_iters: int = 50, min_it
     return tokens / med, threads, len(times), med
 
 
+def bench_config(workload: str, world: int, tokens: int) -> dict:
+    """The `config` object of the JSON line: the same in both arms."""
+    return {"workload": workload_text(workload, world), "tokens_per_step": tokens, "parallelism": f"tp{world}"}
+
+
 def run_reference_arm(a):
     """The reference's path on the host cores: the oracle port (torch CPU kernels, bf16, all host
-    threads) of LlamaDecoderLayer over the same workload; rank 0 only."""
+    threads) of LlamaDecoderLayer over the same workload, every shard of the layer in one process;
+    rank 0 only.  A step = one full pass of the workload (about 30 ms), so `--steps` / `--warmup` are
+    taken as given."""
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
@@ -190,8 +197,7 @@ def run_reference_arm(a):
     case = S.CASES[a.workload]
     threads = os.cpu_count() or 1
     fn, tokens = cpu_layer_runner(case, threads)
-    steps = max(1, min(a.steps, 20))
-    warm = max(1, min(a.warmup, 3))
+    steps, warm = max(1, a.steps), max(0, a.warmup)
     for _ in range(warm):
         fn()
     t0 = time.perf_counter()
@@ -202,18 +208,48 @@ def run_reference_arm(a):
     line = {"metric": METRIC, "value": v, "unit": UNIT, "n_gpus": a.gpus, "steps": steps, "warmup": warm,
             "ms_per_step": dt * 1e3, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
             "dtype": "bf16", "data": "synthetic", "impl": "reference",
-            "config": {"workload": workload_text(a.workload, a.gpus), "tokens_per_step": tokens,
-                       "parallelism": f"tp{a.gpus}",
-                       "how": "oracle port of the reference layer path, one process on the host cores (the whole "
-                              "layer, all shards)"},
+            "config": bench_config(a.workload, a.gpus, tokens),
+            "how": "oracle port of the reference layer path, one process on the host cores (the whole layer, all "
+                   "shards)",
             "cpu_baseline": {"value": v, "unit": UNIT, "cores": threads, "kind": "port",
-                             "sample": f"{steps} full layer passes of the workload (steps capped at 20)"},
+                             "sample": f"{steps} full layer passes of the workload"},
             "e2e": {"value": v, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
             "gpu_launches": 0}
     print(json.dumps(line), flush=True)
 
 
 # --------------------------------------------------------------- native arm
+PARITY_TOL = 2e-2  # bf16: max|a - b| / max|ref| per tensor
+
+
+def check_parity(case, t, world, rank, dev, step_resident, runner0, layers, max_over_ranks) -> dict:
+    import torch
+    from oracle import tp_layer_oracle as O
+    from sarathi_serve_b200 import synthetic as S
+    T = case.num_tokens
+    normed, resid = step_resident(0)
+    normed, resid = normed.clone(), resid.clone()
+    host_out = runner0.replay_host_io()
+    torch.cuda.current_stream().synchronize()
+    e2e_out = host_out.clone()
+    shards = [S.shard(t, r, world) for r in range(world)]
+    cache = O.cos_sin_cache(case.head_dim, case.head_dim, case.max_position, case.rope_theta, case.dtype)
+    nxt_w = layers[1 % len(layers)].input_layernorm.weight.data.cpu()
+    ref = O.decoder_layer(shards, t.x.to(case.dtype), t.positions, num_heads=case.num_heads,
+                          num_kv_heads=case.num_kv_heads, head_dim=case.head_dim, eps=case.rms_norm_eps, cache=cache,
+                          next_norm_weight=nxt_w)
+    rpr = -(-T // world)
+    lo, hi = rank * rpr, min(T, rank * rpr + rpr)
+    err_out = O.rel_err(normed.cpu(), ref["out_normed"])
+    err_res = float((resid[lo:hi].cpu().double() - ref["out"][lo:hi].double()).abs().max()) / float(ref["out"].double().abs().max())
+    err_e2e = O.rel_err(e2e_out, ref["out"])
+    p = {"max_rel_err_out": max_over_ranks(err_out), "max_rel_err_residual_rows": max_over_ranks(err_res),
+         "max_rel_err_e2e": max_over_ranks(err_e2e), "tol": PARITY_TOL,
+         "against": f"CPU oracle of the layer over all {world} shards; every rank checks its outputs, max over ranks"}
+    p["ok"] = all(p[k] <= PARITY_TOL for k in ("max_rel_err_out", "max_rel_err_residual_rows", "max_rel_err_e2e"))
+    return p
+
+
 class QAttention:
     def forward(self, q, k, v, layer_cache_idx, softmax_scale=1.0, layer_id=None):
         return q
@@ -351,6 +387,11 @@ def run_native(a):
         ms_e2e = max_over_ranks((time.perf_counter() - t0) * 1e3 / e2e_steps)
         comm.check_status()
 
+        # ---- parity of what was just timed, outside the timed regions: one resident step (normed output on
+        # every rank, the rows of the new residual this rank owns) and one end-to-end step (host buffers in,
+        # host buffer out) against the CPU oracle of the layer over all `world` shards
+        parity = check_parity(case, t, world, rank, dev, step_resident, runners[0], layers, max_over_ranks)
+
         def graph_ms(fn, n, reps=5, lead_in=True):
             """Mean device time of one fn(i) call: n calls captured in a CUDA graph, replayed reps times;
             lead_in: about 0.3 s of the same load first (the power / clock state of a long run)."""
@@ -431,10 +472,10 @@ def run_native(a):
         line = {"metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": a.steps, "warmup": a.warmup,
                 "ms_per_step": ms_resident, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
                 "dtype": "bf16", "data": "synthetic",
-                "config": {"workload": workload_text(a.workload, world),
-                           "tokens_per_step": T, "parallelism": f"tp{world}",
-                           "l2": f"{n_layers} distinct weight sets ({n_layers * per_layer_bytes >> 20} MiB/GPU) cycled: "
-                                 "operands of consecutive steps exceed the 126 MB L2"},
+                "config": bench_config(a.workload, world, T),
+                "l2": f"{n_layers} distinct weight sets ({n_layers * per_layer_bytes >> 20} MiB/GPU) cycled: "
+                      "operands of consecutive steps exceed the 126 MB L2",
+                "parity": parity,
                 "clocks": clocks,
                 "e2e": {"value": T / (ms_e2e * 1e-3), "unit": UNIT, "ms_per_step": ms_e2e,
                         "h2d_bytes_per_step": T * H * es + T * 8, "d2h_bytes_per_step": T * H * es},
@@ -455,7 +496,7 @@ def run_native(a):
                                             ", one CUDA graph", "ms_per_step": ms_cublas,
                                     "value": T / (ms_cublas * 1e-3), "unit": UNIT} if ms_cublas else
                                    {"unavailable": cublas_err})}
-        if not a.no_cpu_baseline and world == 1:
+        if not a.no_cpu_baseline:
             v, cores, iters, med = time_cpu(case, a.cpu_baseline_seconds)
             line["cpu_baseline"] = {"value": v, "unit": UNIT, "cores": cores, "kind": "port",
                                     "sample": f"{iters} full layer passes of the same workload "
@@ -465,6 +506,8 @@ def run_native(a):
     ps.destroy_model_parallel()
     if world > 1:
         dist.destroy_process_group()
+    if not parity["ok"]:
+        raise SystemExit(f"parity against the oracle failed: {parity}")
 
 
 def run_parts(a):

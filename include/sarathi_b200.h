@@ -251,10 +251,22 @@ int sb200_comm_set_one_shot_bytes(sb200_comm* comm, int64_t bytes);
  * SB200_ERR_PEER_TIMEOUT if a bounded wait ran out since the last clear. */
 int sb200_comm_status(sb200_comm* comm, sb200_stream_t stream, uint32_t* host_status);
 int sb200_comm_clear_status(sb200_comm* comm, sb200_stream_t stream);
-/* Profiling aid: with a device buffer of 148 * 8 uint64, thread 0 of every CTA of the collective
- * kernels records %globaltimer (ns) at: 0 start, 1 own partial rows stored, 2 reduce entered, 3 every
- * rank's "partials stored" flag seen, 4 owned rows reduced, 5 other ranks' rows gathered, 6 exit.  NULL switches it off (default). */
-int sb200_comm_set_trace(sb200_comm* comm, void* device_buffer);
+/* `multicast_base`: address at which ALL ranks' heaps are mapped as one NVSwitch multicast range (same
+ * offsets as the heaps themselves: a multimem store there lands in every rank's heap, a multimem
+ * ld_reduce returns the element-wise sum over the heaps), e.g. the multicast pointer of a torch
+ * symmetric-memory allocation whose per-rank buffers were given to sb200_comm_create_external.  With it,
+ * collectives above the one-shot size are reduced and broadcast by the switch (multimem.ld_reduce /
+ * multimem.st) instead of by peer loads.  NULL (the default) switches that off.  Every rank must make
+ * the same choice.  Replaces what NCCL's NVLS algorithm does behind torch.distributed.all_reduce
+ * (tensor_parallel/mappings.py:24). */
+int sb200_comm_set_multicast(sb200_comm* comm, void* multicast_base);
+int sb200_comm_has_multicast(sb200_comm* comm);
+/* Puts the context back into its initial state (call counter, flags, arrival counters, status word).
+ * After a device-side wait has run out the ranks' counters are out of step and every later collective
+ * would miscount: all ranks call this, with nothing in flight on any of them (host barrier before and
+ * after).  Synchronises `stream`.  No counterpart in the reference (a failed NCCL communicator is
+ * destroyed and rebuilt). */
+int sb200_comm_reset(sb200_comm* comm, sb200_stream_t stream);
 
 /* Sum `in` [T, H] over the ranks; then, on the summed rows,
  *   z = sum (+ bias) (+ residual);   y = norm_w ? rms_norm(z, norm_w, eps) : z.

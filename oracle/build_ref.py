@@ -58,7 +58,7 @@ def _compile(src: str, obj: str, name: str, common):
     return obj
 
 
-def build(reference: str = "/root/reference", jobs: int = 0, verbose: bool = True) -> bool:
+def build(reference: str, jobs: int = 0, verbose: bool = True) -> bool:
     """Build every extension that is out of date. Returns False if the reference is absent."""
     csrc = os.path.join(reference, "csrc")
     if not os.path.isdir(csrc):
@@ -105,7 +105,8 @@ def build(reference: str = "/root/reference", jobs: int = 0, verbose: bool = Tru
 
 if __name__ == "__main__":
     ap = argparse.ArgumentParser()
-    ap.add_argument("--reference", default="/root/reference")
+    ap.add_argument("--reference", default=os.environ.get("SARATHI_REFERENCE"), required="SARATHI_REFERENCE" not in os.environ,
+                    help="checkout of microsoft/sarathi-serve (or $SARATHI_REFERENCE)")
     ap.add_argument("--jobs", type=int, default=0)
     a = ap.parse_args()
     sys.exit(0 if build(a.reference, a.jobs) else 1)

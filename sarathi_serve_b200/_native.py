@@ -60,7 +60,9 @@ _GEMM_SIGS: dict = {
     "sb200_vocab_embedding": (_I, [_P, _P, _P, _L, _L, _L, _L, _I, _P]),
     "sb200_comm_set_wait_limit": (_I, [_P, _L]),
     "sb200_comm_set_one_shot_bytes": (_I, [_P, _L]),
-    "sb200_comm_set_trace": (_I, [_P, _P]),
+    "sb200_comm_set_multicast": (_I, [_P, _P]),
+    "sb200_comm_has_multicast": (_I, [_P]),
+    "sb200_comm_reset": (_I, [_P, _P]),
     "sb200_comm_status": (_I, [_P, _P, ctypes.POINTER(ctypes.c_uint32)]),
     "sb200_comm_clear_status": (_I, [_P, _P]),
     "sb200_all_reduce": (_I, [_P, _P, _L, _L, _I, _P, _P, _P, _F, _I, _P, _P, _P, _PP, _PP]),

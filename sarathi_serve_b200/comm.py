@@ -2,13 +2,20 @@
 the ranks of one node, and the collectives built on them (all-reduce and the
 row-parallel projection fused with its all-reduce, residual add and RMSNorm).
 
-torch.distributed is used only as plumbing: to exchange the 64-byte CUDA IPC
-handles once at construction and for the host barrier that follows.  The data
-path is this library's own kernels storing into peer memory over NVLink; NCCL
-is not called on it."""
+torch.distributed is used only as plumbing: the heaps come from torch's
+symmetric-memory allocator when the node's NVSwitch offers multicast (each rank's
+buffer is mapped into every peer AND all of them are bound to one multicast
+address range, which the kernels use for in-switch reduction and broadcast), or
+from cudaMalloc with the 64-byte CUDA IPC handles exchanged once at
+construction; either way a host barrier follows.  The data path is this
+library's own kernels over NVLink; NCCL is not called on it.
+
+``SB200_NVLS=0`` in the environment (or ``multicast=False``) keeps the heaps
+on plain peer mappings; every rank of a group has to make the same choice."""
 from __future__ import annotations
 
 import ctypes
+import os
 from typing import Optional, Tuple
 
 import torch
@@ -33,29 +40,74 @@ class TPComm:
     ``region_bytes`` bounds the largest [T, H] batch a collective may carry
     (T rounded up to a multiple of the group size)."""
 
-    def __init__(self, rank: int, world: int, region_bytes: int, group=None, device: Optional[torch.device] = None):
+    def __init__(self, rank: int, world: int, region_bytes: int, group=None, device: Optional[torch.device] = None,
+                 multicast: Optional[bool] = None):
         if not torch.cuda.is_available():
             raise RuntimeError("TPComm needs a CUDA device (there is no CPU fallback)")
         self.rank, self.world, self.group = rank, world, group
         self.device = torch.device("cuda", torch.cuda.current_device()) if device is None else device
         self._h = ctypes.c_void_p()
+        self._symm = None       # (tensor, handle) of the symmetric-memory allocation, when the heaps come from there
+        self._poisoned = False
+        self._status_host = None
+        self.multicast = False
         lib = N.lib()
+        if multicast is None:
+            multicast = os.environ.get("SB200_NVLS", "1") != "0"
         with torch.cuda.device(self.device):
-            N.check(lib.sb200_comm_create(ctypes.byref(self._h), rank, world, int(region_bytes)), "comm_create")
-            if world > 1:
-                import torch.distributed as dist
-                mine = (ctypes.c_ubyte * 64)()
-                N.check(lib.sb200_comm_ipc_handle(self._h, mine), "comm_ipc_handle")
-                handles = [None] * world
-                dist.all_gather_object(handles, bytes(mine), group=group)
-                blob = b"".join(handles)
-                N.check(lib.sb200_comm_open_peers(self._h, blob), "comm_open_peers")
-                dist.barrier(group=group)
+            if world > 1 and multicast and self._create_on_symmetric_memory(lib, int(region_bytes)):
+                pass
+            else:
+                N.check(lib.sb200_comm_create(ctypes.byref(self._h), rank, world, int(region_bytes)), "comm_create")
+                if world > 1:
+                    import torch.distributed as dist
+                    mine = (ctypes.c_ubyte * 64)()
+                    N.check(lib.sb200_comm_ipc_handle(self._h, mine), "comm_ipc_handle")
+                    handles = [None] * world
+                    dist.all_gather_object(handles, bytes(mine), group=group)
+                    blob = b"".join(handles)
+                    N.check(lib.sb200_comm_open_peers(self._h, blob), "comm_open_peers")
+                    dist.barrier(group=group)
         self.region_bytes = int(lib.sb200_comm_region_bytes(self._h))
         heap_ptr = lib.sb200_comm_local_heap(self._h)
         heap_bytes = int(lib.sb200_comm_heap_bytes(self.region_bytes))
         self._heap = torch.as_tensor(_DeviceMemory(heap_ptr, heap_bytes), device=self.device)
         self._heap_ptr = heap_ptr
+
+    def _create_on_symmetric_memory(self, lib, region_bytes: int) -> bool:
+        """Heaps from torch's symmetric-memory allocator, bound to an NVSwitch multicast range.  Every rank
+        reaches the same verdict (the outcome is agreed over the group), so either all ranks use these heaps
+        or none does.  Returns False when the allocator, the rendezvous or multicast is not available."""
+        import torch.distributed as dist
+        heap_bytes = int(lib.sb200_comm_heap_bytes(region_bytes))
+        tensor = handle = None
+        ok = 0
+        try:
+            import torch.distributed._symmetric_memory as symm_mem
+            grp = self.group if self.group is not None else dist.group.WORLD
+            tensor = symm_mem.empty(heap_bytes, dtype=torch.uint8, device=self.device)
+            handle = symm_mem.rendezvous(tensor, grp)
+            off = int(getattr(handle, "offset", 0))  # of the tensor inside the allocator's block
+            ptrs = [int(p) + off for p in handle.buffer_ptrs]
+            mc_ptr = int(handle.multicast_ptr) + off if int(handle.multicast_ptr) else 0
+            ok = 1 if (mc_ptr != 0 and len(ptrs) == self.world and handle.rank == self.rank
+                       and ptrs[self.rank] == tensor.data_ptr()) else 0
+        except Exception:  # allocator / rendezvous unavailable: plain peer mappings serve
+            ok = 0
+        verdict = [None] * self.world
+        dist.all_gather_object(verdict, ok, group=self.group)
+        if not all(verdict):
+            return False
+        tensor.zero_()
+        torch.cuda.synchronize(self.device)
+        dist.barrier(group=self.group)  # every heap is zeroed before anybody's kernels touch it
+        table = (ctypes.c_void_p * self.world)(*ptrs)
+        N.check(lib.sb200_comm_create_external(ctypes.byref(self._h), self.rank, self.world, region_bytes, table),
+                "comm_create_external")
+        N.check(lib.sb200_comm_set_multicast(self._h, ctypes.c_void_p(mc_ptr)), "comm_set_multicast")
+        self._symm = (tensor, handle)
+        self.multicast = True
+        return True
 
     # ------------------------------------------------------------------ utils
     def close(self) -> None:
@@ -64,6 +116,7 @@ class TPComm:
             N.lib().sb200_comm_destroy(self._h)
             self._h = ctypes.c_void_p()
             self._heap = None
+            self._symm = None
 
     def __del__(self):
         try:
@@ -80,17 +133,55 @@ class TPComm:
         them.  Every rank must set the same value."""
         N.check(N.lib().sb200_comm_set_one_shot_bytes(self._h, int(nbytes)), "comm_set_one_shot_bytes")
 
-    def set_trace(self, buffer: Optional[torch.Tensor]) -> None:
-        """Profiling aid: int64 tensor [>=148*8] on this device receives per-CTA phase time stamps (ns)."""
-        N.check(N.lib().sb200_comm_set_trace(self._h, N.ptr(buffer)), "comm_set_trace")
-
     def check_status(self) -> None:
-        """Synchronises the current stream; raises if a device-side wait on a peer ran out."""
+        """Synchronises the current stream; raises if a device-side wait ran out.  After that the ranks'
+        device-side call counters are out of step: every later collective on this context raises until all
+        ranks have called ``reset()``."""
         st = ctypes.c_uint32(0)
         rc = N.lib().sb200_comm_status(self._h, N.stream_ptr(), ctypes.byref(st))
         if rc != 0:
+            self._poisoned = True
             N.lib().sb200_comm_clear_status(self._h, N.stream_ptr())
             N.check(rc, "tensor-parallel collective")
+
+    def enqueue_status_read(self) -> None:
+        """Asynchronous copy of the device status word into pinned host memory on the current stream (it can be
+        captured into a CUDA graph); ``raise_if_flagged`` looks at the last value that arrived."""
+        if self._status_host is None:
+            self._status_host = torch.zeros(1, dtype=torch.int32).pin_memory()
+        self._status_host.copy_(self._heap[0:4].view(torch.int32), non_blocking=True)
+
+    def raise_if_flagged(self) -> None:
+        """No synchronisation: raises if the last status word read by ``enqueue_status_read`` was non-zero, i.e.
+        a device-side wait of an EARLIER step ran out (errors surface at the next launch, like the
+        asynchronous device errors of the reference's ops)."""
+        if self._status_host is None:
+            return
+        code = int(self._status_host[0])
+        if code != 0:
+            self._poisoned = True
+            raise RuntimeError(f"tensor-parallel collective: device-side wait timed out in an earlier step "
+                               f"(code {code}: {_STATUS_TEXT.get(code, 'unknown')}); call reset() on every rank")
+
+    def reset(self) -> None:
+        """Collective over the group: host barrier, control words back to their initial state, host barrier.
+        The way back after ``check_status`` raised on any rank."""
+        torch.cuda.synchronize(self.device)
+        if self.world > 1:
+            import torch.distributed as dist
+            dist.barrier(group=self.group)
+        N.check(N.lib().sb200_comm_reset(self._h, N.stream_ptr()), "comm_reset")
+        if self.world > 1:
+            import torch.distributed as dist
+            dist.barrier(group=self.group)
+        if self._status_host is not None:
+            self._status_host.zero_()
+        self._poisoned = False
+
+    def _usable(self) -> None:
+        if self._poisoned:
+            raise RuntimeError("this tensor-parallel context saw a device-side timeout: its ranks are out of step "
+                               "until every rank calls reset()")
 
     def status_code(self) -> int:
         st = ctypes.c_uint32(0)
@@ -123,6 +214,7 @@ class TPComm:
         Returns (y, z): y = the primary result on every rank, z = the pre-norm sum
         (only when norm_weight is given).  Without ``out`` / ``resid_out`` the results
         are views into the context's heap, valid until the second-next collective."""
+        self._usable()
         N.require_cuda(x, bias, residual, norm_weight, out, resid_out)
         if x.dim() != 2 or not x.is_contiguous():
             raise RuntimeError("all_reduce: input must be a contiguous [T, H] tensor")
@@ -144,6 +236,7 @@ class TPComm:
                       tile_n: int = 0) -> Tuple[torch.Tensor, Optional[torch.Tensor]]:
         """(x[T, K/tp] @ weight[N, K/tp]^T) summed over the group, with the same tail
         and result conventions as ``all_reduce`` -- one kernel for bf16/fp16."""
+        self._usable()
         N.require_cuda(x, weight, bias, residual, norm_weight, out, resid_out)
         if x.dim() != 2 or x.stride(1) != 1 or weight.dim() != 2 or weight.stride(1) != 1:
             raise RuntimeError("rowpar_linear: x and weight must be 2-D with unit inner stride")

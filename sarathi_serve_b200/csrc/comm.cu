@@ -19,6 +19,7 @@ struct sb200_comm {
   void* heap[sb200::kMaxRanks];
   bool own_heap;
   bool ipc_opened[sb200::kMaxRanks];
+  void* mc;          // multicast alias of all ranks' heaps (NVSwitch), or null
   uint64_t seq;
   long long wait_cycles;
   unsigned long long* trace;
@@ -37,6 +38,7 @@ static CommView make_view(const sb200_comm* c) {
   v.rank = c->rank;
   v.world = c->world;
   for (int i = 0; i < c->world; ++i) v.heap[i] = (char*)c->heap[i];
+  v.mc = (char*)c->mc;
   size_t off = kCounterBytes;
   v.partial_off[0] = off; off += c->region_bytes;
   v.partial_off[1] = off; off += c->region_bytes;
@@ -62,9 +64,10 @@ all_reduce_kernel(const __grid_constant__ CommView c, const __grid_constant__ Re
   const int nvec = a.H / N;
   const size_t total = (size_t)a.T * nvec;
   const size_t stride = (size_t)gridDim.x * blockDim.x;
+  T* const partial = (T*)partial_of(c, c.rank, call_number(c));
   for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += stride) {
     const int t = (int)(i / nvec), v = (int)(i - (size_t)t * nvec);
-    T* dst = (T*)(c.heap[c.rank] + c.partial_off[a.set]) + i * N;
+    T* dst = partial + i * N;
     if (rows_per_token == 1) {
       st16(dst, ld16(in + i * N));
     } else {
@@ -84,15 +87,51 @@ all_reduce_kernel(const __grid_constant__ CommView c, const __grid_constant__ Re
   }
   trace_mark(a, 1);
   __syncthreads();
-  // this CTA's share of the rows is stored: one arrival per owner (or one in all for a one-shot call)
-  if (a.one_shot) { if (threadIdx.x < 32) signal_push_all(c, a); }
+  // this CTA's share of the rows is stored: one arrival per owner (or one in all when every rank reads all rows)
+  if (a.one_shot || a.use_mc) { if (threadIdx.x < 32) signal_push_all(c, a); }
   else if (threadIdx.x < c.world) signal_push(c, a, threadIdx.x);
-  reduce_phase<T, kMaxVecPerLaneAllReduce>(c, a, blockIdx.x, gridDim.x);
-  trace_mark(a, 4);
-  gather_phase<T>(c, a, blockIdx.x, gridDim.x);
-  trace_mark(a, 5);
+  collective_tail<T, kMaxVecPerLaneAllReduce>(c, a, blockIdx.x, gridDim.x);
   advance_targets(c, a);
   trace_mark(a, 6);
+}
+
+// All-gather of row blocks: rank r contributes rows [r * rows_per_rank, ...) of a [T, H] tensor (`in` holds just
+// those rows); afterwards every rank has all T rows in its `out` region (and in out_copy).  The produce /
+// reduce halves of a collective do not exist here: a rank publishes its rows -- one multimem.st per 16 bytes
+// when the heaps have a multicast alias, else a local copy that the peers pull -- and flags them done.
+template <typename T>
+__global__ void __launch_bounds__(256)
+all_gather_kernel(const __grid_constant__ CommView c, const __grid_constant__ ReduceArgs a, const T* __restrict__ in) {
+  constexpr int N = Vec16<T>::N;
+  const int nvec = a.H / N;
+  const uint32_t n = call_number(c);
+  const int row0 = c.rank * a.rows_per_rank;
+  const int nrows = max(0, min(a.rows_per_rank, a.T - row0));
+  const size_t total = (size_t)nrows * nvec, base = (size_t)row0 * nvec;
+  const size_t stride = (size_t)gridDim.x * blockDim.x;
+  T* const local_out = (T*)(c.heap[c.rank] + c.out_off[a.set]);
+  T* const mc_out = a.use_mc ? (T*)(c.mc + c.out_off[a.set]) : nullptr;
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += stride) {
+    const Vec16<T> v = ld16(in + i * N);
+    if (mc_out) mc_st16(mc_out + (base + i) * N, v.raw);
+    else st16(local_out + (base + i) * N, v);
+    if (!mc_out && a.out_copy) st16((T*)a.out_copy + (base + i) * N, v);
+  }
+  __syncthreads();
+  if (threadIdx.x == 0 && nrows > 0) {
+    if (mc_out) fence_sys();  // this CTA's multicast stores are performed everywhere before the flag
+    if (arrive_acq_rel(comm_counter(c, c.rank, CC_LOCAL_DONE)) + 1u == gridDim.x) {
+      if (mc_out) {
+        mc_st_release_u32(comm_counter_mc(c, done_flag_index(n, c.rank)), n);
+      } else {
+        for (int r = 0; r < c.world; ++r)
+          if (r != c.rank) st_release(comm_counter(c, r, done_flag_index(n, c.rank)), n, true);
+      }
+    }
+  }
+  if (mc_out) mc_wait_all_done<T>(c, a, n, blockIdx.x, gridDim.x);
+  else gather_phase<T>(c, a, blockIdx.x, gridDim.x);
+  advance_targets(c, a);
 }
 
 static int all_reduce_grid(int64_t T_, int64_t H, int dtype, int rows_per_rank) {
@@ -137,11 +176,15 @@ static int plan_call(sb200_comm* c, int64_t T_, int64_t H, int dtype, const void
   // one-shot while the rows every rank would have to load stay below ~4 MB (always with two ranks,
   // where both schemes move the same bytes); the owner-reduce + gather scheme above that
   a.one_shot = (c->world == 1 || (size_t)(c->world - 1) * T_ * H * es <= c->one_shot_bytes) ? 1 : 0;
+  // larger ones go through the NVSwitch multicast alias when the heaps are bound to one
+  a.use_mc = (!a.one_shot && c->mc != nullptr) ? 1 : 0;
   a.bias = bias; a.residual = residual; a.norm_w = norm_w; a.eps = eps;
   a.write_resid_all = write_resid_all;
   a.out_copy = out_copy; a.resid_copy = resid_copy;
   a.wait_cycles = c->wait_cycles;
+#ifdef SB200_TRACE
   a.trace = c->trace;
+#endif
   p->cv = make_view(c);
   return SB200_OK;
 }
@@ -281,11 +324,36 @@ extern "C" int sb200_comm_set_one_shot_bytes(sb200_comm* c, int64_t bytes) {
   return SB200_OK;
 }
 
+extern "C" int sb200_comm_set_multicast(sb200_comm* c, void* multicast_base) {
+  SB_CHECK_ARG(c, "comm_set_multicast: null context");
+  SB_CHECK_ARG(multicast_base == nullptr || (c->world > 1 && aligned16(multicast_base)),
+               "comm_set_multicast: needs a 16-byte aligned address and more than one rank");
+  c->mc = multicast_base;
+  return SB200_OK;
+}
+
+extern "C" int sb200_comm_has_multicast(sb200_comm* c) { return (c && c->mc) ? 1 : 0; }
+
+// Back to the state of a fresh context: control words (call counter, flags, arrival counters, status) and the
+// arrival counters of the split-K workspace.  Every rank has to call it, with no collective in flight anywhere
+// (host barrier before and after), e.g. after a wait on a peer ran out and left the ranks' counters out of step.
+extern "C" int sb200_comm_reset(sb200_comm* c, sb200_stream_t stream) {
+  SB_CHECK_ARG(c, "comm_reset: null context");
+  cudaStream_t s = (cudaStream_t)stream;
+  SB_CUDA(cudaMemsetAsync(c->heap[c->rank], 0, kCounterBytes, s));
+  SB_CUDA(cudaMemsetAsync((char*)c->heap[c->rank] + scratch_off(c), 0, kWsCounterBytes, s));
+  SB_CUDA(cudaStreamSynchronize(s));
+  c->seq = 0;
+  return SB200_OK;
+}
+
+#ifdef SB200_TRACE
 extern "C" int sb200_comm_set_trace(sb200_comm* c, void* device_buffer) {
   SB_CHECK_ARG(c, "comm_set_trace: null context");
   c->trace = (unsigned long long*)device_buffer;
   return SB200_OK;
 }
+#endif
 
 extern "C" int sb200_comm_status(sb200_comm* c, sb200_stream_t stream, uint32_t* host_status) {
   SB_CHECK_ARG(c && host_status, "comm_status: bad arguments");
@@ -315,6 +383,27 @@ extern "C" int sb200_all_reduce(sb200_comm* comm, const void* in, int64_t T, int
                                 void** resid_ptr) {
   return do_all_reduce(comm, in, T, H, dtype, bias, residual, norm_w, eps, write_resid_all, out_copy, resid_copy,
                        (cudaStream_t)stream, out_ptr, resid_ptr);
+}
+
+extern "C" int sb200_all_gather_rows(sb200_comm* comm, const void* in_rows, int64_t T, int64_t H, int dtype,
+                                     void* out_copy, sb200_stream_t stream, void** out_ptr) {
+  CallPlan p;
+  int rc = plan_call(comm, T, H, dtype, nullptr, nullptr, nullptr, 0.f, 0, out_copy, nullptr, &p);
+  if (rc) return rc;
+  const int rpr = p.ra.rows_per_rank;
+  const int64_t own = T - (int64_t)comm->rank * rpr < rpr ? T - (int64_t)comm->rank * rpr : rpr;
+  SB_CHECK_ARG(own <= 0 || (in_rows && aligned16(in_rows)), "all_gather_rows: this rank's rows must be a 16-byte aligned device pointer");
+  p.ra.one_shot = 0;                       // rows always travel from their owner
+  p.ra.use_mc = comm->mc != nullptr ? 1 : 0;
+  int64_t g = ((own > 0 ? own : 1) * (H / (16 / (int64_t)dtype_size(dtype))) + 1023) / 1024;
+  if (comm->world > 1 && g < comm->world - 1) g = comm->world - 1;  // the pulling scheme wants a CTA group per peer
+  if (g > sm_count()) g = sm_count();
+  if (g < 1) g = 1;
+  commit_call(comm, &p, out_ptr, nullptr);
+  cudaStream_t s = (cudaStream_t)stream;
+  SB_DISPATCH_FLOAT(dtype, all_gather_kernel<scalar_t><<<(int)g, 256, 0, s>>>(p.cv, p.ra, (const scalar_t*)in_rows));
+  SB_CHECK_LAUNCH("all_gather_kernel");
+  return SB200_OK;
 }
 
 extern "C" int sb200_moe_sum_all_reduce(sb200_comm* comm, const void* in3, int64_t T, int top_k, int64_t H, int dtype,
@@ -359,7 +448,7 @@ extern "C" int sb200_gemm_rowpar(sb200_comm* comm, const void* x, int64_t ldx, c
     const int64_t lo = (int64_t)o * rpr, hi = (lo + rpr < T ? lo + rpr : T);
     p.ra.push_expected[o] = gemm_push_increments(plan, T, lo, hi);
   }
-  if (p.ra.one_shot) p.ra.push_expected[0] = gemm_push_increments(plan, T, 0, T);  // one arrival per finished (tile, 32-row slot)
+  if (p.ra.one_shot || p.ra.use_mc) p.ra.push_expected[0] = gemm_push_increments(plan, T, 0, T);  // one arrival per finished (tile, 32-row slot)
   GemmArgs g = {};
   g.M = (int)T; g.N = (int)N; g.K = (int)K;
   g.head_size = 128;

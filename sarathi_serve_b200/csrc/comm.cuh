@@ -3,30 +3,40 @@
 // standalone all-reduce.
 //
 // Every rank owns one "symmetric heap" with the same layout, mapped into every
-// peer (P2P over NVLink/NVSwitch).  Data crosses the links only through LOADS:
-// a rank stores into its own memory and tells its peers with one flag store.
-// One collective call ("epoch") runs as:
-//   produce : each rank writes its partial [T, H] into its OWN heap; when the
-//             rows of owner o are complete it stores the call's epoch number
-//             into o's push flag for this rank;
-//   reduce  : the owner of a row waits for every rank's push flag, loads the
-//             row from every heap, sums in fp32 (+bias, +residual), optionally
-//             RMS-normalises, and stores the finished row into its own heap;
-//             when all its rows are done it stores the epoch into every peer's
-//             done flag for this rank;
-//   gather  : each rank waits for the done flags and copies the rows it does
-//             not own from their owners' heaps into its own.
-// Row t is owned by rank t / rows_per_rank.  Buffers and flags are double
-// buffered by call parity (`set`).  Remote stores carry flags only, so the
-// system-scope fence in front of a flag has nothing but local stores to wait
-// for.  The warps / CTAs of a rank count their arrivals in LOCAL counters, and
-// whoever completes a count writes the flag.  Epochs live on the device and
-// advance at the end of each call, so no per-call value comes from the host
-// and a captured CUDA graph of collectives can be replayed.
-// Two ranks can be at most one call apart: a rank that owns rows cannot finish
-// call n before every rank has produced for call n, and a buffer of parity
-// `set` is rewritten in call n+2 at the earliest, after every reader of call n
-// has been released by the flags of call n.
+// peer (P2P over NVLink/NVSwitch) and, when the heaps are bound to an NVSwitch
+// multicast object, reachable as ONE multicast address range as well.
+// One collective call runs as:
+//   produce : each rank writes its partial [T, H] into its OWN heap and tells
+//             the ranks that will read it with a flag (the call's number);
+//   reduce  : the owner of a row waits for every rank's flag, sums the row over
+//             the ranks in fp32 (+bias, +residual), optionally RMS-normalises,
+//             and publishes the finished row;
+//   gather  : every rank ends up with all finished rows in its own heap.
+// Row t is owned by rank t / rows_per_rank.  Three schemes share the buffers
+// and flags:
+//   owner-reduce + gather (peer loads only): owners pull the partial rows from
+//       the peers' heaps, store finished rows locally, and the peers pull them;
+//   one-shot (peer loads only): every rank pulls ALL partial rows and finishes
+//       all T rows itself -- one flag hand-off and one trip over the links;
+//   multicast (NVLS): the owner sums a row with ONE multimem.ld_reduce per
+//       16 bytes (the switch reads the eight heaps and adds in fp32) and
+//       publishes the finished row with multimem.st, which the switch copies
+//       into every rank's heap; flags are multimem stores too.  The reduce
+//       traffic leaves a GPU while the broadcast traffic enters it, so the two
+//       halves of the collective overlap on the full-duplex links.
+//
+// The `partial` buffers and all flags are double buffered by the parity of the
+// call number, which lives ON THE DEVICE (CC_CALLS, advanced by the last CTA of
+// every collective kernel): two ranks can be at most one call apart -- a rank
+// that owns rows cannot finish call n before every rank has produced for call
+// n -- so a buffer of one parity is rewritten in call n+2 at the earliest, after
+// every reader of call n has been released.  Because no per-call value comes
+// from the host, a captured CUDA graph with any number of collectives can be
+// replayed any number of times.  The `out` / `resid` regions the results are
+// left in are chosen by the host (`ReduceArgs::set`) so that the caller knows
+// their addresses when it enqueues the call; a finished row is written there
+// only after every rank has entered the call, i.e. after every kernel that the
+// ranks enqueued before it -- the readers of an earlier result -- has completed.
 // All waits are bounded; a wait that runs out sets the status word and the
 // kernel returns.
 #pragma once
@@ -41,14 +51,13 @@ constexpr int kMaxRanks = 8;
 enum CommCounter {
   CC_STATUS = 0,        // first error recorded by a kernel on this rank (0 = none)
   CC_EXIT_TICKET = 1,   // CTAs of the running collective kernel that have finished
-  CC_EPOCH0 = 2,        // epoch number of the last completed call, set 0 / 1
-  CC_EPOCH1 = 3,
-  CC_LOCAL_DONE = 4,    // local: reduce teams of the running call that have finished their rows
+  CC_CALLS = 2,         // collectives completed on this context: the running call has number CC_CALLS + 1
+  CC_LOCAL_DONE = 4,    // local: reduce teams / CTAs of the running call that have finished their rows
   CC_LOCAL_PUSH = 32,   // local: [kMaxRanks] arrivals of this rank's own pushes, per destination owner
-  CC_PUSH_FLAG0 = 64,   // [kMaxRanks] written by rank s: "my partial rows that you own are stored" (epoch), set 0
-  CC_PUSH_FLAG1 = 96,   //   ... set 1
-  CC_DONE_FLAG0 = 128,  // [kMaxRanks] written by rank s: "all rows I own are finished in my heap" (epoch), set 0
-  CC_DONE_FLAG1 = 160,  //   ... set 1
+  CC_PUSH_FLAG0 = 64,   // [kMaxRanks] written by rank s: "my partial rows (that you own) are stored" (call number), parity 0
+  CC_PUSH_FLAG1 = 96,   //   ... parity 1
+  CC_DONE_FLAG0 = 128,  // [kMaxRanks] written by rank s: "all rows I own are finished" (call number), parity 0
+  CC_DONE_FLAG1 = 160,  //   ... parity 1
   CC_COUNT = 192
 };
 
@@ -63,6 +72,7 @@ struct CommView {
   int rank;
   int world;
   char* heap[kMaxRanks];   // heap[rank] is local memory, the others are peer mappings
+  char* mc;                // multicast alias of all heaps (same offsets), or null
   size_t partial_off[2];   // byte offsets inside a heap
   size_t out_off[2];
   size_t resid_off[2];
@@ -71,6 +81,9 @@ struct CommView {
 
 __device__ __forceinline__ uint32_t* comm_counter(const CommView& c, int r, int which) {
   return reinterpret_cast<uint32_t*>(c.heap[r]) + which;
+}
+__device__ __forceinline__ uint32_t* comm_counter_mc(const CommView& c, int which) {
+  return reinterpret_cast<uint32_t*>(c.mc) + which;
 }
 
 // Memory-ordering helpers.  Flags of a multi-rank context are written by peers over NVLink and
@@ -90,6 +103,7 @@ __device__ __forceinline__ void st_release(uint32_t* p, uint32_t v, bool sys) {
   if (sys) asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
   else asm volatile("st.release.gpu.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
 }
+__device__ __forceinline__ void fence_sys() { asm volatile("fence.acq_rel.sys;" ::: "memory"); }
 
 // Arrival counter increment with release + acquire semantics at GPU scope: publishes what the caller
 // (and the threads it has synchronised with through a barrier) stored before, and makes what earlier
@@ -107,18 +121,52 @@ __device__ __forceinline__ uint32_t ld_acquire(const uint32_t* p, bool sys) {
   return v;
 }
 
-// Bounded spin until the flag word at p holds `epoch`.  Polls with relaxed loads; the load that ends
-// the wait is an acquire load that reads the value the signalling rank stored with st.release, so what
-// that rank wrote before its flag is visible to this thread (and, through a following barrier, to the
-// threads it releases).  A system-scope fence costs microseconds on this machine, an acquire load
-// does not, so no fence is used on the waiting side.  Returns false on timeout.
+// ---- NVSwitch multicast (multimem) accesses; `p` is an address inside the multicast alias -------
+// One store that the switch delivers to the same offset of every rank's heap.
+__device__ __forceinline__ void mc_st_release_u32(uint32_t* p, uint32_t v) {
+  asm volatile("multimem.st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ void mc_st16(void* p, const uint4& v) {
+  asm volatile("multimem.st.relaxed.sys.global.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(p), "r"(v.x), "r"(v.y), "r"(v.z),
+               "r"(v.w) : "memory");
+}
+// 16 bytes of the element-wise sum over all ranks' heaps: the addition happens in the switch, in fp32,
+// and the result is rounded to T once.
+template <typename T> __device__ __forceinline__ uint4 mc_ld_reduce16(const void* p);
+template <> __device__ __forceinline__ uint4 mc_ld_reduce16<__nv_bfloat16>(const void* p) {
+  uint4 v;
+  asm volatile("multimem.ld_reduce.relaxed.sys.global.add.acc::f32.v4.bf16x2 {%0, %1, %2, %3}, [%4];"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p) : "memory");
+  return v;
+}
+template <> __device__ __forceinline__ uint4 mc_ld_reduce16<__half>(const void* p) {
+  uint4 v;
+  asm volatile("multimem.ld_reduce.relaxed.sys.global.add.acc::f32.v4.f16x2 {%0, %1, %2, %3}, [%4];"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p) : "memory");
+  return v;
+}
+template <> __device__ __forceinline__ uint4 mc_ld_reduce16<float>(const void* p) {
+  uint4 v;
+  asm volatile("multimem.ld_reduce.relaxed.sys.global.add.v4.f32 {%0, %1, %2, %3}, [%4];"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p) : "memory");
+  return v;
+}
+
+// Bounded spin until the flag word at p has reached call number `epoch` (a flag word only ever grows; a
+// waiter can see a later number only if the writer was allowed to run ahead, in which case the data it
+// waits for is there as well).  Polls with relaxed loads; the load that ends the wait is an acquire load
+// that reads a value the signalling rank stored with release semantics, so what that rank wrote before
+// its flag is visible to this thread (and, through a following barrier, to the threads it releases).  A
+// system-scope fence costs microseconds on this machine, an acquire load does not, so no fence is used
+// on the waiting side.  Returns false on timeout.
+__device__ __forceinline__ bool flag_reached(uint32_t v, uint32_t epoch) { return (int32_t)(v - epoch) >= 0; }
 __device__ __forceinline__ bool wait_flag(const uint32_t* p, uint32_t epoch, long long limit_cycles, bool sys) {
   const long long t0 = clock64();
-  while (ld_relaxed(p, sys) != epoch) {
+  while (!flag_reached(ld_relaxed(p, sys), epoch)) {
     __nanosleep(20);
     if (clock64() - t0 > limit_cycles) return false;
   }
-  return ld_acquire(p, sys) == epoch;
+  return flag_reached(ld_acquire(p, sys), epoch);
 }
 
 __device__ __forceinline__ void record_status(const CommView& c, int code) {
@@ -128,12 +176,14 @@ __device__ __forceinline__ void record_status(const CommView& c, int code) {
 struct ReduceArgs {
   int T, H;               // rows of the whole batch, row length
   int rows_per_rank;      // ownership granule: owner(t) = t / rows_per_rank
-  int set;                // call parity
+  int set;                // which of the two out / resid regions receives the results (chosen by the host)
   int one_shot;           // 1: every rank loads ALL partial rows and finishes all T rows itself (one flag wait and one
                           // trip over the links instead of two; pays off while (world-1)*T*H bytes is small); 0: rows
                           // are reduced by their owners and gathered afterwards
+  int use_mc;             // 1 (only with one_shot = 0): owners reduce and publish through the NVSwitch multicast alias
   uint32_t push_expected[kMaxRanks];  // arrivals this rank's own kernel reports per destination owner
-                                      // (epilogue warp-tiles of the GEMM, or CTAs of the all-reduce)
+                                      // (epilogue warp-tiles of the GEMM, or CTAs of the all-reduce); one-shot and
+                                      // multicast calls count all arrivals in [0]
   const void* bias;       // [H] or null, added after the sum (reference: layers.py:448-453)
   const void* residual;   // [T, H] local tensor or null: z = sum + residual
   const void* norm_w;     // [H] or null: also produce rms_norm(z) * norm_w
@@ -142,9 +192,12 @@ struct ReduceArgs {
   void* out_copy;         // optional local [T, H] tensor that receives the primary result
   void* resid_copy;       // optional local [T, H] tensor that receives z when norm_w != null
   long long wait_cycles;
-  unsigned long long* trace;  // optional [gridDim.x][8] nanosecond time stamps of the phases (profiling aid), or null
+#ifdef SB200_TRACE
+  unsigned long long* trace;  // [gridDim.x][8] nanosecond time stamps of the phases (profiling builds only)
+#endif
 };
 
+#ifdef SB200_TRACE
 __device__ __forceinline__ unsigned long long global_ns() {
   unsigned long long t;
   asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
@@ -154,10 +207,20 @@ __device__ __forceinline__ unsigned long long global_ns() {
 __device__ __forceinline__ void trace_mark(const ReduceArgs& a, int slot) {
   if (a.trace && threadIdx.x == 0) a.trace[(size_t)blockIdx.x * 8 + slot] = global_ns();
 }
+#else
+__device__ __forceinline__ void trace_mark(const ReduceArgs&, int) {}
+#endif
 
-// Epoch number of the running call on this set.
-__device__ __forceinline__ uint32_t call_epoch(const CommView& c, const ReduceArgs& a) {
-  return *(volatile uint32_t*)comm_counter(c, c.rank, CC_EPOCH0 + a.set) + 1u;
+// Number of the running call on this context (1, 2, ...): every CTA reads it before the call's last CTA
+// advances it.  Its parity selects the `partial` buffer and the flag words of the call.
+__device__ __forceinline__ uint32_t call_number(const CommView& c) {
+  return *(volatile uint32_t*)comm_counter(c, c.rank, CC_CALLS) + 1u;
+}
+__device__ __forceinline__ int push_flag_index(uint32_t n, int src) { return ((n & 1u) ? CC_PUSH_FLAG1 : CC_PUSH_FLAG0) + src; }
+__device__ __forceinline__ int done_flag_index(uint32_t n, int src) { return ((n & 1u) ? CC_DONE_FLAG1 : CC_DONE_FLAG0) + src; }
+// This rank's partial [T, H] of call n.
+__device__ __forceinline__ char* partial_of(const CommView& c, int r, uint32_t n) {
+  return c.heap[r] + c.partial_off[n & 1u];
 }
 
 // Called by ONE thread after the stores it and its group made to this rank's partial region and a
@@ -165,24 +228,32 @@ __device__ __forceinline__ uint32_t call_epoch(const CommView& c, const ReduceAr
 // increment (which covers the group's stores); the arrival that completes this rank's share of
 // `owner`'s rows tells the owner with a single remote release store.
 __device__ __forceinline__ void signal_push(const CommView& c, const ReduceArgs& a, int owner) {
-  const uint32_t n = arrive_acq_rel(comm_counter(c, c.rank, CC_LOCAL_PUSH + owner)) + 1u;
-  if (n == a.push_expected[owner])
-    st_release(comm_counter(c, owner, (a.set ? CC_PUSH_FLAG1 : CC_PUSH_FLAG0) + c.rank), call_epoch(c, a), c.world > 1);
+  const uint32_t cnt = arrive_acq_rel(comm_counter(c, c.rank, CC_LOCAL_PUSH + owner)) + 1u;
+  if (cnt == a.push_expected[owner]) {
+    const uint32_t n = call_number(c);
+    st_release(comm_counter(c, owner, push_flag_index(n, c.rank)), n, c.world > 1);
+  }
 }
-// One-shot calls: every rank needs all rows, so the arrivals are counted in one counter
-// (push_expected[0] = all arrivals of this rank's kernel) and the last one flags every rank.
-// Called by ALL lanes of a converged warp after its stores (and, for a CTA-wide share, a
-// __syncthreads): lane 0 counts the arrival; when it completes the count, lanes 0..world-1 store one
+// One-shot and multicast calls: every rank reads all of this rank's rows (or the switch does), so the
+// arrivals are counted in one counter (push_expected[0] = all arrivals of this rank's kernel) and the
+// last one flags every rank.  Called by ALL lanes of a converged warp after its stores (and, for a
+// CTA-wide share, a __syncthreads): lane 0 counts the arrival; when it completes the count, one
+// multicast store reaches every rank's flag word, or, without multicast, lanes 0..world-1 store one
 // rank's flag each, so the fan-out costs one release, not world of them in a row.
 __device__ __forceinline__ void signal_push_all(const CommView& c, const ReduceArgs& a) {
   const int lane = threadIdx.x & 31;
   __syncwarp();
-  uint32_t n = 0;
-  if (lane == 0) n = arrive_acq_rel(comm_counter(c, c.rank, CC_LOCAL_PUSH)) + 1u;
-  n = __shfl_sync(0xffffffffu, n, 0);  // (also orders lane 0's acquire before the other lanes' stores)
-  if (n == a.push_expected[0] && lane < c.world)
-    st_release(comm_counter(c, lane, (a.set ? CC_PUSH_FLAG1 : CC_PUSH_FLAG0) + c.rank), call_epoch(c, a),
-               lane != c.rank);
+  uint32_t cnt = 0;
+  if (lane == 0) cnt = arrive_acq_rel(comm_counter(c, c.rank, CC_LOCAL_PUSH)) + 1u;
+  cnt = __shfl_sync(0xffffffffu, cnt, 0);
+  __syncwarp();  // a memory-ordering barrier of the warp: lane 0's acquire comes before the other lanes' release stores
+  if (cnt != a.push_expected[0]) return;
+  const uint32_t n = call_number(c);
+  if (a.use_mc) {
+    if (lane == 0) mc_st_release_u32(comm_counter_mc(c, push_flag_index(n, c.rank)), n);
+  } else if (lane < c.world) {
+    st_release(comm_counter(c, lane, push_flag_index(n, c.rank)), n, lane != c.rank);
+  }
 }
 
 // Primary result = rms_norm(z)*w when norm_w is set, else z, kept in the `out` region; z is
@@ -212,9 +283,27 @@ __device__ __forceinline__ void team_barrier(int id, int threads) {
   asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(threads) : "memory");
 }
 
+// z = round(round(sum + bias) + residual) for one 16-byte vector; returns the vector's sum of squares.
+template <typename T>
+__device__ __forceinline__ float finish_vec(const float* acc, const Vec16<T>* bias, const Vec16<T>* resid, Vec16<T>* z) {
+  constexpr int N = Vec16<T>::N;
+  float ss = 0.f;
+#pragma unroll
+  for (int j = 0; j < N; ++j) {
+    float f = acc[j];
+    if (bias) f = rt<T>(rt<T>(f) + DT<T>::to_f(bias->v[j]));
+    if (resid) f = rt<T>(DT<T>::to_f(resid->v[j]) + rt<T>(f));
+    z->v[j] = DT<T>::from_f(f);
+    const float zf = DT<T>::to_f(z->v[j]);
+    ss += zf * zf;
+  }
+  return ss;
+}
+
 template <typename T, int VPL>
-__device__ __forceinline__ void reduce_rows(const CommView& c, const ReduceArgs& a, int gteam, int num_teams, int tw,
-                                            int team, int wt, int lane, int warp, int row0, int nrows, float* s_ss) {
+__device__ __forceinline__ void reduce_rows(const CommView& c, const ReduceArgs& a, uint32_t n, int gteam, int num_teams,
+                                            int tw, int team, int wt, int lane, int warp, int row0, int nrows,
+                                            float* s_ss) {
   constexpr int N = Vec16<T>::N;
   constexpr int SB = VPL <= 2 ? 8 : 8 / VPL;  // source ranks whose loads are issued together (8-16 vectors in flight per lane)
   const int nvec = a.H / N;
@@ -231,7 +320,7 @@ __device__ __forceinline__ void reduce_rows(const CommView& c, const ReduceArgs&
 #pragma unroll
     for (int i = 0; i < SB; ++i)
       if (s0 + i < c.world) {
-        const T* p = (const T*)(c.heap[s0 + i] + c.partial_off[a.set]) + row_off;
+        const T* p = (const T*)partial_of(c, s0 + i, n) + row_off;
 #pragma unroll
         for (int b = 0; b < VPL; ++b) {
           const int v = vbase + vstep * b;
@@ -276,15 +365,7 @@ __device__ __forceinline__ void reduce_rows(const CommView& c, const ReduceArgs&
       if (v >= nvec) continue;
       Vec16<T> bv;
       if (bias) bv = ld16(bias + (size_t)v * N);
-#pragma unroll
-      for (int j = 0; j < N; ++j) {
-        float f = acc[b][j];
-        if (bias) f = rt<T>(rt<T>(f) + DT<T>::to_f(bv.v[j]));
-        if (resid) f = rt<T>(DT<T>::to_f(rv[b].v[j]) + rt<T>(f));
-        z[b].v[j] = DT<T>::from_f(f);
-        const float zf = DT<T>::to_f(z[b].v[j]);
-        ss += zf * zf;
-      }
+      ss += finish_vec<T>(acc[b], bias ? &bv : nullptr, resid ? &rv[b] : nullptr, &z[b]);
       st16(zrow + (size_t)v * N, z[b]);
       if (zcopy) st16(zcopy + row_off + (size_t)v * N, z[b]);
     }
@@ -339,7 +420,7 @@ __device__ void reduce_phase(const CommView& c, const ReduceArgs& a, int cta, in
   const int teams_per_cta = kReduceWarps / tw;
   const int team = warp / tw, wt = warp - team * tw;
   const int gteam = cta * teams_per_cta + team, num_teams = num_ctas * teams_per_cta;
-  const uint32_t epoch = call_epoch(c, a);
+  const uint32_t n = call_number(c);
   const int teams_with_rows = min(num_teams, nrows);
   if (cta * teams_per_cta >= nrows) return;  // no row for any team of this CTA: nothing to wait for either
   {
@@ -347,8 +428,7 @@ __device__ void reduce_phase(const CommView& c, const ReduceArgs& a, int cta, in
     trace_mark(a, 2);
     if (warp == 0) {
       bool ok = true;
-      if (lane < c.world)
-        ok = wait_flag(comm_counter(c, c.rank, (a.set ? CC_PUSH_FLAG1 : CC_PUSH_FLAG0) + lane), epoch, a.wait_cycles, sys);
+      if (lane < c.world) ok = wait_flag(comm_counter(c, c.rank, push_flag_index(n, lane)), n, a.wait_cycles, sys);
       ok = __all_sync(0xffffffffu, ok);
       if (lane == 0 && !ok) record_status(c, CS_TIMEOUT_PUSH);
     }
@@ -358,21 +438,22 @@ __device__ void reduce_phase(const CommView& c, const ReduceArgs& a, int cta, in
     //  results are not to be used -- so that every rank keeps counting the same arrivals)
   }
   if (gteam >= nrows) return;
-  if (vpl <= 1) reduce_rows<T, 1>(c, a, gteam, num_teams, tw, team, wt, lane, warp, row0, nrows, s_ss);
-  else if (vpl <= 2) reduce_rows<T, 2>(c, a, gteam, num_teams, tw, team, wt, lane, warp, row0, nrows, s_ss);
-  else if (vpl <= 4 || MAXVPL <= 4) reduce_rows<T, 4>(c, a, gteam, num_teams, tw, team, wt, lane, warp, row0, nrows, s_ss);
-  else reduce_rows<T, (MAXVPL > 4 ? 8 : 4)>(c, a, gteam, num_teams, tw, team, wt, lane, warp, row0, nrows, s_ss);
+  if (vpl <= 1) reduce_rows<T, 1>(c, a, n, gteam, num_teams, tw, team, wt, lane, warp, row0, nrows, s_ss);
+  else if (vpl <= 2) reduce_rows<T, 2>(c, a, n, gteam, num_teams, tw, team, wt, lane, warp, row0, nrows, s_ss);
+  else if (vpl <= 4 || MAXVPL <= 4) reduce_rows<T, 4>(c, a, n, gteam, num_teams, tw, team, wt, lane, warp, row0, nrows, s_ss);
+  else reduce_rows<T, (MAXVPL > 4 ? 8 : 4)>(c, a, n, gteam, num_teams, tw, team, wt, lane, warp, row0, nrows, s_ss);
   if (a.one_shot) return;  // every rank has finished all rows itself: nothing to tell, nothing to gather
   // publish: the team is counted locally (a release increment after the team's barrier covers the
   // stores of all its warps), and the team that completes the count tells every peer, with one remote
   // release store each, that this rank's rows are done
   if (tw > 1) team_barrier(1 + team, 32 * tw); else __syncwarp();
   if (wt == 0) {
-    uint32_t n = 0;
-    if (lane == 0) n = arrive_acq_rel(comm_counter(c, c.rank, CC_LOCAL_DONE)) + 1u;
-    n = __shfl_sync(0xffffffffu, n, 0);
-    if (n == (uint32_t)teams_with_rows && lane < c.world && lane != c.rank)
-      st_release(comm_counter(c, lane, (a.set ? CC_DONE_FLAG1 : CC_DONE_FLAG0) + c.rank), epoch, sys);
+    uint32_t cnt = 0;
+    if (lane == 0) cnt = arrive_acq_rel(comm_counter(c, c.rank, CC_LOCAL_DONE)) + 1u;
+    cnt = __shfl_sync(0xffffffffu, cnt, 0);
+    __syncwarp();  // lane 0's acquire is ordered before the other lanes' release stores
+    if (cnt == (uint32_t)teams_with_rows && lane < c.world && lane != c.rank)
+      st_release(comm_counter(c, lane, done_flag_index(n, c.rank)), n, sys);
   }
 }
 
@@ -387,7 +468,7 @@ __device__ void gather_phase(const CommView& c, const ReduceArgs& a, int cta, in
   const int others = c.world - 1;
   if (others == 0 || a.one_shot) return;
   const int nvec = a.H / N;
-  const uint32_t epoch = call_epoch(c, a);
+  const uint32_t n = call_number(c);
   const int groups = min(others, num_ctas);
   const int group = cta % groups, rank_in_group = cta / groups;
   const int ctas_in_group = (num_ctas - group + groups - 1) / groups;
@@ -395,11 +476,10 @@ __device__ void gather_phase(const CommView& c, const ReduceArgs& a, int cta, in
   for (int j = group; j < others; j += groups) {
     const int o = (c.rank + 1 + j) % c.world;
     const int r0 = o * a.rows_per_rank;
-    const int n = min(a.rows_per_rank, a.T - r0);
-    if (n <= 0) continue;
+    const int nr = min(a.rows_per_rank, a.T - r0);
+    if (nr <= 0) continue;
     if (threadIdx.x == 0) {
-      const bool ok = wait_flag(comm_counter(c, c.rank, (a.set ? CC_DONE_FLAG1 : CC_DONE_FLAG0) + o), epoch,
-                                a.wait_cycles, true);
+      const bool ok = wait_flag(comm_counter(c, c.rank, done_flag_index(n, o)), n, a.wait_cycles, true);
       if (!ok) record_status(c, CS_TIMEOUT_DONE);
       s_ok = ok ? 1 : 0;
     }
@@ -414,7 +494,7 @@ __device__ void gather_phase(const CommView& c, const ReduceArgs& a, int cta, in
     T* dst_res = (T*)(c.heap[c.rank] + c.resid_off[a.set]) + base;
     T* cp_out = a.out_copy ? (T*)a.out_copy + base : nullptr;
     T* cp_res = (pull_resid && a.resid_copy) ? (T*)a.resid_copy + base : nullptr;
-    const size_t total = (size_t)n * nvec;
+    const size_t total = (size_t)nr * nvec;
     const size_t stride = (size_t)ctas_in_group * blockDim.x;
     for (size_t i0 = (size_t)rank_in_group * blockDim.x + threadIdx.x; i0 < total; i0 += stride * U) {
       Vec16<T> y[U], z[U];
@@ -442,10 +522,186 @@ __device__ void gather_phase(const CommView& c, const ReduceArgs& a, int cta, in
   }
 }
 
+// ------------------------------------------------------------- multicast (NVLS) scheme
+// Rows of one owner, one CTA per row at a time (all kReduceWarps warps share the row).  The
+// multimem.ld_reduce of a CTA's NEXT row is in flight while the current one is normalised.
+template <typename T, int VPL>
+__device__ __forceinline__ void mc_reduce_rows(const CommView& c, const ReduceArgs& a, uint32_t n, int cta, int num_ctas,
+                                               int row0, int nrows, float* s_ss) {
+  constexpr int N = Vec16<T>::N;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int nvec = a.H / N;
+  const T* bias = (const T*)a.bias;
+  const T* resid = (const T*)a.residual;
+  const T* nw = (const T*)a.norm_w;
+  const int vbase = warp * 32 + lane, vstep = 32 * kReduceWarps;
+  const T* mc_partial = (const T*)(c.mc + c.partial_off[n & 1u]);
+  T* mc_out = (T*)(c.mc + c.out_off[a.set]);
+  T* mc_res = (T*)(c.mc + c.resid_off[a.set]);
+  T* my_res = (T*)(c.heap[c.rank] + c.resid_off[a.set]);
+  Vec16<T> x[VPL];
+  auto load_row = [&](size_t row_off) {
+#pragma unroll
+    for (int b = 0; b < VPL; ++b) {
+      const int v = vbase + vstep * b;
+      if (v < nvec) x[b].raw = mc_ld_reduce16<T>(mc_partial + row_off + (size_t)v * N);
+    }
+  };
+  if (cta < nrows) load_row((size_t)(row0 + cta) * a.H);
+  int parity = 0;
+  for (int lr = cta; lr < nrows; lr += num_ctas, parity ^= 1) {
+    const size_t row_off = (size_t)(row0 + lr) * a.H;
+    Vec16<T> z[VPL];
+    float ss = 0.f;
+#pragma unroll
+    for (int b = 0; b < VPL; ++b) {
+      const int v = vbase + vstep * b;
+      if (v >= nvec) continue;
+      Vec16<T> rv, bv;
+      if (resid) rv = ld16(resid + row_off + (size_t)v * N);
+      if (bias) bv = ld16(bias + (size_t)v * N);
+      float acc[N];
+#pragma unroll
+      for (int j = 0; j < N; ++j) acc[j] = DT<T>::to_f(x[b].v[j]);
+      ss += finish_vec<T>(acc, bias ? &bv : nullptr, resid ? &rv : nullptr, &z[b]);
+    }
+    if (lr + num_ctas < nrows) load_row((size_t)(row0 + lr + num_ctas) * a.H);
+#pragma unroll
+    for (int b = 0; b < VPL; ++b) {
+      const int v = vbase + vstep * b;
+      if (v >= nvec) continue;
+      const size_t e = row_off + (size_t)v * N;
+      if (!nw) {
+        mc_st16(mc_out + e, z[b].raw);                     // z is the primary result: every rank gets it
+      } else if (a.write_resid_all) {
+        mc_st16(mc_res + e, z[b].raw);
+      } else {
+        st16(my_res + e, z[b]);                            // the new residual stays with the owner of the row
+        if (a.resid_copy) st16((T*)a.resid_copy + e, z[b]);
+      }
+    }
+    if (nw) {
+      Vec16<T> w[VPL];
+#pragma unroll
+      for (int b = 0; b < VPL; ++b) {
+        const int v = vbase + vstep * b;
+        if (v < nvec) w[b] = ld16(nw + (size_t)v * N);
+      }
+      ss = warp_sum(ss);
+      if (lane == 0) s_ss[parity * kReduceWarps + warp] = ss;  // two sets of slots: no second barrier per row
+      team_barrier(14, 32 * kReduceWarps);
+      ss = 0.f;
+#pragma unroll
+      for (int i = 0; i < kReduceWarps; ++i) ss += s_ss[parity * kReduceWarps + i];
+      const float inv = rsqrtf(ss / (float)a.H + a.eps);
+#pragma unroll
+      for (int b = 0; b < VPL; ++b) {
+        const int v = vbase + vstep * b;
+        if (v >= nvec) continue;
+        Vec16<T> y;
+#pragma unroll
+        for (int j = 0; j < N; ++j)
+          y.v[j] = DT<T>::from_f(rt<T>(DT<T>::to_f(z[b].v[j]) * inv) * DT<T>::to_f(w[b].v[j]));
+        mc_st16(mc_out + row_off + (size_t)v * N, y.raw);
+      }
+    }
+  }
+}
+
+// Multicast scheme, last step: every owner's rows have arrived in this rank's heap once its done flag has.
+// Then the caller's own tensors are filled, if it asked for copies (the heap regions are the primary
+// location).  Called by all threads of every CTA.
+template <typename T>
+__device__ void mc_wait_all_done(const CommView& c, const ReduceArgs& a, uint32_t n, int cta, int num_ctas) {
+  constexpr int N = Vec16<T>::N;
+  __shared__ int s_ok;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int nvec = a.H / N;
+  if (warp == 0) {
+    bool ok = true;
+    if (lane < c.world && lane * a.rows_per_rank < a.T)
+      ok = wait_flag(comm_counter(c, c.rank, done_flag_index(n, lane)), n, a.wait_cycles, true);
+    ok = __all_sync(0xffffffffu, ok);
+    if (lane == 0) {
+      if (!ok) record_status(c, CS_TIMEOUT_DONE);
+      s_ok = ok ? 1 : 0;
+    }
+  }
+  __syncthreads();
+  if (!s_ok) return;
+  const bool copy_res = a.resid_copy && a.norm_w && a.write_resid_all;
+  if (a.out_copy || copy_res) {
+    const T* src_out = (const T*)(c.heap[c.rank] + c.out_off[a.set]);
+    const T* src_res = (const T*)(c.heap[c.rank] + c.resid_off[a.set]);
+    const size_t total = (size_t)a.T * nvec;
+    const size_t stride = (size_t)num_ctas * blockDim.x;
+    for (size_t i = (size_t)cta * blockDim.x + threadIdx.x; i < total; i += stride) {
+      if (a.out_copy) st16((T*)a.out_copy + i * N, ldcg16(src_out + i * N));
+      if (copy_res) st16((T*)a.resid_copy + i * N, ldcg16(src_res + i * N));
+    }
+  }
+}
+
+// Reduce + publish the rows this rank owns through the multicast alias, then wait until every owner
+// has published.  Called by all threads of every CTA (warps beyond kReduceWarps only take part in
+// the final barrier and copy).
+template <typename T, int MAXVPL>
+__device__ void mc_reduce_gather_phase(const CommView& c, const ReduceArgs& a, int cta, int num_ctas) {
+  constexpr int N = Vec16<T>::N;
+  __shared__ float s_ss[2 * kReduceWarps];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const uint32_t n = call_number(c);
+  const int row0 = c.rank * a.rows_per_rank;
+  const int nrows = max(0, min(a.rows_per_rank, a.T - row0));
+  const int nvec = a.H / N;
+  const int ctas_with_rows = min(num_ctas, nrows);
+  if (warp < kReduceWarps && cta < nrows) {
+    trace_mark(a, 2);
+    if (warp == 0) {
+      bool ok = true;
+      if (lane < c.world) ok = wait_flag(comm_counter(c, c.rank, push_flag_index(n, lane)), n, a.wait_cycles, true);
+      ok = __all_sync(0xffffffffu, ok);
+      if (lane == 0 && !ok) record_status(c, CS_TIMEOUT_PUSH);
+    }
+    team_barrier(15, 32 * kReduceWarps);
+    trace_mark(a, 3);
+    const int vpl = (nvec + 32 * kReduceWarps - 1) / (32 * kReduceWarps);
+    if (vpl <= 1) mc_reduce_rows<T, 1>(c, a, n, cta, num_ctas, row0, nrows, s_ss);
+    else if (vpl <= 2) mc_reduce_rows<T, 2>(c, a, n, cta, num_ctas, row0, nrows, s_ss);
+    else if (vpl <= 4 || MAXVPL <= 4) mc_reduce_rows<T, 4>(c, a, n, cta, num_ctas, row0, nrows, s_ss);
+    else mc_reduce_rows<T, (MAXVPL > 4 ? 8 : 4)>(c, a, n, cta, num_ctas, row0, nrows, s_ss);
+    // This CTA's multicast stores have to be performed at every rank before the done flag: the CTA's
+    // warps meet, one thread fences at system scope (which covers, through the barrier, the stores of
+    // the whole CTA) and counts the CTA; the CTA that completes the count publishes the flag with one
+    // multicast store.
+    team_barrier(15, 32 * kReduceWarps);
+    if (threadIdx.x == 0) {
+      fence_sys();
+      if (arrive_acq_rel(comm_counter(c, c.rank, CC_LOCAL_DONE)) + 1u == (uint32_t)ctas_with_rows)
+        mc_st_release_u32(comm_counter_mc(c, done_flag_index(n, c.rank)), n);
+    }
+    trace_mark(a, 4);
+  }
+  mc_wait_all_done<T>(c, a, n, cta, num_ctas);
+}
+
+// The phases after the partial rows have been produced, for whichever scheme the call uses.
+template <typename T, int MAXVPL>
+__device__ __forceinline__ void collective_tail(const CommView& c, const ReduceArgs& a, int cta, int num_ctas) {
+  if (a.use_mc) {
+    mc_reduce_gather_phase<T, MAXVPL>(c, a, cta, num_ctas);
+  } else {
+    reduce_phase<T, MAXVPL>(c, a, cta, num_ctas);
+    trace_mark(a, 4);
+    gather_phase<T>(c, a, cta, num_ctas);
+  }
+  trace_mark(a, 5);
+}
+
 // Last step of every collective kernel, called by all threads of every CTA after their phases:
-// the last CTA to get here closes the call -- it advances this set's epoch and clears the local
-// arrival counters.  Every CTA has read the epoch by then (it reads it before it can finish), the
-// local counters are only touched by this rank's own kernels, and the next collective on this
+// the last CTA to get here closes the call -- it advances the call counter and clears the local
+// arrival counters.  Every CTA has read the call number by then (it reads it before it can finish),
+// the local counters are only touched by this rank's own kernels, and the next collective on this
 // context is a later kernel on the same stream.
 __device__ __forceinline__ void advance_targets(const CommView& c, const ReduceArgs& a) {
   __syncthreads();
@@ -453,7 +709,7 @@ __device__ __forceinline__ void advance_targets(const CommView& c, const ReduceA
     __threadfence();
     uint32_t* ticket = comm_counter(c, c.rank, CC_EXIT_TICKET);
     if (atomicAdd(ticket, 1u) == gridDim.x - 1) {
-      *(volatile uint32_t*)comm_counter(c, c.rank, CC_EPOCH0 + a.set) += 1u;
+      *(volatile uint32_t*)comm_counter(c, c.rank, CC_CALLS) += 1u;
       for (int i = 0; i < kMaxRanks; ++i) *(volatile uint32_t*)comm_counter(c, c.rank, CC_LOCAL_PUSH + i) = 0u;
       *(volatile uint32_t*)comm_counter(c, c.rank, CC_LOCAL_DONE) = 0u;
       *(volatile uint32_t*)ticket = 0;

@@ -396,7 +396,7 @@ __device__ __forceinline__ RowCtx<T> make_row_ctx(const GemmArgs& g, const CommV
     if (rc.row_ok) rc.scale = g.topk_w[slot];
   } else if constexpr (EPI == EPI_PUSH) {
     // the partial [T, N] of this rank stays in its own heap; the owners of the rows come and read it
-    rc.out_row = reinterpret_cast<T*>(comm.heap[comm.rank] + comm.partial_off[red.set]) + (size_t)gm * (size_t)g.N;
+    rc.out_row = reinterpret_cast<T*>(partial_of(comm, comm.rank, call_number(comm))) + (size_t)gm * (size_t)g.N;
     rc.vec_ok = (g.N & 7) == 0;
   } else {
     rc.out_row = reinterpret_cast<T*>(g.out) + (size_t)gm * g.ldo;
@@ -412,7 +412,7 @@ __device__ __forceinline__ RowCtx<T> make_row_ctx(const GemmArgs& g, const CommV
 __device__ __forceinline__ void push_rows_done(const CommView& comm, const ReduceArgs& red, const GemmArgs& g, int r_lo) {
   const int r_hi = min(g.M, r_lo + 32) - 1;
   if (r_hi < r_lo) return;  // warp-uniform
-  if (red.one_shot) { signal_push_all(comm, red); return; }
+  if (red.one_shot || red.use_mc) { signal_push_all(comm, red); return; }
   __syncwarp();
   if ((threadIdx.x & 31) == 0)
     for (int o = r_lo / red.rows_per_rank; o <= r_hi / red.rows_per_rank; ++o) signal_push(comm, red, o);
@@ -720,10 +720,7 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
 
   if constexpr (EPI == EPI_PUSH) {
     trace_mark(red, 1);
-    reduce_phase<T, kMaxVecPerLaneGemm>(comm, red, blockIdx.x, gridDim.x);
-    trace_mark(red, 4);
-    gather_phase<T>(comm, red, blockIdx.x, gridDim.x);
-    trace_mark(red, 5);
+    collective_tail<T, kMaxVecPerLaneGemm>(comm, red, blockIdx.x, gridDim.x);
     advance_targets(comm, red);
     trace_mark(red, 6);
   }

@@ -49,6 +49,29 @@ def check_status(device: torch.device) -> None:
         raise RuntimeError(f"sm_100a GEMM pipeline wait timed out (device status code {v})")
 
 
+_status_host: dict = {}
+
+
+def enqueue_status_read(device: torch.device) -> None:
+    """Asynchronous (graph-capturable) copy of the device's GEMM status word into pinned host memory."""
+    key = (device.type, device.index if device.index is not None else torch.cuda.current_device())
+    h = _status_host.get(key)
+    if h is None:
+        h = _status_host[key] = torch.zeros(1, dtype=torch.int32).pin_memory()
+    h.copy_(status_word(device), non_blocking=True)
+
+
+def raise_if_flagged(device: torch.device) -> None:
+    """No synchronisation: raises if the status word last read by ``enqueue_status_read`` was non-zero."""
+    key = (device.type, device.index if device.index is not None else torch.cuda.current_device())
+    h = _status_host.get(key)
+    if h is not None and int(h[0]) != 0:
+        code = int(h[0])
+        h.zero_()
+        status_word(device).zero_()
+        raise RuntimeError(f"sm_100a GEMM pipeline wait timed out in an earlier step (device status code {code})")
+
+
 def _ws(x: torch.Tensor):
     """(pointer, bytes) of the split-K workspace for x's device; fp32 runs the FFMA kernel and needs none."""
     if x.dtype == torch.float32:

@@ -51,9 +51,11 @@ def moe_align_block_size(topk_ids: torch.Tensor, block_size: int, num_experts: i
     return sorted_ids, expert_ids, num_tokens_post_pad
 
 
-def _expert_slots(hidden_states, w1, w2, topk_weights, topk_ids):
+def _expert_slots(hidden_states, w1, w2, topk_weights, topk_ids, ids_in_range: bool = False):
     """Common part of fused_experts: returns out3 [T*k, H] (per-slot expert outputs, already scaled by
-    the routed weights) for bf16/fp16 inputs."""
+    the routed weights) for bf16/fp16 inputs.  ``ids_in_range``: the caller guarantees 0 <= id < E for
+    every slot (ids produced by ``fused_topk``); otherwise the slots are zeroed first, because a slot whose
+    id is out of range is skipped by the alignment and the GEMMs and would keep uninitialised memory."""
     T, H = hidden_states.shape
     E, two_d, K = w1.shape
     k = topk_ids.shape[1]
@@ -75,7 +77,7 @@ def _expert_slots(hidden_states, w1, w2, topk_weights, topk_ids):
     act = torch.empty(rows_cap, two_d // 2, dtype=dt, device=dev)
     N.check(lib.sb200_moe_gemm1(N.ptr(act), N.ptr(xs), N.ptr(w1), N.ptr(expert_ids), N.ptr(num_post_pad), rows_cap, E,
                                 two_d, K, N.dtype_id(hidden_states), st, 0, N.stream_ptr()), "moe_gemm1")
-    out3 = torch.empty(T * k, w2.shape[1], dtype=dt, device=dev)
+    out3 = (torch.empty if ids_in_range else torch.zeros)(T * k, w2.shape[1], dtype=dt, device=dev)
     N.check(lib.sb200_moe_gemm2(N.ptr(out3), N.ptr(act), N.ptr(w2), N.ptr(expert_ids), N.ptr(num_post_pad),
                                 N.ptr(sorted_ids), N.ptr(topk_weights), rows_cap, T * k, E, w2.shape[1], w2.shape[2],
                                 N.dtype_id(hidden_states), st, 0, N.stream_ptr()), "moe_gemm2")
@@ -170,7 +172,7 @@ class FusedMoE(torch.nn.Module):
         if T == 0:
             return hidden_states
         topk_weights, topk_ids = fused_topk(hidden_states, router_logits, self.top_k, self.renormalize)
-        out3 = _expert_slots(hidden_states, self.w13_weight, self.w2_weight, topk_weights, topk_ids)
+        out3 = _expert_slots(hidden_states, self.w13_weight, self.w2_weight, topk_weights, topk_ids, ids_in_range=True)
         comm = ps.get_tensor_model_parallel_comm()
         op = ctypes.c_void_p()
         # sum over the k slots fused into the push of the all-reduce; result written over the input

@@ -15,6 +15,9 @@ from typing import Optional
 
 import torch
 
+from . import dense_ops
+from . import parallel_state as ps
+
 
 class LayerGraph:
     """Graph of ``layer.forward`` for ``num_tokens`` tokens.
@@ -60,13 +63,25 @@ class LayerGraph:
                 self.output = layer(self.positions, self.hidden_states, layer_cache_idx, attention_backend_wrapper)
                 if self.host_io:
                     self.host_output.copy_(self.output, non_blocking=True)
+                # the device status words (bounded waits that ran out) travel to pinned host memory with every
+                # replay; the NEXT call looks at them before it launches, without a synchronisation
+                self._comm = ps._TP_COMM
+                if self._comm is not None:
+                    self._comm.enqueue_status_read()
+                dense_ops.enqueue_status_read(self.device)
         torch.cuda.current_stream(self.device).wait_stream(self.stream)
+
+    def _raise_if_an_earlier_step_failed(self) -> None:
+        if self._comm is not None:
+            self._comm.raise_if_flagged()
+        dense_ops.raise_if_flagged(self.device)
 
     def replay_host_io(self) -> torch.Tensor:
         """One launch: host inputs -> device, the layer, output -> ``host_output`` (valid after the
         current stream has been synchronised)."""
         if not self.host_io:
             raise RuntimeError("LayerGraph: built without host_io=True")
+        self._raise_if_an_earlier_step_failed()
         self.graph.replay()
         return self.host_output
 
@@ -77,6 +92,7 @@ class LayerGraph:
         if hidden_states.shape != self.hidden_states.shape or positions.shape != self.positions.shape:
             raise RuntimeError(f"LayerGraph: captured for {tuple(self.hidden_states.shape)} hidden states, "
                                f"got {tuple(hidden_states.shape)}")
+        self._raise_if_an_earlier_step_failed()
         self.positions.copy_(positions, non_blocking=True)
         self.hidden_states.copy_(hidden_states, non_blocking=True)
         self.graph.replay()

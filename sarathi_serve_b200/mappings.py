@@ -16,6 +16,22 @@ def divide(numerator: int, denominator: int) -> int:
     return numerator // denominator
 
 
+_MAX_ROW_BYTES = 32 * 1024
+
+
+def _regroup_width(numel: int, es: int) -> int:
+    """Largest row length (elements) with 16-byte-multiple rows of at most 32 KiB that divides ``numel``; 0 if none."""
+    step = 16 // es
+    if numel % step != 0:
+        return 0
+    w = min(numel, _MAX_ROW_BYTES // es) // step * step
+    while w >= step:
+        if numel % w == 0:
+            return w
+        w -= step
+    return 0
+
+
 def copy_to_tensor_model_parallel_region(input_: torch.Tensor) -> torch.Tensor:
     return input_
 
@@ -26,9 +42,25 @@ def reduce_from_tensor_model_parallel_region(input_: torch.Tensor) -> torch.Tens
         return input_
     if not input_.is_contiguous():
         raise RuntimeError("reduce_from_tensor_model_parallel_region: tensor must be contiguous")
-    flat = input_.view(-1, input_.shape[-1])
-    comm = ps.get_tensor_model_parallel_comm()
-    comm.all_reduce(flat, out=flat)
+    es = input_.element_size()
+    width = input_.shape[-1]
+    if (width * es) % 16 != 0 or width * es > _MAX_ROW_BYTES:
+        # The kernels move whole 16-byte vectors of rows of at most 32 KiB.  An element-wise sum does not care
+        # about the row structure: regroup the elements into rows the kernels take, or, when the tensor's size
+        # itself is not a multiple of 16 bytes, leave this (off-path) call to torch.distributed.
+        width = _regroup_width(input_.numel(), es)
+        if width == 0:
+            import torch.distributed as dist
+            dist.all_reduce(input_, group=ps.get_tensor_model_parallel_group())
+            return input_
+    flat = input_.view(-1, width)
+    es_total = flat.shape[0] * width * es
+    comm = ps.get_tensor_model_parallel_comm(max(es_total, ps.DEFAULT_COMM_REGION_BYTES)
+                                             if ps._TP_COMM is None else None)
+    rows_per_call = max(1, comm.region_bytes // (width * es) // comm.world * comm.world)
+    for r0 in range(0, flat.shape[0], rows_per_call):  # batches larger than the context's regions go in slices
+        part = flat[r0:r0 + rows_per_call]
+        comm.all_reduce(part, out=part)
     return input_
 
 

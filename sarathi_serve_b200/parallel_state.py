@@ -13,6 +13,23 @@ _TP_WORLD_SIZE_OVERRIDE: Optional[int] = None
 _TP_RANK_OVERRIDE: Optional[int] = None
 _TP_COMM = None
 _INITIALISED = False
+# The reference's own parallel_state module, when this package runs underneath the reference's model_executor
+# (sarathi_serve_b200.install): group, rank and size are then read from there.
+_FOLLOWED = None
+
+
+def follow(reference_parallel_state) -> None:
+    """Read the tensor-parallel group / rank / size from another module with the reference's accessor names
+    (``get_tensor_model_parallel_{group,rank,world_size}``, ``model_parallel_is_initialized``); ``None`` stops that."""
+    global _FOLLOWED, _TP_COMM
+    if _TP_COMM is not None and reference_parallel_state is not _FOLLOWED:
+        _TP_COMM.close()
+        _TP_COMM = None
+    _FOLLOWED = reference_parallel_state
+
+
+def _following() -> bool:
+    return _FOLLOWED is not None and _FOLLOWED.model_parallel_is_initialized()
 
 # Largest [T, H] batch (bytes) a collective of the shared context may carry.
 DEFAULT_COMM_REGION_BYTES = 64 << 20
@@ -46,10 +63,12 @@ def initialize_model_parallel(tensor_model_parallel_size: int = 1, pipeline_mode
 
 
 def model_parallel_is_initialized() -> bool:
-    return _INITIALISED
+    return _INITIALISED or _following()
 
 
 def get_tensor_model_parallel_group():
+    if _following():
+        return _FOLLOWED.get_tensor_model_parallel_group()
     assert _INITIALISED, "tensor model parallel group is not initialized"
     return _TP_GROUP
 
@@ -67,6 +86,8 @@ def set_tensor_model_parallel_rank(rank: Optional[int]) -> None:
 def get_tensor_model_parallel_world_size() -> int:
     if _TP_WORLD_SIZE_OVERRIDE is not None:
         return _TP_WORLD_SIZE_OVERRIDE
+    if _following():
+        return _FOLLOWED.get_tensor_model_parallel_world_size()
     if not _INITIALISED or _TP_GROUP is None:
         return 1 if _TP_RANKS is None else len(_TP_RANKS)
     import torch.distributed as dist
@@ -76,6 +97,8 @@ def get_tensor_model_parallel_world_size() -> int:
 def get_tensor_model_parallel_rank() -> int:
     if _TP_RANK_OVERRIDE is not None:
         return _TP_RANK_OVERRIDE
+    if _following():
+        return _FOLLOWED.get_tensor_model_parallel_rank()
     if not _INITIALISED or _TP_GROUP is None:
         return 0
     import torch.distributed as dist
@@ -93,7 +116,8 @@ def get_tensor_model_parallel_comm(region_bytes: Optional[int] = None):
     if _TP_COMM is None:
         from .comm import TPComm
         _TP_COMM = TPComm(get_tensor_model_parallel_rank(), get_tensor_model_parallel_world_size(),
-                          region_bytes or DEFAULT_COMM_REGION_BYTES, group=_TP_GROUP)
+                          region_bytes or DEFAULT_COMM_REGION_BYTES,
+                          group=get_tensor_model_parallel_group() if model_parallel_is_initialized() else None)
     elif region_bytes is not None and region_bytes > _TP_COMM.region_bytes:
         raise RuntimeError(f"the tensor-parallel context was created with {_TP_COMM.region_bytes} byte regions; "
                            f"{region_bytes} requested -- create it first with the larger size")

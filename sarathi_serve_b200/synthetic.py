@@ -51,7 +51,7 @@ class LayerCase:
                                max_position_embeddings=self.max_position, hidden_act="silu", num_hidden_layers=1)
 
 
-# BASELINE configurations (1: CPU/gloo fp32 oracle case, 2: Llama-3-8B-shaped bf16 layer, 4: 70B-shaped).
+# Named workloads (config1: CPU/gloo fp32 oracle case, config2: Llama-3-8B-shaped bf16 layer, config4_*: 70B-shaped).
 CASES: Dict[str, LayerCase] = {
     "config1": LayerCase("config1", 1024, 16, 4, 64, 2816, 1e-5, 10000.0, 2048, 256, 0, 32, 256, 2048, torch.float32),
     "config2": LayerCase("config2", 4096, 32, 8, 128, 14336, 1e-5, 500000.0, 8192, 448, 0, 64, 512, 8192, torch.bfloat16),

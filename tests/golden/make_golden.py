@@ -426,7 +426,8 @@ def _worker_rope(rank: int, reference: str, out_path: str) -> None:
 
 def main() -> None:
     ap = argparse.ArgumentParser()
-    ap.add_argument("--reference", default="/root/reference")
+    ap.add_argument("--reference", default=os.environ.get("SARATHI_REFERENCE"), required="SARATHI_REFERENCE" not in os.environ,
+                    help="checkout of microsoft/sarathi-serve (or $SARATHI_REFERENCE)")
     ap.add_argument("--only", default=None)
     a = ap.parse_args()
     import torch.multiprocessing as mp

@@ -34,11 +34,12 @@ def _host_barrier():
     dist.barrier()
 
 
-def _entry(rank, world, port, fn_name, ret):
+def _entry(rank, world, port, fn_name, ret, nvls):
     try:
         os.environ["MASTER_ADDR"] = "127.0.0.1"
         os.environ["MASTER_PORT"] = str(port)
         os.environ["NCCL_NVLS_ENABLE"] = "0"
+        os.environ["SB200_NVLS"] = "1" if nvls else "0"  # heaps bound to an NVSwitch multicast range, or plain peer mappings
         import torch.distributed as dist
         torch.cuda.set_device(rank)
         dist.init_process_group("gloo", rank=rank, world_size=world)
@@ -47,27 +48,32 @@ def _entry(rank, world, port, fn_name, ret):
         try:
             globals()[fn_name](rank, world)
             torch.cuda.synchronize()
+            dist.barrier()  # nobody unbinds its heap while a peer's kernels may still touch it
+            mc = ps._TP_COMM is not None and ps._TP_COMM.multicast
         finally:
             ps.destroy_model_parallel()
             dist.destroy_process_group()
-        ret[rank] = "ok"
+        ret[rank] = "ok" if (mc or not nvls) else "ok-without-multicast"
     except Exception:  # report the traceback to the parent instead of a bare exit code
         ret[rank] = traceback.format_exc()
 
 
-def _run(fn_name, port, world):
+def _run(fn_name, port, world, nvls=True):
     _need_gpus(world)
-    port += 10 * world
+    port += 10 * world + (100 if nvls else 0)
     ctx = mp.get_context("spawn")
     mgr = ctx.Manager()
     ret = mgr.dict()
-    procs = [ctx.Process(target=_entry, args=(r, world, port, fn_name, ret)) for r in range(world)]
+    procs = [ctx.Process(target=_entry, args=(r, world, port, fn_name, ret, nvls)) for r in range(world)]
     [p.start() for p in procs]
     [p.join(timeout=300) for p in procs]
     for p in procs:
         if p.is_alive():
             p.terminate()
             pytest.fail(f"{fn_name}: a rank did not finish within the time limit")
+    if nvls and all(ret.get(r) == "ok-without-multicast" for r in range(world)):
+        pytest.skip("the heaps could not be bound to an NVSwitch multicast range on this box: this run repeated the "
+                    "peer-mapping variant")
     bad = {r: ret.get(r) for r in range(world) if ret.get(r) != "ok"}
     if bad:  # the children's tracebacks, in full, on stdout as well (the assertion message gets truncated)
         for r, text in bad.items():
@@ -308,28 +314,85 @@ def _body_lost_peer(rank, world):
         with pytest.raises(RuntimeError, match="timed out"):
             comm.check_status()
         assert comm.status_code() == 0  # cleared by check_status
+        with pytest.raises(RuntimeError, match="out of step"):
+            comm.all_reduce(x)  # the context refuses further collectives until it is reset
     dist.barrier()  # rank 1 was idle on the host the whole time: nothing of it was in flight
+    comm.reset()  # collective: control words back to their initial state on every rank
+    y, _ = comm.all_reduce(x)
+    torch.cuda.synchronize()
+    assert float(y[0, 0]) == world
+    comm.check_status()
+
+
+def _body_graph_odd(rank, world):
+    """A CUDA graph that holds ONE collective, replayed three times in a row, then an eager call, then the
+    graph again: the buffers and flags a call uses alternate with a counter kept on the device, so an odd
+    number of collectives per replay must neither corrupt a peer's reads nor stall."""
+    from sarathi_serve_b200 import parallel_state as ps
+    comm = ps.get_tensor_model_parallel_comm(16 << 20)
+    T, H = 256, 2048
+    for one_shot in (4 << 20, 0):
+        comm.set_one_shot_bytes(one_shot)
+        g = torch.Generator().manual_seed(11 + one_shot % 7)
+        parts = [torch.randn(T, H, generator=g).to(torch.bfloat16) for _ in range(world)]
+        x = parts[rank].cuda()
+        xs = x.clone()
+        out = torch.empty_like(x)
+        comm.all_reduce(xs, out=out)
+        _host_barrier()
+        st = torch.cuda.Stream()
+        st.wait_stream(torch.cuda.current_stream())
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.stream(st):
+            with torch.cuda.graph(graph, stream=st):
+                comm.all_reduce(xs, out=out)
+        torch.cuda.current_stream().wait_stream(st)
+        for rep in range(7):
+            scale = float(rep + 1)
+            xs.copy_(x * scale)
+            if rep == 4:
+                y, _ = comm.all_reduce(xs)  # an eager call between replays
+                res = y.clone()
+            else:
+                graph.replay()
+                res = out.clone()
+            total = sum((p * scale).to(torch.bfloat16).float() for p in parts)
+            assert _rel(res, total) <= 1e-2, (one_shot, rep)
+    comm.check_status()
 
 
 # -------------------------------------------------------------------- tests
+SCHEMES = pytest.mark.parametrize("nvls", (False, True), ids=("peer-loads", "nvls"))
+
+
+@SCHEMES
 @pytest.mark.parametrize("world", WORLDS)
-def test_all_reduce_multi_gpu(world):
-    _run("_body_all_reduce", 29801, world)
+def test_all_reduce_multi_gpu(world, nvls):
+    _run("_body_all_reduce", 29801, world, nvls)
 
 
+@SCHEMES
 @pytest.mark.parametrize("world", WORLDS)
-def test_rowpar_linear_multi_gpu(world):
-    _run("_body_rowpar", 29802, world)
+def test_rowpar_linear_multi_gpu(world, nvls):
+    _run("_body_rowpar", 29802, world, nvls)
 
 
+@SCHEMES
 @pytest.mark.parametrize("world", WORLDS)
-def test_decoder_layer_multi_gpu(world):
-    _run("_body_layer", 29803, world)
+def test_decoder_layer_multi_gpu(world, nvls):
+    _run("_body_layer", 29803, world, nvls)
 
 
+@SCHEMES
 @pytest.mark.parametrize("world", WORLDS)
-def test_layer_stack_with_sharded_residual_multi_gpu(world):
-    _run("_body_carry", 29806, world)
+def test_layer_stack_with_sharded_residual_multi_gpu(world, nvls):
+    _run("_body_carry", 29806, world, nvls)
+
+
+@SCHEMES
+@pytest.mark.parametrize("world", (2, 4))
+def test_graph_with_an_odd_number_of_collectives_replays(world, nvls):
+    _run("_body_graph_odd", 29808, world, nvls)
 
 
 @pytest.mark.parametrize("world", WORLDS)
@@ -344,4 +407,5 @@ def test_moe_block_multi_gpu(world):
 
 @pytest.mark.parametrize("world", (2, 4))
 def test_lost_peer_reports_timeout(world):
-    _run("_body_lost_peer", 29804, world)
+    # peer mappings only: a rank must not leave while its memory is bound to a multicast object
+    _run("_body_lost_peer", 29804, world, nvls=False)

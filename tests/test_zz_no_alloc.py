@@ -34,6 +34,12 @@ def _compare(ids, E, block):
     assert int(n1) == npp
     assert torch.equal(s1, s0), "sorted_token_ids differ between the two entry points"
     assert torch.equal(e1[:npp // block], e0[:npp // block]), "expert_ids differ between the two entry points"
+    # and directly against the CPU oracle of the reference's kernel (not only through the other entry point)
+    from oracle import tp_layer_oracle as O
+    so, eo, no = O.moe_align_block_size(ids.cpu(), block, E)
+    assert int(no) == int(n1)
+    assert torch.equal(s1.cpu()[:npp], so[:npp].to(torch.int32)), "sorted_token_ids differ from the oracle"
+    assert torch.equal(e1.cpu()[:npp // block], eo[:npp // block].to(torch.int32)), "expert_ids differ from the oracle"
 
 
 def test_noalloc_matches_regular_entry_point_twice_in_a_row():
