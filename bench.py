@@ -20,7 +20,8 @@ the path).  Inputs are seeded synthetic tensors (sarathi_serve_b200.synthetic).
 `e2e`     : tokens/s through the public layer API with HOST buffers: pinned H2D of the
             hidden states and positions, LlamaDecoderLayer.forward and the D2H of the result, all captured
             once per layer in a CUDA graph (graph_runner.LayerGraph with host_io) and replayed, then a host
-            sync, every step.
+            sync, every step.  At N > 1 every rank moves its T/N token rows over PCIe and the full input is
+            assembled over NVLink inside the graph (shard_host_io).
 `roofline`: the dominant kernel (gate_up GEMM + SiLU*mul), timed alone with CUDA events.
 Weights of several distinct layers are cycled so that each step's operands exceed the L2.
 One JSON line is printed by rank 0.
@@ -85,6 +86,9 @@ def parse():
     ap.add_argument("--parts", action="store_true",
                     help="instead of the step benchmark: time every kernel of the path on its own (CUDA graphs) and "
                          "print one JSON line of per-kernel times with achieved TFLOP/s, HBM GB/s and NVLink GB/s")
+    ap.add_argument("--kernel-pass", action="store_true",
+                    help="with --parts: launch every kernel of the path twice, eagerly, at the workload's shapes and "
+                         "exit -- the short program a profiler is pointed at (one GPU)")
     ap.add_argument("--tune-cache", default=None,
                     help="JSON file of tile configurations: read if present (no tuning launches), else written")
     ap.add_argument("--cpu-baseline-seconds", type=float, default=15.0)
@@ -242,7 +246,8 @@ def check_parity(case, t, world, rank, dev, step_resident, runner0, layers, max_
     lo, hi = rank * rpr, min(T, rank * rpr + rpr)
     err_out = O.rel_err(normed.cpu(), ref["out_normed"])
     err_res = float((resid[lo:hi].cpu().double() - ref["out"][lo:hi].double()).abs().max()) / float(ref["out"].double().abs().max())
-    err_e2e = O.rel_err(e2e_out, ref["out"])
+    io_lo, io_hi = runner0.row_range
+    err_e2e = float((e2e_out.double() - ref["out"][io_lo:io_hi].double()).abs().max()) / float(ref["out"].double().abs().max())
     p = {"max_rel_err_out": max_over_ranks(err_out), "max_rel_err_residual_rows": max_over_ranks(err_res),
          "max_rel_err_e2e": max_over_ranks(err_e2e), "tol": PARITY_TOL,
          "against": f"CPU oracle of the layer over all {world} shards; every rank checks its outputs, max over ranks"}
@@ -366,10 +371,14 @@ def run_native(a):
         from sarathi_serve_b200.graph_runner import LayerGraph
         # (host_io: the H2D copies of the step's inputs and the D2H copy of its result are nodes of the graph,
         #  so a step is one launch and one host synchronisation)
-        runners = [LayerGraph(l, T, attn, host_io=True) for l in layers]
+        #  At N > 1 the host buffers are sharded by token rows: each rank uploads T/N rows, the full input is
+        #  assembled over NVLink by an all-gather inside the graph, and each rank downloads its T/N rows of the
+        #  result -- the step's hidden states cross PCIe once per node, not once per rank.)
+        runners = [LayerGraph(l, T, attn, host_io=True, shard_host_io=world > 1) for l in layers]
+        io_lo, io_hi = runners[0].row_range
         for r_ in runners:
             r_.host_positions.copy_(pos_host)
-            r_.host_hidden_states.copy_(x_host)
+            r_.host_hidden_states.copy_(x_host[io_lo:io_hi])
         barrier()
 
         def step_e2e(i):
@@ -377,7 +386,15 @@ def run_native(a):
             torch.cuda.current_stream().synchronize()
 
         e2e_steps = max(50, a.steps)
-        for i in range(max(10, a.warmup)):
+        # untimed lead-in: at least `warmup` steps and at least 0.3 s of them, so that the clocks have settled under
+        # this leg's duty cycle (the GPU idled while the graphs were built); the same count on every rank
+        n_warm = max(10, a.warmup)
+        t_w = time.perf_counter()
+        for i in range(n_warm):
+            step_e2e(i)
+        per = max(1e-5, (time.perf_counter() - t_w) / n_warm)
+        extra = int(max_over_ranks(max(0.0, 0.3 - n_warm * per) / per))
+        for i in range(extra):
             step_e2e(i)
         barrier()
         t0 = time.perf_counter()
@@ -430,7 +447,12 @@ def run_native(a):
 
         # ---- the reference's GPU sequence on this box, for comparison: cuBLAS GEMMs (torch.matmul), the
         # separate rotary / SiLU*mul / add+RMSNorm kernels and an NCCL all-reduce after each row-parallel GEMM
-        from sarathi_serve_b200 import activation_ops, layernorm_ops, pos_encoding_ops
+        ref_ops = load_reference_ops()
+        if ref_ops is not None:
+            # the reference's own compiled kernels (its csrc built by its setup.py into baseline/_ref)
+            layernorm_ops, activation_ops, pos_encoding_ops = ref_ops["layernorm_ops"], ref_ops["activation_ops"], ref_ops["pos_encoding_ops"]
+        else:
+            from sarathi_serve_b200 import activation_ops, layernorm_ops, pos_encoding_ops
         sa0 = layers[0].self_attn
         cache = sa0.rotary_emb.cos_sin_cache
         d_loc = case.intermediate_size // world
@@ -445,15 +467,24 @@ def run_native(a):
             if world > 1:
                 dist.all_reduce(o)
             h = torch.empty_like(o)
-            r = torch.empty_like(o)
-            layernorm_ops.fused_add_rms_norm(h, r, o, x_dev, l.post_attention_layernorm.weight.data, 1e-5)
+            if ref_ops is not None:
+                # as the reference's layer does it (models/llama.py:248-254): ATen add, then its rms_norm kernel
+                r = x_dev + o
+                layernorm_ops.rms_norm(h, r, l.post_attention_layernorm.weight.data, 1e-5)
+            else:
+                r = torch.empty_like(o)
+                layernorm_ops.fused_add_rms_norm(h, r, o, x_dev, l.post_attention_layernorm.weight.data, 1e-5)
             gu_ = torch.matmul(h, l.mlp.gate_up_proj.weight.t())
             act = torch.empty(T, d_loc, dtype=gu_.dtype, device=dev)
             activation_ops.silu_and_mul(act, gu_)
             dn = torch.matmul(act, l.mlp.down_proj.weight.t())
             if world > 1:
                 dist.all_reduce(dn)
-            layernorm_ops.fused_add_rms_norm(h, o, dn, r, nxt.weight.data, 1e-5)
+            if ref_ops is not None:
+                o2 = r + dn
+                layernorm_ops.rms_norm(h, o2, nxt.weight.data, 1e-5)
+            else:
+                layernorm_ops.fused_add_rms_norm(h, o, dn, r, nxt.weight.data, 1e-5)
             return h
 
         try:
@@ -476,9 +507,13 @@ def run_native(a):
                 "l2": f"{n_layers} distinct weight sets ({n_layers * per_layer_bytes >> 20} MiB/GPU) cycled: "
                       "operands of consecutive steps exceed the 126 MB L2",
                 "parity": parity,
+                "pcie": pcie_probe(dev, T * H * es),
                 "clocks": clocks,
                 "e2e": {"value": T / (ms_e2e * 1e-3), "unit": UNIT, "ms_per_step": ms_e2e,
-                        "h2d_bytes_per_step": T * H * es + T * 8, "d2h_bytes_per_step": T * H * es},
+                        "h2d_bytes_per_step": (io_hi - io_lo) * H * es + T * 8, "d2h_bytes_per_step": (io_hi - io_lo) * H * es,
+                        "io": (f"per rank: token rows [{io_lo}, {io_hi}) of the {T} x {H} hidden states up and down, all "
+                               f"{T} positions up; whole job: {T * H * es} B up and down plus {world} x {T * 8} B of positions"
+                               if world > 1 else "the full batch up and down")},
                 "gpu_launches": (4 if world > 1 else 6) * a.steps, "launch_mode": "one CUDA graph of all timed steps",
                 "tile_cfgs": {k[0] + f"[{k[2]}x{k[3]}]": v for k, v in dense_ops._tuned.items()},
                 "roofline": {"bound": "tensor", "kernel": "gemm_sm100_kernel<bf16, EPI_SILU_MUL> (gate_up + SiLU*mul)",
@@ -491,9 +526,14 @@ def run_native(a):
                                        frac=layer_roofline(case, T, world, peak_tf, peak_hbm)["t_roof_us"] / (ms_resident * 1e3),
                                        peaks=f"{peak_src}: {peak_tf} TFLOP/s bf16 burst, {peak_hbm} GB/s HBM; NVLink "
                                              f"{NVLINK_GBS} GB/s per direction (measured peer copy)"),
-                "gpu_comparison": ({"what": "same step as cuBLAS GEMMs (torch.matmul) + separate rotary / SiLU*mul / "
-                                            "add+RMSNorm kernels" + (" + NCCL all-reduce" if world > 1 else "") +
-                                            ", one CUDA graph", "ms_per_step": ms_cublas,
+                "gpu_comparison": ({"what": "the reference's GPU sequence on this box: cuBLAS GEMMs (torch.matmul, what its "
+                                            "F.linear calls), " +
+                                            ("the reference's own rotary / silu_and_mul / rms_norm kernels compiled from its csrc "
+                                             f"({ref_ops['where']}) and ATen residual adds" if ref_ops is not None else
+                                             "this library's rotary / SiLU*mul / add+RMSNorm kernels (the reference's "
+                                             "compiled ops were not found under oracle/_ref or baseline/_ref)") +
+                                            (" + NCCL all-reduce" if world > 1 else "") + ", one CUDA graph",
+                                    "ms_per_step": ms_cublas,
                                     "value": T / (ms_cublas * 1e-3), "unit": UNIT} if ms_cublas else
                                    {"unavailable": cublas_err})}
         if not a.no_cpu_baseline:
@@ -508,6 +548,246 @@ def run_native(a):
         dist.destroy_process_group()
     if not parity["ok"]:
         raise SystemExit(f"parity against the oracle failed: {parity}")
+
+
+def load_reference_ops():
+    """The reference's own compiled CUDA ops (layernorm_ops, activation_ops, pos_encoding_ops) for the GPU comparison
+    arm: the reference's csrc compiled for sm_100 by oracle/build_ref.py into oracle/_ref (preferred), or the
+    extensions of a pip install of the reference under baseline/_ref; loaded as extension modules without importing
+    the reference's Python package.  None if neither is there or its kernels do not run on this GPU."""
+    import glob
+    import importlib.util
+    import torch
+    for base, pattern in ((os.path.join(ROOT, "oracle", "_ref"), "{}.so"),
+                          (os.path.join(ROOT, "baseline", "_ref", "sarathi"), "{}.*.so")):
+        mods = {}
+        try:
+            for name in ("layernorm_ops", "activation_ops", "pos_encoding_ops"):
+                path = glob.glob(os.path.join(base, pattern.format(name)))
+                if not path:
+                    raise FileNotFoundError(name)
+                spec = importlib.util.spec_from_file_location(name, path[0])
+                m = importlib.util.module_from_spec(spec)
+                spec.loader.exec_module(m)
+                mods[name] = m
+            # one trial launch: a build for another architecture fails here, not inside a graph capture
+            t = torch.ones(8, 64, device="cuda", dtype=torch.bfloat16)
+            o = torch.empty_like(t)
+            mods["layernorm_ops"].rms_norm(o, t, torch.ones(64, device="cuda", dtype=torch.bfloat16), 1e-5)
+            torch.cuda.synchronize()
+            mods["where"] = os.path.relpath(base, ROOT)
+            return mods
+        except Exception:
+            continue
+    return None
+
+
+def pcie_probe(dev, nbytes: int) -> dict:
+    """Pinned-host <-> device copy rates of this box for a buffer of the step's size (explains the gap between
+    the device-resident and the end-to-end figure; other tenants of the host share the PCIe links)."""
+    import torch
+    h = torch.empty(nbytes, dtype=torch.uint8).pin_memory()
+    d = torch.empty(nbytes, dtype=torch.uint8, device=dev)
+    out = {}
+    for name, fn in (("h2d", lambda: d.copy_(h, non_blocking=True)), ("d2h", lambda: h.copy_(d, non_blocking=True))):
+        for _ in range(3):
+            fn()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(10):
+            fn()
+        e1.record()
+        torch.cuda.synchronize()
+        us = e0.elapsed_time(e1) * 100.0
+        out[name + "_us"] = us
+        out[name + "_gbs"] = nbytes / us / 1e3
+    out["bytes"] = nbytes
+    return out
+
+
+def run_moe(a):
+    """Mixtral-8x7B-shaped MoE block (hidden 4096, 8 experts, top-2, expert intermediate 14336, experts sharded
+    along the intermediate dimension over N ranks) on a 1024-token chunk: router gate, routing, block
+    alignment, the two grouped expert GEMMs and the sum over the k slots fused with the all-reduce.  The block is
+    HBM-bound (every expert's shard is read once per step), so the roofline is bytes over the HBM copy rate.
+    `--parts` adds the time of every kernel of the block on its own."""
+    import torch
+    import torch.distributed as dist
+    from sarathi_serve_b200 import dense_ops, fused_moe as FM, moe_ops, parallel_state as ps, synthetic as S
+    from sarathi_serve_b200.decoder_layer import MixtralMoE
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("cpu:gloo,cuda:nccl", rank=rank, world_size=world, device_id=dev)
+    ps.initialize_model_parallel(world)
+    case = S.MOE_CASES[a.workload]
+    T, H, E, k, I = case.num_tokens, case.hidden_size, case.num_experts, case.top_k, case.intermediate_size
+    es = 2
+    d = I // world
+    comm = ps.get_tensor_model_parallel_comm(max(64 << 20, -(-T // world) * world * H * es))
+    shard = S.generate_moe(case, world=world, rank=rank)
+    g = torch.Generator().manual_seed(5)
+    gate_w = (torch.randn(E, H, generator=g) * 0.05).to(case.dtype)
+    weight_bytes = E * 3 * H * d * es
+    n_sets = max(1, -(-2 * L2_BYTES // weight_bytes))
+    torch.set_default_dtype(case.dtype)
+    blocks = []
+    for _ in range(n_sets):
+        m = MixtralMoE(E, k, H, I)
+        sd = m.state_dict()
+        with torch.no_grad():
+            sd["gate.weight"].copy_(gate_w)
+            sd["experts.w13_weight"].copy_(shard["w13"])
+            sd["experts.w2_weight"].copy_(shard["w2"])
+        blocks.append(m)
+    x = shard["x"].to(dev)
+    xs = [x.clone() for _ in range(n_sets)]  # the block overwrites its input
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def max_over_ranks(v: float) -> float:
+        if world == 1:
+            return v
+        tt = torch.tensor([v], dtype=torch.float64, device=dev)
+        dist.all_reduce(tt, op=dist.ReduceOp.MAX)
+        return float(tt.item())
+
+    def graph_us(fn, n, reps=5):
+        st = torch.cuda.Stream()
+        st.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(st), torch.inference_mode():
+            for i in range(3):
+                fn(i)
+            barrier()
+            g_ = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g_, stream=st):
+                for i in range(n):
+                    fn(i)
+            g_.replay()
+            barrier()
+            k0, k1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            k0.record(st)
+            for _ in range(reps):
+                g_.replay()
+            k1.record(st)
+            barrier()
+        torch.cuda.current_stream().wait_stream(st)
+        return max_over_ranks(k0.elapsed_time(k1) / (n * reps) * 1e3)
+
+    def step(i):
+        j = i % n_sets
+        xs[j].copy_(x)  # restores the input the previous use overwrote (4 MiB, part of neither figure's bytes)
+        return blocks[j](xs[j])
+
+    peak_tf, peak_hbm, peak_src = peaks()
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
+    us_copy = graph_us(lambda i: xs[i % n_sets].copy_(x), max(a.steps, 4))
+    us_step = graph_us(step, max(a.steps, 4)) - us_copy
+    clocks = sampler.stop() if rank == 0 else None
+    comm.check_status()
+    dense_ops.check_status(dev)
+    # parity of one step against the CPU oracle on a subset of tokens (the oracle of the full block takes minutes):
+    # the block is token-wise apart from the expert sort, so the first 64 tokens alone give the same rows
+    from oracle import tp_layer_oracle as O
+    with torch.inference_mode():
+        got = blocks[0](x.clone())[:64].cpu()
+    shards_all = [S.generate_moe(case, world=world, rank=r) for r in range(world)] if world <= 2 or case.name != "config5" else None
+    parity = None
+    if shards_all is not None:
+        ref = O.moe_layer(shard["x"][:64], gate_w, [s_["w13"] for s_ in shards_all], [s_["w2"] for s_ in shards_all], k)
+        err = max_over_ranks(O.rel_err(got, ref))
+        parity = {"max_rel_err_out": err, "tol": PARITY_TOL, "ok": err <= PARITY_TOL,
+                  "against": "CPU oracle of the MoE block on the first 64 tokens"}
+    flops = 2.0 * T * k * H * 3 * d
+    hbm_bytes = weight_bytes + es * (T * H * 2 + T * k * (H + 2 * d) * 2)
+    parts = None
+    if a.parts:
+        with torch.inference_mode():
+            m0 = blocks[0]
+            logits, _ = m0.gate(x)
+            tw, ti = FM.fused_topk(x, logits, k, True)
+            blk = FM.block_rows()
+            parts = {}
+            parts["router_gate_gemm"] = {"us": graph_us(lambda i: blocks[i % n_sets].gate(x), 8)}
+            parts["topk_softmax"] = {"us": graph_us(lambda i: FM.fused_topk(x, logits, k, True), 8)}
+            parts["moe_align_block_size"] = {"us": graph_us(lambda i: FM.moe_align_block_size(ti, blk, E), 8)}
+            us_e = graph_us(lambda i: FM._expert_slots(x, blocks[i % n_sets].experts.w13_weight,
+                                                       blocks[i % n_sets].experts.w2_weight, tw, ti, True), 2 * n_sets)
+            parts["align+gather+gemm1+gemm2"] = {"us": us_e, "hbm_gbs": weight_bytes / us_e / 1e3,
+                                                 "tflops": flops / us_e / 1e6}
+    if rank == 0:
+        line = {"metric": "tp_moe_block_tokens_per_s", "value": T / (us_step * 1e-6), "unit": UNIT, "n_gpus": world,
+                "steps": a.steps, "warmup": a.warmup, "ms_per_step": us_step * 1e-3, "higher_is_better": True,
+                "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+                "config": {"workload": f"{a.workload}: Mixtral-8x7B-shaped MoE block (hidden {H}, {E} experts, top-{k}, expert "
+                                       f"intermediate {I}), {T}-token chunk, TP={world}", "tokens_per_step": T,
+                           "parallelism": f"tp{world}"},
+                "clocks": clocks, "parity": parity,
+                "roofline": {"bound": "hbm", "kernel": "MoE block: grouped expert GEMMs (gemm_sm100_kernel, grouped mode)",
+                             "achieved": hbm_bytes / us_step / 1e3, "peak": peak_hbm, "unit": "GB/s",
+                             "frac": hbm_bytes / us_step / 1e3 / peak_hbm, "peak_source": peak_src, "traffic": None,
+                             "algorithmic_bytes": hbm_bytes, "compute_us": flops / (peak_tf * 1e6),
+                             "hbm_us": hbm_bytes / (peak_hbm * 1e3)},
+                "parts": parts, "gpu_launches": 7 * a.steps}
+        print(json.dumps(line), flush=True)
+    barrier()
+    ps.destroy_model_parallel()
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def kernel_pass(case, layers, x, pos, normed, q, h, resid, act, nw, comm, dev):
+    """Two eager launches of every kernel of the path at the workload's shapes (nothing timed)."""
+    import torch
+    from sarathi_serve_b200 import (activation_ops, dense_ops, embedding_ops, fused_moe as FM, layernorm_ops, moe_ops,
+                                    pos_encoding_ops, synthetic as S)
+    T, H = x.shape
+    nl = len(layers)
+    sa = layers[0].self_attn
+    d = act.shape[1]
+    o1, o2 = torch.empty_like(x), torch.empty_like(x)
+    gu = torch.randn(T, 2 * d, device=dev, dtype=torch.float32).to(x.dtype)
+    ao = torch.empty(T, d, device=dev, dtype=x.dtype)
+    qkv = torch.randn(T, sa.q_size + 2 * sa.kv_size, device=dev, dtype=torch.float32).to(x.dtype)
+    qs, ks, _ = qkv.split([sa.q_size, sa.kv_size, sa.kv_size], dim=-1)
+    mc = S.MOE_CASES["config5"]
+    E, k, Tm, blk = mc.num_experts, mc.top_k, mc.num_tokens, FM.block_rows()
+    logits = torch.randn(Tm, E, device=dev, dtype=torch.float32)
+    tw = torch.empty(Tm, k, dtype=torch.float32, device=dev)
+    ti = torch.empty(Tm, k, dtype=torch.int32, device=dev)
+    xm = torch.randn(Tm, H, device=dev, dtype=torch.float32).to(x.dtype)
+    dm = mc.intermediate_size // 8  # the per-rank expert shard of an 8-way split
+    w13 = (torch.randn(E, 2 * dm, H, device=dev, dtype=torch.float32) * 0.02).to(x.dtype)
+    w2 = (torch.randn(E, H, dm, device=dev, dtype=torch.float32) * 0.02).to(x.dtype)
+    for i in range(2):
+        l = layers[i % nl]
+        layernorm_ops.rms_norm(o1, x, nw, 1e-5)
+        layernorm_ops.fused_add_rms_norm(o1, o2, h, x, nw, 1e-5)
+        activation_ops.silu_and_mul(ao, gu)
+        pos_encoding_ops.rotary_embedding(pos, qs, ks, sa.head_dim, sa.rotary_emb.cos_sin_cache, True)
+        l.self_attn.qkv_rotary(pos, normed)
+        dense_ops.linear(q, l.self_attn.o_proj.weight)
+        l.mlp.gate_up_proj.forward_silu_mul(h)
+        dense_ops.linear(act, l.mlp.down_proj.weight, residual=resid)
+        comm.rowpar_linear(q, l.self_attn.o_proj.weight, residual=x, norm_weight=nw, eps=1e-5)
+        moe_ops.topk_softmax(tw, ti, None, logits, renormalize=True)
+        FM.moe_align_block_size(ti, blk, E)
+        out3 = FM._expert_slots(xm, w13, w2, tw, ti, True)
+        FM.fused_experts(xm, w13, w2, tw, ti)
+        torch.cuda.synchronize()
+    comm.check_status()
+    dense_ops.check_status(dev)
+    print("kernel pass done", flush=True)
 
 
 def run_parts(a):
@@ -604,6 +884,12 @@ def run_parts(a):
         h, resid = sa.o_proj.forward_fused(q, x, nw, 1e-5)
         h, resid = h.clone(), resid.clone()
         act = l0.mlp.gate_up_proj.forward_silu_mul(h)
+        if a.kernel_pass:
+            kernel_pass(case, layers, x, pos, normed, q, h, resid, act, nw, comm, dev)
+            ps.destroy_model_parallel()
+            if world > 1:
+                dist.destroy_process_group()
+            return
         ar_bytes = 2.0 * (world - 1) / world * T * H * es  # per direction, per GPU
         gemm_entry("qkv_gemm+rotary", graph_us(lambda i: layers[i % nl].self_attn.qkv_rotary(pos, normed)), 2.0 * T * H * qkv_n)
         us = graph_us(lambda i: layers[i % nl].self_attn.o_proj.forward_fused(q, x, nw, 1e-5))
@@ -673,6 +959,8 @@ def main():
     a = parse()
     if a.impl == "reference":
         run_reference_arm(a)
+    elif a.workload in ("config5", "mini_moe"):
+        run_moe(a)
     elif a.parts:
         run_parts(a)
     else:

@@ -154,6 +154,14 @@ typedef struct sb200_rotary_args {
   int rot_dim;                /* must equal head_size for the fused epilogue */
   int rot_cols;               /* output columns [0, rot_cols) are q and k heads; the rest (v) pass through */
   int is_neox;
+  /* Optional: also append this step's keys and values to the paged KV cache from the epilogue (what the
+   * reference's attention wrapper does with three .contiguous() copies and flashinfer's
+   * append_paged_kv_cache, attention/flashinfer_attention_wrapper.py:253-270).  kv_cache NULL: off. */
+  void* kv_cache;             /* [pages, 2, page_size, kv_heads, head_size], output dtype */
+  const int64_t* kv_slots;    /* [T] from sb200_kv_cache_slots (-1: token not stored) */
+  int kv_page_size;
+  int num_kv_heads;           /* k columns are [rot_cols - num_kv_heads * head_size, rot_cols), v columns the next
+                                 num_kv_heads * head_size */
 } sb200_rotary_args;
 
 /* out[T, N] = x[T, K] * w[N, K]^T: the local matmul of a ColumnParallelLinear /
@@ -165,6 +173,10 @@ typedef struct sb200_rotary_args {
  *                        (out is the fused qkv buffer [T, N]).
  *   SB200_EPI_SILU_MUL : w holds the gate shard in rows [0, N/2) and the up shard in
  *                        rows [N/2, N); out is [T, N/2].
+ * residual / ldr: optional [T, N] tensor (row stride ldr) added to the rounded product in the
+ *   epilogue of the plain bf16 / fp16 kernel: out = residual + round(x w^T (+ bias)) -- the
+ *   `hidden_states = residual + hidden_states` that follows a row-parallel projection when there is
+ *   nothing to reduce (tensor-parallel size 1), models/llama.py:248,254.  NULL: none.
  * status: optional device word that receives a non-zero code if a bounded
  * pipeline wait inside the kernel ran out.
  * tile_cfg: 0 = let the library choose the tile shape, else
@@ -182,9 +194,27 @@ typedef struct sb200_rotary_args {
  * and, with the fused epilogues, the rotary_embedding call of models/llama.py:176-177
  * and the SiluAndMul call of models/llama.py:101-104. */
 int sb200_gemm_colpar(void* out, int64_t ldo, const void* x, int64_t ldx, const void* w, int64_t ldw,
-                      const void* bias, int64_t T, int64_t N, int64_t K, int dtype, int epilogue,
+                      const void* bias, const void* residual, int64_t ldr, int64_t T, int64_t N, int64_t K,
+                      int dtype, int epilogue,
                       const sb200_rotary_args* rot, uint32_t* status, int tile_cfg, void* workspace,
                       int64_t workspace_bytes, sb200_stream_t stream);
+
+/* Paged KV cache, layout [pages, 2, page_size, kv_heads, head_dim] ("NHD"; the reference's
+ * attention/flashinfer_attention_wrapper.py:69-77).  Entry i of a step belongs to request
+ * batch_indices[i] and is the token at position positions[i] of that request; its key goes to
+ * cache[page, 0, slot], its value to cache[page, 1, slot] with page = kv_indices[kv_indptr[b] + p / page_size],
+ * slot = p % page_size -- the semantics of flashinfer's append_paged_kv_cache, which the reference calls at
+ * flashinfer_attention_wrapper.py:261-270.
+ * sb200_kv_cache_slots: slots[i] = page * 2 * page_size + slot (the row of the cache seen as
+ *   [pages * 2 * page_size, kv_heads * head_dim] that receives the key; the value goes page_size rows
+ *   further), or -1 when batch_indices[i] < 0.  All arrays on the device, int32 except slots (int64).
+ * sb200_kv_cache_append: copies k / v rows ([n, kv_heads * head_dim] with row strides ldk / ldv in
+ *   elements: views of the fused qkv buffer are fine, no contiguous copy is needed) to those rows. */
+int sb200_kv_cache_slots(int64_t* slots, const int32_t* batch_indices, const int32_t* positions,
+                         const int32_t* kv_indices, const int32_t* kv_indptr, int64_t n, int page_size,
+                         sb200_stream_t stream);
+int sb200_kv_cache_append(void* cache, const void* k, int64_t ldk, const void* v, int64_t ldv, const int64_t* slots,
+                          int64_t n, int num_kv_heads, int head_dim, int page_size, int dtype, sb200_stream_t stream);
 
 /* The tile shape and schedule the two GEMM entry points would pick (epilogue 3 = the
  * row-parallel kernel): out[0..10] = cta_pairs, accumulators, BN, scheduling units,
@@ -193,6 +223,14 @@ int sb200_gemm_colpar(void* out, int64_t ldo, const void* x, int64_t ldx, const 
  * k-blocks.  Host-only; no counterpart in the reference. */
 int sb200_gemm_plan(int epilogue, int64_t T, int64_t N, int64_t K, int head_size, int tile_cfg,
                     int64_t workspace_bytes, int* out);
+
+/* Diagnostic: clocks the tensor pipe takes for `iters` k-blocks of four tcgen05.mma (bf16, K = 16 each) with
+ * M = 128 on one CTA (pair = 0) or M = 256 on a CTA pair (pair = 1) and N columns, both operands resident in
+ * shared memory (no loads in the timed loop).  dev_clocks[0] = SM clocks until the last MMA was issued,
+ * dev_clocks[1] = until all had completed (-1: the wait ran out).  These are the per-MMA costs the tile
+ * planner's model uses; `python -m sarathi_serve_b200.mma_rate` prints the table for the current GPU.
+ * No counterpart in the reference. */
+int sb200_diag_mma_rate(int pair, int n, int iters, int64_t* dev_clocks, sb200_stream_t stream);
 
 /* Vocabulary-parallel embedding lookup: out[t, :] = weight[ids[t] - vocab_start, :] if
  * vocab_start <= ids[t] < vocab_end, else zeros.  out: [T, H]; ids: [T] int64 (device); weight:
@@ -268,6 +306,16 @@ int sb200_comm_has_multicast(sb200_comm* comm);
  * destroyed and rebuilt). */
 int sb200_comm_reset(sb200_comm* comm, sb200_stream_t stream);
 
+/* All-gather of row blocks over the ranks: rank r holds rows [r * ceil(T / world), ...) of a [T, H]
+ * tensor (`in_rows` points at just those rows); afterwards every rank has all T rows in a
+ * context-owned buffer (*out_ptr, valid until the second-next collective) and, if given, in the local
+ * [T, H] tensor `out_copy`.  With a multicast alias each rank publishes its rows with multimem stores,
+ * otherwise the peers pull them.  Replaces gather-style plumbing around the layer stack such as the
+ * broadcast of a step's hidden states to the tensor-parallel workers; the reference itself has every
+ * worker receive the full batch (sarathi/model_executor/model_runner.py:67-117). */
+int sb200_all_gather_rows(sb200_comm* comm, const void* in_rows, int64_t T, int64_t H, int dtype, void* out_copy,
+                          sb200_stream_t stream, void** out_ptr);
+
 /* Sum `in` [T, H] over the ranks; then, on the summed rows,
  *   z = sum (+ bias) (+ residual);   y = norm_w ? rms_norm(z, norm_w, eps) : z.
  * The primary result (y) lands in a context-owned buffer on EVERY rank
@@ -319,11 +367,16 @@ int sb200_moe_gemm2(void* out3, const void* act, const void* w2, const int32_t* 
                     const int32_t* num_post_pad, const int32_t* sorted_ids, const float* topk_weights,
                     int64_t rows_cap, int64_t num_slots, int E, int64_t H, int64_t d, int dtype,
                     uint32_t* status, int tile_cfg, sb200_stream_t stream);
-/* out[t, :] = sum_j in3[t * top_k + j, :] (fp32 sum rounded once; fused_moe.py:539-543). */
-int sb200_moe_sum(void* out, const void* in3, int64_t T, int top_k, int64_t H, int dtype, sb200_stream_t stream);
+/* out[t, :] = sum_j in3[t * top_k + j, :] (fp32 sum rounded once; fused_moe.py:539-543).  With
+ * `residual` [T, H] (may be NULL): out = residual + that sum, the add that follows the MoE block in the
+ * decoder layer (models/mixtral.py:257). */
+int sb200_moe_sum(void* out, const void* in3, const void* residual, int64_t T, int top_k, int64_t H, int dtype,
+                  sb200_stream_t stream);
 /* The same sum fused into the copy-in phase of the all-reduce over the tensor-parallel ranks
- * (fused_moe/layer.py:128-132); results as sb200_all_reduce without bias / residual / norm. */
-int sb200_moe_sum_all_reduce(sb200_comm* comm, const void* in3, int64_t T, int top_k, int64_t H, int dtype,
+ * (fused_moe/layer.py:128-132); results as sb200_all_reduce without bias / norm; `residual` [T, H] (may
+ * be NULL) is added to the reduced rows. */
+int sb200_moe_sum_all_reduce(sb200_comm* comm, const void* in3, const void* residual, int64_t T, int top_k, int64_t H,
+                             int dtype,
                              void* out_copy, sb200_stream_t stream, void** out_ptr);
 
 #ifdef __cplusplus

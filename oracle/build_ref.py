@@ -103,6 +103,34 @@ def build(reference: str, jobs: int = 0, verbose: bool = True) -> bool:
     return True
 
 
+def complete_python_install(reference: str, target: str, verbose: bool = True) -> int:
+    """The reference's setup.py lists its packages with find_packages(), which skips the four directories of
+    the package that have no __init__.py (core/proto, core/sequence_manager,
+    model_executor/parallel_utils/pipeline_parallel, layers/fused_moe/configs), so a
+    `pip install --target <target> <reference>` cannot even `import sarathi`.  This adds those directories to
+    such an install (a git-ignored directory; nothing of the reference enters the repository).  Returns the
+    number of files added."""
+    import shutil
+    src_root, dst_root = os.path.join(reference, "sarathi"), os.path.join(target, "sarathi")
+    if not (os.path.isdir(src_root) and os.path.isdir(dst_root)):
+        return 0
+    added = 0
+    for d, dirs, files in os.walk(src_root):
+        dirs[:] = [x for x in dirs if x != "__pycache__"]
+        rel = os.path.relpath(d, src_root)
+        dst = os.path.join(dst_root, rel)
+        if os.path.isdir(dst):
+            continue
+        os.makedirs(dst)
+        for f in files:
+            if f.endswith((".py", ".pyi", ".json")):
+                shutil.copy2(os.path.join(d, f), os.path.join(dst, f))
+                added += 1
+        if verbose:
+            print(f"[baseline/_ref] added sarathi/{rel}")
+    return added
+
+
 if __name__ == "__main__":
     ap = argparse.ArgumentParser()
     ap.add_argument("--reference", default=os.environ.get("SARATHI_REFERENCE"), required="SARATHI_REFERENCE" not in os.environ,

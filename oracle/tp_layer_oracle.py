@@ -238,6 +238,38 @@ def sum_over_ranks(parts: Sequence[torch.Tensor]) -> torch.Tensor:
     return acc
 
 
+def kv_cache_slots(batch_indices, positions, kv_indices, kv_indptr, page_size: int) -> torch.Tensor:
+    """Row of the cache, seen as [pages * 2 * page_size, kv_heads * head_dim], that receives each token's key
+    (-1 for a negative batch index): page = kv_indices[kv_indptr[b] + p // page_size], slot = p % page_size --
+    the addressing of flashinfer's append_paged_kv_cache (flashinfer-python, pinned 0.4.1 in the reference's
+    requirements.txt:18; not vendored), which the reference calls at
+    attention/flashinfer_attention_wrapper.py:261-270."""
+    b = np.asarray(batch_indices, dtype=np.int64)
+    p = np.asarray(positions, dtype=np.int64)
+    ki = np.asarray(kv_indices, dtype=np.int64)
+    kp = np.asarray(kv_indptr, dtype=np.int64)
+    out = np.full(b.shape, -1, dtype=np.int64)
+    ok = b >= 0
+    page = ki[kp[b[ok]] + p[ok] // page_size]
+    out[ok] = page * (2 * page_size) + p[ok] % page_size
+    return torch.from_numpy(out)
+
+
+def append_paged_kv_cache(key: torch.Tensor, value: torch.Tensor, batch_indices, positions, cache: torch.Tensor,
+                          kv_indices, kv_indptr) -> None:
+    """In place on ``cache`` [pages, 2, page_size, kv_heads, head_dim] (attention/flashinfer_attention_wrapper.py:69-77):
+    cache[page, 0, slot] = key[i], cache[page, 1, slot] = value[i]."""
+    page_size = cache.shape[2]
+    s = kv_cache_slots(batch_indices, positions, kv_indices, kv_indptr, page_size)
+    flat = cache.view(cache.shape[0] * 2 * page_size, -1)
+    n = s.numel()
+    k2, v2 = key.reshape(n, -1), value.reshape(n, -1)
+    for i in range(n):
+        if s[i] >= 0:
+            flat[s[i]] = k2[i]
+            flat[s[i] + page_size] = v2[i]
+
+
 def decoder_layer(params: Sequence[Dict[str, torch.Tensor]], x: torch.Tensor, positions: torch.Tensor, *,
                   num_heads: int, num_kv_heads: int, head_dim: int, eps: float, cache: torch.Tensor,
                   all_reduce: Optional[Callable[[List[torch.Tensor]], torch.Tensor]] = None,

@@ -33,20 +33,24 @@ _P, _I, _L, _F = c_void_p, c_int, c_int64, c_float
 class RotaryArgs(ctypes.Structure):
     """Mirror of ``sb200_rotary_args`` (include/sarathi_b200.h)."""
     _fields_ = [("positions", c_void_p), ("cos_sin_cache", c_void_p), ("head_size", c_int),
-                ("rot_dim", c_int), ("rot_cols", c_int), ("is_neox", c_int)]
+                ("rot_dim", c_int), ("rot_cols", c_int), ("is_neox", c_int),
+                ("kv_cache", c_void_p), ("kv_slots", c_void_p), ("kv_page_size", c_int), ("num_kv_heads", c_int)]
 
 
 _PP = ctypes.POINTER(c_void_p)
 _GEMM_SIGS: dict = {
-    "sb200_gemm_colpar": (_I, [_P, _L, _P, _L, _P, _L, _P, _L, _L, _L, _I, _I, ctypes.POINTER(RotaryArgs), _P, _I, _P,
-                               _L, _P]),
+    "sb200_gemm_colpar": (_I, [_P, _L, _P, _L, _P, _L, _P, _P, _L, _L, _L, _L, _I, _I, ctypes.POINTER(RotaryArgs), _P, _I,
+                               _P, _L, _P]),
     "sb200_moe_block_rows": (_I, []),
     "sb200_moe_gather_rows": (_I, [_P, _P, _P, _P, _L, _L, _L, _I, _I, _P]),
     "sb200_moe_gemm1": (_I, [_P, _P, _P, _P, _P, _L, _I, _L, _L, _I, _P, _I, _P]),
     "sb200_moe_gemm2": (_I, [_P, _P, _P, _P, _P, _P, _P, _L, _L, _I, _L, _L, _I, _P, _I, _P]),
-    "sb200_moe_sum": (_I, [_P, _P, _L, _I, _L, _I, _P]),
-    "sb200_moe_sum_all_reduce": (_I, [_P, _P, _L, _I, _L, _I, _P, _P, _PP]),
+    "sb200_moe_sum": (_I, [_P, _P, _P, _L, _I, _L, _I, _P]),
+    "sb200_moe_sum_all_reduce": (_I, [_P, _P, _P, _L, _I, _L, _I, _P, _P, _PP]),
     "sb200_gemm_plan": (_I, [_I, _L, _L, _L, _I, _I, _L, ctypes.POINTER(c_int)]),
+    "sb200_kv_cache_slots": (_I, [_P, _P, _P, _P, _P, _L, _I, _P]),
+    "sb200_kv_cache_append": (_I, [_P, _P, _L, _P, _L, _P, _L, _I, _I, _I, _I, _P]),
+    "sb200_diag_mma_rate": (_I, [_I, _I, _I, _P, _P]),
     "sb200_comm_heap_bytes": (_L, [_L]),
     "sb200_comm_create": (_I, [_PP, _I, _I, _L]),
     "sb200_comm_create_external": (_I, [_PP, _I, _I, _L, _PP]),
@@ -63,6 +67,7 @@ _GEMM_SIGS: dict = {
     "sb200_comm_set_multicast": (_I, [_P, _P]),
     "sb200_comm_has_multicast": (_I, [_P]),
     "sb200_comm_reset": (_I, [_P, _P]),
+    "sb200_all_gather_rows": (_I, [_P, _P, _L, _L, _I, _P, _P, _PP]),
     "sb200_comm_status": (_I, [_P, _P, ctypes.POINTER(ctypes.c_uint32)]),
     "sb200_comm_clear_status": (_I, [_P, _P]),
     "sb200_all_reduce": (_I, [_P, _P, _L, _L, _I, _P, _P, _P, _F, _I, _P, _P, _P, _PP, _PP]),

@@ -10,8 +10,9 @@ from cudaMalloc with the 64-byte CUDA IPC handles exchanged once at
 construction; either way a host barrier follows.  The data path is this
 library's own kernels over NVLink; NCCL is not called on it.
 
-``SB200_NVLS=0`` in the environment (or ``multicast=False``) keeps the heaps
-on plain peer mappings; every rank of a group has to make the same choice."""
+``SB200_NVLS=1`` in the environment (or ``multicast=True``) asks for the
+multicast heaps; without it the heaps stay on plain peer mappings.  Every rank
+of a group has to make the same choice."""
 from __future__ import annotations
 
 import ctypes
@@ -53,7 +54,7 @@ class TPComm:
         self.multicast = False
         lib = N.lib()
         if multicast is None:
-            multicast = os.environ.get("SB200_NVLS", "1") != "0"
+            multicast = os.environ.get("SB200_NVLS", "0") == "1"
         with torch.cuda.device(self.device):
             if world > 1 and multicast and self._create_on_symmetric_memory(lib, int(region_bytes)):
                 pass
@@ -230,6 +231,26 @@ class TPComm:
         y = out if out is not None else self._view(op.value, T, H, x.dtype)
         z = resid_out if resid_out is not None else self._view(rp.value, T, H, x.dtype)
         return y, (z if norm_weight is not None else None)
+
+    def all_gather_rows(self, rows: torch.Tensor, T: int, *, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """``rows``: this rank's block of a [T, H] tensor -- rows [rank * ceil(T / world), ...), possibly none.
+        Returns the full [T, H] tensor (``out``, or a view into the context's heap valid until the
+        second-next collective) on every rank."""
+        self._usable()
+        N.require_cuda(rows, out)
+        if rows.dim() != 2 or not rows.is_contiguous():
+            raise RuntimeError("all_gather_rows: rows must be a contiguous [n, H] tensor")
+        H = rows.shape[1]
+        rpr = -(-T // self.world)
+        own = max(0, min(rpr, T - self.rank * rpr))
+        if rows.shape[0] != own:
+            raise RuntimeError(f"all_gather_rows: rank {self.rank} of {self.world} holds {own} of {T} rows, got {rows.shape[0]}")
+        if out is not None and (out.dtype != rows.dtype or tuple(out.shape) != (T, H) or not out.is_contiguous()):
+            raise RuntimeError(f"out must be a contiguous [{T}, {H}] tensor of the rows' dtype")
+        op = ctypes.c_void_p()
+        N.check(N.lib().sb200_all_gather_rows(self._h, N.ptr(rows) if own else None, T, H, N.dtype_id(rows), N.ptr(out),
+                                              N.stream_ptr(), ctypes.byref(op)), "all_gather_rows")
+        return out if out is not None else self._view(op.value, T, H, rows.dtype)
 
     def rowpar_linear(self, x: torch.Tensor, weight: torch.Tensor, *, bias=None, residual=None, norm_weight=None,
                       eps: float = 0.0, resid_everywhere: bool = True, out=None, resid_out=None,

@@ -239,6 +239,7 @@ static int comm_new(sb200_comm** out, int rank, int world, int64_t region_bytes)
   c->wait_cycles = 5 * ptx::kWaitLimitCycles;  // ~10 s: ranks of a serving engine can be seconds apart on the host (first steps, GC)
   c->one_shot_bytes = 4u << 20;
   if (const char* e = getenv("SB200_ONE_SHOT_BYTES")) c->one_shot_bytes = (size_t)atoll(e);
+  if (const char* e = getenv("SB200_WAIT_LIMIT_CYCLES")) { const long long v = atoll(e); if (v > 0) c->wait_cycles = v; }
   if (cudaGetDevice(&c->device) != cudaSuccess) { delete c; set_error("comm_create: no current CUDA device"); return SB200_ERR_CUDA; }
   *out = c;
   return SB200_OK;
@@ -406,10 +407,10 @@ extern "C" int sb200_all_gather_rows(sb200_comm* comm, const void* in_rows, int6
   return SB200_OK;
 }
 
-extern "C" int sb200_moe_sum_all_reduce(sb200_comm* comm, const void* in3, int64_t T, int top_k, int64_t H, int dtype,
-                                        void* out_copy, sb200_stream_t stream, void** out_ptr) {
+extern "C" int sb200_moe_sum_all_reduce(sb200_comm* comm, const void* in3, const void* residual, int64_t T, int top_k,
+                                        int64_t H, int dtype, void* out_copy, sb200_stream_t stream, void** out_ptr) {
   SB_CHECK_ARG(top_k >= 1, "moe_sum_all_reduce: top_k must be positive");
-  return do_all_reduce(comm, in3, T, H, dtype, nullptr, nullptr, nullptr, 0.f, 0, out_copy, nullptr,
+  return do_all_reduce(comm, in3, T, H, dtype, nullptr, residual, nullptr, 0.f, 0, out_copy, nullptr,
                        (cudaStream_t)stream, out_ptr, nullptr, top_k);
 }
 

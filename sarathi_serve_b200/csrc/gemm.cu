@@ -64,7 +64,7 @@ int make_tmap_2d(CUtensorMap* map, int dtype, const void* ptr, int64_t rows, int
 //   data-parallel: whole tiles per unit (no fix-up, but units may get unequal tile counts);
 //   stream-K: every unit gets the same number of k-blocks and tiles cut along K are summed
 //   through the workspace by the last unit to arrive.
-GemmPlan plan_gemm(int epi, int64_t M, int64_t N, int64_t K, int head_size, int tile_cfg, size_t ws_bytes) {
+GemmPlan plan_gemm(int epi, int64_t M, int64_t N, int64_t K, int head_size, int tile_cfg, size_t ws_bytes, int neox) {
   GemmPlan best = {};
   const int sms = sm_count();
   const int k_blocks = (int)((K + kBK - 1) / kBK);
@@ -87,7 +87,8 @@ GemmPlan plan_gemm(int epi, int64_t M, int64_t N, int64_t K, int head_size, int 
     const int mi = cta2 ? mode - 2 : mode;
     for (int bn = 32; bn <= 256; bn += 32) {
       if (f_bn && bn != f_bn) continue;
-      if (epi == EPI_ROTARY && bn % head_size != 0) continue;
+      // rotary: whole heads per tile, or (NeoX) a 64-column slice of both halves of a head
+      if (epi == EPI_ROTARY && bn % head_size != 0 && !(neox && bn < head_size && bn == 64 && head_size % bn == 0)) continue;
       if (epi == EPI_SILU_MUL && bn % 64 != 0) continue;
       if (cta2 && bn % 64 != 0) continue;  // each CTA of a pair keeps bn/2 rows of B: whole 32-column chunks
       if (!f_bn && bn < 64) continue;
@@ -160,7 +161,7 @@ GemmPlan plan_gemm(int epi, int64_t M, int64_t N, int64_t K, int head_size, int 
     }
   }
   // a forced cut along K that is impossible (workspace too small, or it degenerates to whole tiles)
-  if (best.bn == 0 && tile_cfg >= 100000) return plan_gemm(epi, M, N, K, head_size, tile_cfg % 100000, ws_bytes);
+  if (best.bn == 0 && tile_cfg >= 100000) return plan_gemm(epi, M, N, K, head_size, tile_cfg % 100000, ws_bytes, neox);
   return best;
 }
 
@@ -288,8 +289,9 @@ int run_gemm_sm100(int dtype, int epi, const GemmPlan& plan, const void* x, int6
   CUtensorMap ta, tb;
   int rc = make_tmap_2d(&ta, dtype, x, g.M, g.K, ldx, 128, kBK);
   if (rc) return rc;
+  g.rot_split = (epi == EPI_ROTARY && plan.bn < g.head_size) ? 1 : 0;
   rc = make_tmap_2d(&tb, dtype, w, b_rows > 0 ? b_rows : g.N, g.K, ldw,
-                    (epi == EPI_SILU_MUL || plan.cta2) ? plan.bn / 2 : plan.bn, kBK);
+                    (epi == EPI_SILU_MUL || plan.cta2 || g.rot_split) ? plan.bn / 2 : plan.bn, kBK);
   if (rc) return rc;
   if (dtype == SB200_BF16) return dispatch_epi<__nv_bfloat16>(epi, ta, tb, g, cv, ra, s);
   if (dtype == SB200_F16) return dispatch_epi<__half>(epi, ta, tb, g, cv, ra, s);
@@ -347,7 +349,8 @@ int run_gemm_f32(float* C, int64_t ldc, const float* A, int64_t lda, const float
 using namespace sb200;
 
 extern "C" int sb200_gemm_colpar(void* out, int64_t ldo, const void* x, int64_t ldx, const void* w, int64_t ldw,
-                                 const void* bias, int64_t T, int64_t N, int64_t K, int dtype, int epilogue,
+                                 const void* bias, const void* residual, int64_t ldr, int64_t T, int64_t N, int64_t K,
+                                 int dtype, int epilogue,
                                  const sb200_rotary_args* rot, uint32_t* status, int tile_cfg, void* workspace,
                                  int64_t workspace_bytes, sb200_stream_t stream) {
   SB_CHECK_ARG(T >= 0 && N > 0 && K > 0 && T <= INT32_MAX && N <= INT32_MAX && K <= INT32_MAX,
@@ -355,6 +358,8 @@ extern "C" int sb200_gemm_colpar(void* out, int64_t ldo, const void* x, int64_t 
   if (T == 0) return SB200_OK;
   SB_CHECK_ARG(out && x && w, "gemm_colpar: null pointer");
   SB_CHECK_ARG(epilogue >= SB200_EPI_NONE && epilogue <= SB200_EPI_SILU_MUL, "gemm_colpar: bad epilogue %d", epilogue);
+  SB_CHECK_ARG(residual == nullptr || (epilogue == SB200_EPI_NONE && dtype != SB200_F32 && ldr >= N),
+               "gemm_colpar: a residual goes with the plain epilogue of the bf16 / fp16 kernel only (ldr >= N)");
   cudaStream_t s = (cudaStream_t)stream;
   if (dtype == SB200_F32) {
     SB_CHECK_ARG(epilogue == SB200_EPI_NONE, "gemm_colpar: fp32 supports only the plain epilogue (compose the "
@@ -365,6 +370,7 @@ extern "C" int sb200_gemm_colpar(void* out, int64_t ldo, const void* x, int64_t 
   GemmArgs g = {};
   g.M = (int)T; g.N = (int)N; g.K = (int)K;
   g.out = out; g.ldo = ldo; g.bias = bias; g.status = status;
+  g.residual = residual; g.ldr = ldr;
   g.head_size = 128;
   int epi = EPI_STORE;
   if (epilogue == SB200_EPI_ROTARY) {
@@ -378,6 +384,15 @@ extern "C" int sb200_gemm_colpar(void* out, int64_t ldo, const void* x, int64_t 
     SB_CHECK_ARG(aligned16(rot->cos_sin_cache), "gemm_colpar: cos_sin_cache must be 16-byte aligned");
     g.positions = rot->positions; g.cos_sin = rot->cos_sin_cache; g.head_size = rot->head_size;
     g.rot_cols = rot->rot_cols; g.is_neox = rot->is_neox;
+    if (rot->kv_cache) {
+      const int64_t kvc = (int64_t)rot->num_kv_heads * rot->head_size;
+      SB_CHECK_ARG(rot->kv_slots && rot->kv_page_size > 0 && rot->num_kv_heads > 0 && kvc <= rot->rot_cols &&
+                       rot->rot_cols + kvc <= N && aligned16(rot->kv_cache),
+                   "gemm_colpar: fused KV-cache append needs slots, a page size, and k / v column blocks of "
+                   "num_kv_heads * head_size columns at [rot_cols - that, rot_cols + that)");
+      g.kv_cache = rot->kv_cache; g.kv_slots = rot->kv_slots; g.kv_page_size = rot->kv_page_size;
+      g.kv_cols = (int)kvc; g.q_cols = rot->rot_cols - (int)kvc;
+    }
     epi = EPI_ROTARY;
   } else if (epilogue == SB200_EPI_SILU_MUL) {
     SB_CHECK_ARG(bias == nullptr, "gemm_colpar: silu_and_mul epilogue does not take a bias");
@@ -386,7 +401,8 @@ extern "C" int sb200_gemm_colpar(void* out, int64_t ldo, const void* x, int64_t 
   }
   CommView cv = {};
   ReduceArgs ra = {};
-  const GemmPlan plan = plan_gemm(epi, T, N, K, g.head_size, tile_cfg, workspace ? (size_t)workspace_bytes : 0);
+  const GemmPlan plan = plan_gemm(epi, T, N, K, g.head_size, tile_cfg, workspace ? (size_t)workspace_bytes : 0,
+                                  epi == EPI_ROTARY ? g.is_neox : 1);
   return run_gemm_sm100(dtype, epi, plan, x, ldx, w, ldw, g, workspace, cv, ra, s);
 }
 

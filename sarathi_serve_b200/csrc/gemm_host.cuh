@@ -19,7 +19,7 @@ struct GemmPlan {
   double est_clocks;
 };
 // tile_cfg: 0 = choose; else BN + 1000*MODE + 100000*S (MODE 1|2: one CTA, 3|4: CTA pairs; S >= 2: the tiles of the last partial round are cut along K so that about S units share one).  ws_bytes: split-K workspace available (0 = none).
-GemmPlan plan_gemm(int epi, int64_t M, int64_t N, int64_t K, int head_size, int tile_cfg, size_t ws_bytes);
+GemmPlan plan_gemm(int epi, int64_t M, int64_t N, int64_t K, int head_size, int tile_cfg, size_t ws_bytes, int neox = 1);
 uint32_t gemm_push_increments(const GemmPlan& p, int64_t M, int64_t lo, int64_t hi);
 int run_gemm_sm100(int dtype, int epi, const GemmPlan& plan, const void* x, int64_t ldx, const void* w, int64_t ldw,
                    GemmArgs g, void* workspace, const CommView& cv, const ReduceArgs& ra, cudaStream_t s,

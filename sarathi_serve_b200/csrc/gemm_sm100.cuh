@@ -59,12 +59,22 @@ struct GemmArgs {
   void* out;               // [M, ldo] (EPI_SILU_MUL: [M, d])
   int64_t ldo;
   const void* bias;        // [N] or null (EPI_STORE only)
+  const void* residual;    // [M, ldr] or null (EPI_STORE only): out = residual + round(acc (+ bias))
+  int64_t ldr;
   // EPI_ROTARY
   const int64_t* positions;
   const void* cos_sin;     // [max_pos, rot_dim], same dtype as the output
   int head_size;
   int rot_cols;            // columns [0, rot_cols) hold q and k heads, the rest (v) is stored as is
   int is_neox;
+  // EPI_ROTARY, optional: the k and v columns of the qkv row are ALSO stored into the paged KV cache
+  void* kv_cache;            // [pages, 2, page_size, kv_heads, head_dim] of T, or null
+  const int64_t* kv_slots;   // [M] row of the cache seen as [pages * 2 * page_size, kv_cols] for token i's key (-1: skip)
+  int kv_page_size;
+  int q_cols, kv_cols;       // output columns [q_cols, q_cols + kv_cols) are k, the next kv_cols are v
+  int rot_split;           // EPI_ROTARY with bn < head_size (NeoX only): a tile holds bn/2 columns of the first half
+                           // of a head followed by the matching bn/2 columns of its second half, so that every
+                           // rotation pair (i, i + head_size/2) sits in one accumulator
   // tiling (host-chosen)
   int mi;                  // accumulators per tile (BM = 128 * mi)
   int bn;                  // tile columns
@@ -253,6 +263,8 @@ template <typename T> struct RowCtx {
   int n0;          // first global output column of the tile (for SILU_MUL: first column of d)
   T* out_row;      // out + gm * ldo   (EPI_PUSH: the owner's partial slot row)
   const T* cs;     // rotary: cache row of this token
+  const T* res_row;  // EPI_STORE: residual + gm * ldr, or null
+  T* kv_row;       // EPI_ROTARY: this token's key row in the paged KV cache, or null
   bool vec_ok;
   float scale;     // EPI_MOE_SCATTER: routed weight of this row's slot
 };
@@ -264,13 +276,28 @@ template <typename T> struct RowCtx {
 //                  for a NeoX-rotated head only j < upH/2 does work (chunks j and j + upH/2).
 // (EPI_MOE_SCATTER uses the units of STORE.)
 template <int EPI> __device__ __forceinline__ int num_units(const GemmArgs& g) {
-  return EPI == EPI_SILU_MUL ? g.bn / 64 : g.bn / 32;
+  return (EPI == EPI_SILU_MUL || (EPI == EPI_ROTARY && g.rot_split)) ? g.bn / 64 : g.bn / 32;
+}
+// First output column of tile column block nt.  A split rotary tile (see GemmArgs::rot_split) starts at
+// column j * bn/2 of its head and continues at head_size/2 + j * bn/2.
+template <int EPI> __device__ __forceinline__ int tile_first_col(const GemmArgs& g, int nt) {
+  if (EPI == EPI_SILU_MUL) return nt * (g.bn / 2);
+  if (EPI == EPI_ROTARY && g.rot_split) {
+    const int tph = g.head_size / g.bn;  // tiles per head
+    return (nt / tph) * g.head_size + (nt % tph) * (g.bn / 2);
+  }
+  return nt * g.bn;
 }
 
 // Columns (inside the accumulator) a unit reads; returns how many chunks (0, 1 or 2).
 template <int EPI>
 __device__ __forceinline__ int unit_chunks(const GemmArgs& g, int n0, int u, int* cols) {
   if (EPI == EPI_SILU_MUL) {
+    cols[0] = u * 32;
+    cols[1] = g.bn / 2 + u * 32;
+    return 2;
+  }
+  if (EPI == EPI_ROTARY && g.rot_split) {
     cols[0] = u * 32;
     cols[1] = g.bn / 2 + u * 32;
     return 2;
@@ -290,6 +317,19 @@ __device__ __forceinline__ int unit_chunks(const GemmArgs& g, int n0, int u, int
   }
   cols[0] = u * 32;
   return 1;
+}
+
+// qkv projection with the KV-cache append fused in: the 32 final values of output columns [gn, gn + 32)
+// of this thread's token also go to the token's slot of the paged cache when they are k or v columns
+// (what flashinfer's append_paged_kv_cache does after the reference's `.contiguous()` copies,
+// attention/flashinfer_attention_wrapper.py:253-270).  Head sizes are multiples of 32, so a chunk never
+// straddles the k / v boundary.
+template <typename T>
+__device__ __forceinline__ void store_kv32(const GemmArgs& g, const RowCtx<T>& rc, int gn, const float* f) {
+  if (!rc.kv_row || gn < g.q_cols || gn >= g.q_cols + 2 * g.kv_cols) return;
+  const int c = gn - g.q_cols;
+  T* dst = c < g.kv_cols ? rc.kv_row + c : rc.kv_row + (int64_t)g.kv_page_size * g.kv_cols + (c - g.kv_cols);
+  store_row32<T>(dst, f, 32, true);
 }
 
 // Finish one unit: fetch its chunk(s) from `src`, apply the epilogue math, store.
@@ -318,6 +358,20 @@ __device__ __forceinline__ void finish_unit(const GemmArgs& g, const RowCtx<T>& 
         for (int j = 0; j < 32; ++j)
           if (gn + j < g.N) a[j] += DT<T>::to_f(bias[gn + j]);
       }
+      if (EPI == EPI_STORE && rc.res_row) {
+        // Reference: hidden_states = residual + hidden_states on the rounded projection output
+        // (models/llama.py:248,254): one more operator result of the 16-bit type.
+        if (g.N - gn >= 32 && rc.vec_ok && ((g.ldr & 7) == 0) && aligned16(g.residual)) {
+          float r[32];
+          load_row32<T>(rc.res_row + gn, r);
+#pragma unroll
+          for (int j = 0; j < 32; ++j) a[j] = rt<T>(r[j] + rt<T>(a[j]));
+        } else {
+#pragma unroll
+          for (int j = 0; j < 32; ++j)
+            if (gn + j < g.N) a[j] = rt<T>(DT<T>::to_f(rc.res_row[gn + j]) + rt<T>(a[j]));
+        }
+      }
       store_row32<T>(rc.out_row + gn, a, g.N - gn, rc.vec_ok);
     }
   } else if constexpr (EPI == EPI_SILU_MUL) {
@@ -340,23 +394,27 @@ __device__ __forceinline__ void finish_unit(const GemmArgs& g, const RowCtx<T>& 
     // Reference: F.linear output rounded to T (tensor_parallel/layers.py:278-284), then
     // rotary_embedding in T arithmetic on the q and k heads (csrc/pos_encoding_kernels.cu:8-76).
     const int gn = rc.n0 + cols[0];
-    if (nch == 2) {  // NeoX pair of chunks: x = cols[0].., y = x + head_size/2
+    if (nch == 2) {  // NeoX pair of chunks: x = global columns gn.., y = x + head_size/2
       float b[32];
       src.load32(cols[1], b);
       if (rc.row_ok && gn < g.N) {
         const int half = g.head_size / 2;
-        const int in_head = cols[0] % g.head_size;  // = j*32
-        float co[32], si[32];
-        load_row32<T>(rc.cs + in_head, co);
-        load_row32<T>(rc.cs + half + in_head, si);
+        const int in_head = gn % g.head_size;  // (whole-head tiles: = cols[0] % head_size)
+        if (gn - in_head < g.rot_cols) {  // a q or k head; the v heads of a split tile are stored as they are
+          float co[32], si[32];
+          load_row32<T>(rc.cs + in_head, co);
+          load_row32<T>(rc.cs + half + in_head, si);
 #pragma unroll
-        for (int j = 0; j < 32; ++j) {
-          const float x = rt<T>(a[j]), y = rt<T>(b[j]);
-          a[j] = rt<T>(rt<T>(x * co[j]) - rt<T>(y * si[j]));
-          b[j] = rt<T>(rt<T>(y * co[j]) + rt<T>(x * si[j]));
+          for (int j = 0; j < 32; ++j) {
+            const float x = rt<T>(a[j]), y = rt<T>(b[j]);
+            a[j] = rt<T>(rt<T>(x * co[j]) - rt<T>(y * si[j]));
+            b[j] = rt<T>(rt<T>(y * co[j]) + rt<T>(x * si[j]));
+          }
         }
         store_row32<T>(rc.out_row + gn, a, g.N - gn, rc.vec_ok);
         store_row32<T>(rc.out_row + gn + half, b, g.N - gn - half, rc.vec_ok);
+        store_kv32<T>(g, rc, gn, a);
+        store_kv32<T>(g, rc, gn + half, b);
       }
     } else if (rc.row_ok && gn < g.N) {
       const int head0 = (cols[0] / g.head_size) * g.head_size;
@@ -373,6 +431,7 @@ __device__ __forceinline__ void finish_unit(const GemmArgs& g, const RowCtx<T>& 
         }
       }
       store_row32<T>(rc.out_row + gn, a, g.N - gn, rc.vec_ok);
+      store_kv32<T>(g, rc, gn, a);
     }
   }
 }
@@ -386,6 +445,8 @@ __device__ __forceinline__ RowCtx<T> make_row_ctx(const GemmArgs& g, const CommV
   rc.row_ok = gm < g.M;
   rc.n0 = n0;
   rc.cs = nullptr;
+  rc.res_row = nullptr;
+  rc.kv_row = nullptr;
   rc.scale = 1.f;
   if constexpr (EPI == EPI_MOE_SCATTER) {
     int slot = g.num_slots;
@@ -401,8 +462,15 @@ __device__ __forceinline__ RowCtx<T> make_row_ctx(const GemmArgs& g, const CommV
   } else {
     rc.out_row = reinterpret_cast<T*>(g.out) + (size_t)gm * g.ldo;
     rc.vec_ok = ((g.ldo & 7) == 0) && aligned16(g.out);
-    if (EPI == EPI_ROTARY && rc.row_ok)
+    if (EPI == EPI_STORE && g.residual && rc.row_ok)
+      rc.res_row = reinterpret_cast<const T*>(g.residual) + (size_t)gm * g.ldr;
+    if (EPI == EPI_ROTARY && rc.row_ok) {
       rc.cs = reinterpret_cast<const T*>(g.cos_sin) + g.positions[gm] * g.head_size;
+      if (g.kv_cache) {
+        const int64_t slot = g.kv_slots[gm];
+        if (slot >= 0) rc.kv_row = reinterpret_cast<T*>(g.kv_cache) + slot * (int64_t)g.kv_cols;
+      }
+    }
   }
   return rc;
 }
@@ -516,7 +584,10 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
           if (!ptx::mbar_wait(&empty_bar[stage], phase ^ 1u, abort_flag)) { ok = false; break; }
           uint8_t* sa = stage_base + (size_t)stage * stage_bytes;
           uint8_t* sb = sa + a_bytes;
-          if (g.l2_prefetch > 0 && kb + g.l2_prefetch < sg.kb1) {
+          const bool halves = (EPI == EPI_SILU_MUL) || (EPI == EPI_ROTARY && g.rot_split);  // B tile = two row blocks
+          const int b_first = tile_first_col<EPI>(g, nt);                                  // first row of the first block
+          const int b_second = b_first + (EPI == EPI_SILU_MUL ? g.N / 2 : g.head_size / 2);  // ... of the second
+          if (g.l2_prefetch > 0 && kb + g.l2_prefetch < sg.kb1 && !(EPI == EPI_ROTARY && g.rot_split)) {
             // weights are read once: start their trip from HBM to L2 a few stages early
             const int pk = (kb + g.l2_prefetch) * kBK;
             if (CTA2) {
@@ -534,8 +605,8 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
 #pragma unroll
             for (int a = 0; a < MI; ++a)  // accumulator a covers tile rows [256a, 256a+256): this CTA's half of them
               ptx::tma_load_2d_pair(sa + a * (128 * kBK * 2), &tmap_a, bar, kb * kBK, mt * BM + a * 256 + (int)cta_rank * 128);
-            if (EPI == EPI_SILU_MUL)  // even CTA: gate rows, odd CTA: the matching up rows
-              ptx::tma_load_2d_pair(sb, &tmap_b, bar, kb * kBK, b_row0 + (int)cta_rank * (g.N / 2) + nt * (BN / 2));
+            if (halves)  // even CTA: gate rows (first half of the head), odd CTA: the matching up rows (second half)
+              ptx::tma_load_2d_pair(sb, &tmap_b, bar, kb * kBK, b_row0 + (cta_rank ? b_second : b_first));
             else
               ptx::tma_load_2d_pair(sb, &tmap_b, bar, kb * kBK, b_row0 + nt * BN + (int)cta_rank * (BN / 2));
           } else {
@@ -543,10 +614,11 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
 #pragma unroll
             for (int a = 0; a < MI; ++a)
               ptx::tma_load_2d(sa + a * (128 * kBK * 2), &tmap_a, &full_bar[stage], kb * kBK, mt * BM + a * 128);
-            if (EPI == EPI_SILU_MUL) {
+            if (halves) {
               // B tile = BN/2 rows of the gate shard followed by the matching BN/2 rows of the up shard
-              ptx::tma_load_2d(sb, &tmap_b, &full_bar[stage], kb * kBK, b_row0 + nt * (BN / 2));
-              ptx::tma_load_2d(sb + (BN / 2) * (kBK * 2), &tmap_b, &full_bar[stage], kb * kBK, b_row0 + g.N / 2 + nt * (BN / 2));
+              // (rotary: of the first and of the second half of the head)
+              ptx::tma_load_2d(sb, &tmap_b, &full_bar[stage], kb * kBK, b_row0 + b_first);
+              ptx::tma_load_2d(sb + (BN / 2) * (kBK * 2), &tmap_b, &full_bar[stage], kb * kBK, b_row0 + b_second);
             } else {
               ptx::tma_load_2d(sb, &tmap_b, &full_bar[stage], kb * kBK, b_row0 + nt * BN);
             }
@@ -623,7 +695,7 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
       if (!ok) break;  // warp-uniform: no lane is left behind in an aligned tcgen05.ld
       ptx::tc_fence_after();
 
-      const int n0 = nt * (EPI == EPI_SILU_MUL ? BN / 2 : BN);
+      const int n0 = tile_first_col<EPI>(g, nt);
       const RowCtx<T> rc = make_row_ctx<T, EPI>(g, comm, red, mt * BM + row_in_tile, n0);
       const TmemSource tsrc{tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)((buf * MI + a0) * BN)};
       if (S == 1) {
@@ -681,7 +753,7 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
       }
       arrived = __shfl_sync(0xffffffffu, arrived, 0);
       if (!arrived) { ok = false; break; }
-      const int n0 = nt * (EPI == EPI_SILU_MUL ? BN / 2 : BN);
+      const int n0 = tile_first_col<EPI>(g, nt);
       const RowCtx<T> rc = make_row_ctx<T, EPI>(g, comm, red, mt * BM + row_in_tile, n0);
       {
         const int my_part = sg.part_slot - sg.first_slot;

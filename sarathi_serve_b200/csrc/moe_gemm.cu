@@ -35,7 +35,7 @@ moe_gather_kernel(T* __restrict__ out, const T* __restrict__ x, const int32_t* _
 
 template <typename T>
 __global__ void __launch_bounds__(256)
-moe_sum_kernel(T* __restrict__ out, const T* __restrict__ in3, int64_t T_, int k, int H) {
+moe_sum_kernel(T* __restrict__ out, const T* __restrict__ in3, const T* __restrict__ residual, int64_t T_, int k, int H) {
   constexpr int N = Vec16<T>::N;
   const int nvec = H / N;
   const int64_t total = T_ * nvec, stride = (int64_t)gridDim.x * blockDim.x;
@@ -51,8 +51,14 @@ moe_sum_kernel(T* __restrict__ out, const T* __restrict__ in3, int64_t T_, int k
       for (int j = 0; j < N; ++j) acc[j] += DT<T>::to_f(a.v[j]);
     }
     Vec16<T> o;
+    if (residual) {  // the layer's `residual + hidden_states` on the rounded sum (models/mixtral.py:257)
+      const Vec16<T> r = ld16(residual + t * H + (int64_t)v * N);
 #pragma unroll
-    for (int j = 0; j < N; ++j) o.v[j] = DT<T>::from_f(acc[j]);
+      for (int j = 0; j < N; ++j) o.v[j] = DT<T>::from_f(DT<T>::to_f(r.v[j]) + rt<T>(acc[j]));
+    } else {
+#pragma unroll
+      for (int j = 0; j < N; ++j) o.v[j] = DT<T>::from_f(acc[j]);
+    }
     st16(out + t * H + (int64_t)v * N, o);
   }
 }
@@ -131,14 +137,16 @@ extern "C" int sb200_moe_gemm2(void* out3, const void* act, const void* w2, cons
                   H, d, dtype, status, tile_cfg, (cudaStream_t)stream);
 }
 
-extern "C" int sb200_moe_sum(void* out, const void* in3, int64_t T, int top_k, int64_t H, int dtype,
-                             sb200_stream_t stream) {
+extern "C" int sb200_moe_sum(void* out, const void* in3, const void* residual, int64_t T, int top_k, int64_t H,
+                             int dtype, sb200_stream_t stream) {
   SB_CHECK_ARG(out && in3 && T >= 0 && top_k > 0 && H > 0, "moe_sum: bad arguments");
-  SB_CHECK_ARG((H * dtype_size(dtype)) % 16 == 0 && aligned16(out) && aligned16(in3), "moe_sum: rows must be 16-byte multiples");
+  SB_CHECK_ARG((H * dtype_size(dtype)) % 16 == 0 && aligned16(out) && aligned16(in3) &&
+                   (!residual || aligned16(residual)), "moe_sum: rows must be 16-byte multiples");
   if (T == 0) return SB200_OK;
   cudaStream_t s = (cudaStream_t)stream;
   const int grid = grid_1d(T * (H / (16 / (int64_t)dtype_size(dtype))));
-  SB_DISPATCH_FLOAT(dtype, (moe_sum_kernel<scalar_t><<<grid, 256, 0, s>>>((scalar_t*)out, (const scalar_t*)in3, T, top_k, (int)H)));
+  SB_DISPATCH_FLOAT(dtype, (moe_sum_kernel<scalar_t><<<grid, 256, 0, s>>>((scalar_t*)out, (const scalar_t*)in3,
+                                                                         (const scalar_t*)residual, T, top_k, (int)H)));
   SB_CHECK_LAUNCH("moe_sum_kernel");
   return SB200_OK;
 }

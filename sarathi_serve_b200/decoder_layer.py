@@ -25,6 +25,20 @@ from .mappings import gather_from_tensor_model_parallel_region
 from .tp_layers import ColumnParallelLinear, ReplicatedLinear, RowParallelLinear, VocabParallelEmbedding
 
 
+def fused_kv_append(attention_backend_wrapper, layer_cache_idx: int):
+    """An attention wrapper that keeps a paged KV cache of layout [pages, 2, page_size, kv_heads, head_dim] can
+    have this step's keys and values stored by the qkv GEMM's epilogue instead of appending them itself
+    (the reference's wrapper appends inside ``forward``:
+    attention/flashinfer_attention_wrapper.py:253-270).  It opts in by defining
+
+        fused_kv_append(layer_cache_idx) -> (paged_kv_cache, kv_slots) | None
+
+    with ``kv_slots`` from ``kv_cache_ops.slots`` (computed once per step in its ``begin_forward``); its
+    ``forward`` must then not append again.  Wrappers without that method are used unchanged."""
+    hook = getattr(attention_backend_wrapper, "fused_kv_append", None)
+    return hook(layer_cache_idx) if hook is not None else None
+
+
 class LlamaMLP(nn.Module):
     def __init__(self, hidden_size: int, intermediate_size: int, hidden_act: str,
                  layer_id: Optional[int] = None) -> None:
@@ -75,9 +89,12 @@ class LlamaAttention(nn.Module):
                                    max_position=self.max_position_embeddings, base=self.rope_theta,
                                    is_neox_style=True, rope_scaling=rope_scaling)
 
-    def qkv_rotary(self, positions: torch.Tensor, hidden_states: torch.Tensor):
-        """qkv projection with the rotary embedding fused into the GEMM epilogue; returns q, k, v views."""
-        qkv = self.qkv_proj.forward_rotary(hidden_states, positions, self.rotary_emb, self.q_size + self.kv_size)
+    def qkv_rotary(self, positions: torch.Tensor, hidden_states: torch.Tensor, kv_append=None):
+        """qkv projection with the rotary embedding fused into the GEMM epilogue; returns q, k, v views.
+        ``kv_append``: optional (paged_kv_cache, kv_slots) -- the rotated keys and the values are then also
+        stored into the paged cache from the same epilogue (see ``fused_kv_append``)."""
+        qkv = self.qkv_proj.forward_rotary(hidden_states, positions, self.rotary_emb, self.q_size + self.kv_size,
+                                           kv_append=kv_append, num_kv_heads=self.num_kv_heads)
         return qkv.split([self.q_size, self.kv_size, self.kv_size], dim=-1)
 
     def forward(self, positions: torch.Tensor, hidden_states: torch.Tensor, layer_cache_idx: int,
@@ -123,7 +140,7 @@ class LlamaDecoderLayer(nn.Module):
     def _attn_mlp(self, positions, normed, residual, layer_cache_idx, attn, next_norm_weight, next_eps, out=None,
                   resid_everywhere=True):
         sa = self.self_attn
-        q, k, v = sa.qkv_rotary(positions, normed)
+        q, k, v = sa.qkv_rotary(positions, normed, fused_kv_append(attn, layer_cache_idx))
         attn_out = attn.forward(q, k, v, layer_cache_idx, sa.scaling, sa.layer_id)
         # the mid-layer residual is only read by the down projection's tail, which touches the rows this
         # rank owns: they need not be gathered on every rank
@@ -241,6 +258,12 @@ class MixtralMoE(nn.Module):
         final_hidden_states = self.experts(hidden_states, router_logits)
         return final_hidden_states.view(num_tokens, hidden_size)
 
+    def forward_fused(self, hidden_states: torch.Tensor, residual: torch.Tensor) -> torch.Tensor:
+        """``residual + moe(hidden_states)`` in a new tensor; ``hidden_states`` is left as it is (it may be a
+        view into the communication context)."""
+        router_logits, _ = self.gate(hidden_states)
+        return self.experts.forward_fused(hidden_states, router_logits, residual)
+
 
 class MixtralDecoderLayer(nn.Module):
     """Mixtral decoder layer (mixtral.py:194-258): Llama-style attention block, MoE feed-forward.
@@ -265,10 +288,10 @@ class MixtralDecoderLayer(nn.Module):
                 attention_backend_wrapper) -> torch.Tensor:
         sa = self.self_attn
         normed = self.input_layernorm(hidden_states)
-        q, k, v = sa.qkv_rotary(positions, normed)
+        q, k, v = sa.qkv_rotary(positions, normed, fused_kv_append(attention_backend_wrapper, layer_cache_idx))
         attn_out = attention_backend_wrapper.forward(q, k, v, layer_cache_idx, sa.scaling, sa.layer_id)
         # o_proj + all-reduce + residual add + post-attention RMSNorm in one kernel
         h, resid = sa.o_proj.forward_fused(attn_out, hidden_states, self.post_attention_layernorm.weight.data,
                                            self.post_attention_layernorm.variance_epsilon)
-        moe_out = self.block_sparse_moe(h.clone())  # the experts overwrite their input; `h` lives in the comm heap
-        return resid + moe_out
+        # experts + sum over the routed slots + all-reduce + the layer's residual add, without touching `h`
+        return self.block_sparse_moe.forward_fused(h, resid)

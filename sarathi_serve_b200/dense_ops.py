@@ -89,10 +89,11 @@ def _rows_2d(x: torch.Tensor, what: str) -> torch.Tensor:
 
 
 def linear(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor] = None,
-           out: Optional[torch.Tensor] = None, tile_n: int = 0) -> torch.Tensor:
+           out: Optional[torch.Tensor] = None, tile_n: int = 0, residual: Optional[torch.Tensor] = None) -> torch.Tensor:
     """y[T, N] = x[T, K] @ weight[N, K]^T (+ bias): F.linear semantics
-    (reference call sites: tensor_parallel/layers.py:284,423,518)."""
-    N.require_cuda(x, weight, bias)
+    (reference call sites: tensor_parallel/layers.py:284,423,518).  ``residual`` [T, N] (bf16 / fp16 only):
+    y = residual + round(x @ weight^T (+ bias)), the add of models/llama.py:248,254 in the GEMM epilogue."""
+    N.require_cuda(x, weight, bias, residual)
     lead = x.shape[:-1]
     x2 = _rows_2d(x, "linear input")
     if weight.dim() != 2 or weight.stride(1) != 1 or weight.shape[1] != x2.shape[1]:
@@ -107,8 +108,15 @@ def linear(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor] =
         raise RuntimeError("linear: bad out tensor")
     if bias is not None and not bias.is_contiguous():
         bias = bias.contiguous()
+    ldr = 0
+    if residual is not None:
+        residual = _rows_2d(residual, "linear residual")
+        if residual.shape != (T, Nn) or residual.dtype != x2.dtype:
+            raise RuntimeError("linear: residual must be [T, N] of the activation dtype")
+        ldr = residual.stride(0)
     N.check(N.lib().sb200_gemm_colpar(N.ptr(out), out.stride(0), N.ptr(x2), x2.stride(0), N.ptr(weight),
-                                      weight.stride(0), N.ptr(bias), T, Nn, K, N.dtype_id(x2), EPI_NONE, None,
+                                      weight.stride(0), N.ptr(bias), N.ptr(residual), ldr, T, Nn, K, N.dtype_id(x2),
+                                      EPI_NONE, None,
                                       N.ptr(status_word(x2.device)), tile_n, *_ws(x2), N.stream_ptr()), "gemm_colpar")
     return out.view(*lead, Nn) if len(lead) != 1 else out
 
@@ -119,11 +127,14 @@ def fused_rotary_supported(x: torch.Tensor, head_size: int, rot_dim: int) -> boo
 
 def linear_rotary(x: torch.Tensor, weight: torch.Tensor, positions: torch.Tensor, cos_sin_cache: torch.Tensor,
                   head_size: int, rot_cols: int, is_neox: bool, out: Optional[torch.Tensor] = None,
-                  tile_n: int = 0) -> torch.Tensor:
+                  tile_n: int = 0, kv_cache: Optional[torch.Tensor] = None, kv_slots: Optional[torch.Tensor] = None,
+                  num_kv_heads: int = 0) -> torch.Tensor:
     """qkv[T, N] = x @ weight^T with rotary_embedding applied to columns [0, rot_cols)
     (the q and k heads) in the GEMM epilogue -- the qkv_proj + rotary_emb pair of
-    models/llama.py:175-177 in one kernel."""
-    N.require_cuda(x, weight, positions, cos_sin_cache)
+    models/llama.py:175-177 in one kernel.  With ``kv_cache`` ([pages, 2, page_size, num_kv_heads, head_size])
+    and ``kv_slots`` (kv_cache_ops.slots(...)) the rotated keys and the values are also appended to the paged
+    cache from the epilogue."""
+    N.require_cuda(x, weight, positions, cos_sin_cache, kv_cache, kv_slots)
     x2 = _rows_2d(x, "linear_rotary input")
     T, K = x2.shape
     Nn = weight.shape[0]
@@ -133,10 +144,19 @@ def linear_rotary(x: torch.Tensor, weight: torch.Tensor, positions: torch.Tensor
         raise RuntimeError("linear_rotary: cos_sin_cache must be contiguous and share the activation dtype")
     if out is None:
         out = torch.empty(T, Nn, dtype=x2.dtype, device=x2.device)
+    page = 0
+    if kv_cache is not None:
+        if (kv_slots is None or kv_slots.dtype != torch.int64 or kv_slots.numel() != T or not kv_slots.is_contiguous()
+                or kv_cache.dim() != 5 or kv_cache.shape[1] != 2 or tuple(kv_cache.shape[3:]) != (num_kv_heads, head_size)
+                or kv_cache.dtype != x2.dtype or not kv_cache.is_contiguous()):
+            raise RuntimeError("linear_rotary: kv_cache must be a contiguous [pages, 2, page_size, num_kv_heads, head_size] "
+                               "tensor of the activation dtype and kv_slots a contiguous int64 [T] tensor")
+        page = kv_cache.shape[2]
     rot = N.RotaryArgs(N.ptr(positions), N.ptr(cos_sin_cache), head_size, cos_sin_cache.shape[1], rot_cols,
-                       1 if is_neox else 0)
+                       1 if is_neox else 0, N.ptr(kv_cache), N.ptr(kv_slots) if kv_cache is not None else None, page,
+                       num_kv_heads)
     N.check(N.lib().sb200_gemm_colpar(N.ptr(out), out.stride(0), N.ptr(x2), x2.stride(0), N.ptr(weight),
-                                      weight.stride(0), None, T, Nn, K, N.dtype_id(x2), EPI_ROTARY,
+                                      weight.stride(0), None, None, 0, T, Nn, K, N.dtype_id(x2), EPI_ROTARY,
                                       ctypes.byref(rot), N.ptr(status_word(x2.device)), tile_n, *_ws(x2),
                                       N.stream_ptr()),
             "gemm_colpar[rotary]")
@@ -154,7 +174,7 @@ def linear_silu_mul(x: torch.Tensor, weight: torch.Tensor, out: Optional[torch.T
     if out is None:
         out = torch.empty(T, Nn // 2, dtype=x2.dtype, device=x2.device)
     N.check(N.lib().sb200_gemm_colpar(N.ptr(out), out.stride(0), N.ptr(x2), x2.stride(0), N.ptr(weight),
-                                      weight.stride(0), None, T, Nn, K, N.dtype_id(x2), EPI_SILU_MUL, None,
+                                      weight.stride(0), None, None, 0, T, Nn, K, N.dtype_id(x2), EPI_SILU_MUL, None,
                                       N.ptr(status_word(x2.device)), tile_n, *_ws(x2), N.stream_ptr()),
             "gemm_colpar[silu_mul]")
     return out

@@ -101,7 +101,7 @@ def fused_experts(hidden_states: torch.Tensor, w1: torch.Tensor, w2: torch.Tenso
     if T == 0:
         return out
     out3 = _expert_slots(hidden_states, w1, w2, topk_weights.contiguous(), topk_ids.contiguous())
-    N.check(N.lib().sb200_moe_sum(N.ptr(out), N.ptr(out3), T, topk_ids.shape[1], out.shape[1], N.dtype_id(out),
+    N.check(N.lib().sb200_moe_sum(N.ptr(out), N.ptr(out3), None, T, topk_ids.shape[1], out.shape[1], N.dtype_id(out),
                                   N.stream_ptr()), "moe_sum")
     return out
 
@@ -166,17 +166,32 @@ class FusedMoE(torch.nn.Module):
         """Overwrites and returns ``hidden_states`` (the reference runs the experts in place too)."""
         if not (self.reduce_results and self.world_size > 1):
             return self.apply_weights(hidden_states, router_logits)
+        return self.forward_fused(hidden_states, router_logits, None, out=hidden_states)
+
+    def forward_fused(self, hidden_states: torch.Tensor, router_logits: torch.Tensor,
+                      residual: Optional[torch.Tensor], out: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """``residual + experts(hidden_states)`` (just the experts' output when ``residual`` is None) written to
+        ``out`` (a new tensor by default; ``hidden_states`` itself is allowed): the sum over the k routed slots,
+        the all-reduce over the tensor-parallel ranks and the decoder layer's residual add
+        (models/mixtral.py:257) happen in one kernel.  ``hidden_states`` is not modified unless it is ``out``."""
         if self.use_grouped_topk:
             raise NotImplementedError("grouped_topk (DeepSeek-V2 routing) is outside this path")
         T, H = hidden_states.shape
+        if out is None:
+            out = torch.empty_like(hidden_states)
         if T == 0:
-            return hidden_states
+            return out
         topk_weights, topk_ids = fused_topk(hidden_states, router_logits, self.top_k, self.renormalize)
         out3 = _expert_slots(hidden_states, self.w13_weight, self.w2_weight, topk_weights, topk_ids, ids_in_range=True)
-        comm = ps.get_tensor_model_parallel_comm()
-        op = ctypes.c_void_p()
-        # sum over the k slots fused into the push of the all-reduce; result written over the input
-        N.check(N.lib().sb200_moe_sum_all_reduce(comm._h, N.ptr(out3), T, self.top_k, H, N.dtype_id(out3),
-                                                 N.ptr(hidden_states), N.stream_ptr(), ctypes.byref(op)),
-                "moe_sum_all_reduce")
-        return hidden_states
+        if self.reduce_results and self.world_size > 1:
+            comm = ps.get_tensor_model_parallel_comm()
+            comm._usable()
+            op = ctypes.c_void_p()
+            # sum over the k slots fused into the push of the all-reduce
+            N.check(N.lib().sb200_moe_sum_all_reduce(comm._h, N.ptr(out3), N.ptr(residual), T, self.top_k, H,
+                                                     N.dtype_id(out3), N.ptr(out), N.stream_ptr(), ctypes.byref(op)),
+                    "moe_sum_all_reduce")
+        else:
+            N.check(N.lib().sb200_moe_sum(N.ptr(out), N.ptr(out3), N.ptr(residual), T, self.top_k, H, N.dtype_id(out3),
+                                          N.stream_ptr()), "moe_sum")
+        return out

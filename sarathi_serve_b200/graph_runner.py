@@ -29,11 +29,23 @@ class LayerGraph:
     With ``host_io=True`` the graph also owns pinned host buffers (``host_positions``,
     ``host_hidden_states``, ``host_output``) and the copies between them and the device are nodes of
     the graph: a step is then ONE graph launch -- fill the host inputs, ``replay_host_io()``,
-    synchronise, read ``host_output`` -- which matters when several ranks have to stay in step."""
+    synchronise, read ``host_output`` -- which matters when several ranks have to stay in step.
+
+    ``shard_host_io=True`` (with ``host_io``, tensor-parallel size > 1): the hidden states cross PCIe once
+    per node instead of once per rank.  Rank r's host buffers hold only the token rows
+    [r * ceil(T/tp), (r+1) * ceil(T/tp)) -- ``row_range`` -- of the input and of the output; the graph
+    uploads those rows, assembles the full [T, H] input on every rank with an all-gather over NVLink
+    (``TPComm.all_gather_rows``), runs the layer and downloads this rank's rows of the result.  (The
+    reference hands every worker the full batch: model_runner.py:67-117.)
+
+    ``poll_status`` (default on): every replay also copies the device status words (bounded waits that ran
+    out in a collective or in a GEMM pipeline) to pinned host memory, and the NEXT call raises if they were
+    set -- errors surface one step late and without a synchronisation, like the asynchronous device errors
+    of the reference's ops."""
 
     def __init__(self, layer: torch.nn.Module, num_tokens: int, attention_backend_wrapper, *, layer_cache_idx: int = 0,
                  dtype: Optional[torch.dtype] = None, device: Optional[torch.device] = None, warmup: int = 2,
-                 host_io: bool = False):
+                 host_io: bool = False, shard_host_io: bool = False, poll_status: bool = True):
         p = next(layer.parameters())
         self.device = device or p.device
         self.dtype = dtype or p.dtype
@@ -45,33 +57,55 @@ class LayerGraph:
         self.positions = torch.zeros(self.num_tokens, dtype=torch.int64, device=self.device)
         self.hidden_states = torch.zeros(self.num_tokens, hidden, dtype=self.dtype, device=self.device)
         self.host_io = bool(host_io)
+        self.poll_status = bool(poll_status)
+        world = ps.get_tensor_model_parallel_world_size()
+        self.shard_host_io = bool(shard_host_io) and self.host_io and world > 1
+        self.row_range = (0, self.num_tokens)
+        if self.shard_host_io:
+            rpr = -(-self.num_tokens // world)
+            lo = min(self.num_tokens, ps.get_tensor_model_parallel_rank() * rpr)
+            self.row_range = (lo, min(self.num_tokens, lo + rpr))
+        lo, hi = self.row_range
         if self.host_io:
             self.host_positions = torch.zeros(self.num_tokens, dtype=torch.int64).pin_memory()
-            self.host_hidden_states = torch.zeros(self.num_tokens, hidden, dtype=self.dtype).pin_memory()
-            self.host_output = torch.zeros(self.num_tokens, hidden, dtype=self.dtype).pin_memory()
+            self.host_hidden_states = torch.zeros(hi - lo, hidden, dtype=self.dtype).pin_memory()
+            self.host_output = torch.zeros(hi - lo, hidden, dtype=self.dtype).pin_memory()
+        if self.shard_host_io:
+            self._rows = torch.zeros(hi - lo, hidden, dtype=self.dtype, device=self.device)
+            self._comm_io = ps.get_tensor_model_parallel_comm()
         self.stream = torch.cuda.Stream(device=self.device)
         self.stream.wait_stream(torch.cuda.current_stream(self.device))
         with torch.cuda.stream(self.stream), torch.inference_mode():
             for _ in range(max(1, warmup)):  # first calls create the communication context, tile plans, caches
-                layer(self.positions, self.hidden_states, layer_cache_idx, attention_backend_wrapper)
+                layer(self.positions, self._gathered() if self.shard_host_io else self.hidden_states,
+                      layer_cache_idx, attention_backend_wrapper)
             self.stream.synchronize()
             self.graph = torch.cuda.CUDAGraph()
             with torch.cuda.graph(self.graph, stream=self.stream):
                 if self.host_io:
                     self.positions.copy_(self.host_positions, non_blocking=True)
-                    self.hidden_states.copy_(self.host_hidden_states, non_blocking=True)
-                self.output = layer(self.positions, self.hidden_states, layer_cache_idx, attention_backend_wrapper)
+                    (self._rows if self.shard_host_io else self.hidden_states).copy_(self.host_hidden_states,
+                                                                                    non_blocking=True)
+                hidden = self._gathered() if self.shard_host_io else self.hidden_states
+                self.output = layer(self.positions, hidden, layer_cache_idx, attention_backend_wrapper)
                 if self.host_io:
-                    self.host_output.copy_(self.output, non_blocking=True)
+                    self.host_output.copy_(self.output[lo:hi], non_blocking=True)
                 # the device status words (bounded waits that ran out) travel to pinned host memory with every
                 # replay; the NEXT call looks at them before it launches, without a synchronisation
-                self._comm = ps._TP_COMM
+                self._comm = ps._TP_COMM if poll_status else None
                 if self._comm is not None:
                     self._comm.enqueue_status_read()
-                dense_ops.enqueue_status_read(self.device)
+                if poll_status:
+                    dense_ops.enqueue_status_read(self.device)
         torch.cuda.current_stream(self.device).wait_stream(self.stream)
 
+    def _gathered(self) -> torch.Tensor:
+        """Full [T, H] hidden states assembled from every rank's rows (a view into the communication heap)."""
+        return self._comm_io.all_gather_rows(self._rows, self.num_tokens)
+
     def _raise_if_an_earlier_step_failed(self) -> None:
+        if not self.poll_status:
+            return
         if self._comm is not None:
             self._comm.raise_if_flagged()
         dense_ops.raise_if_flagged(self.device)

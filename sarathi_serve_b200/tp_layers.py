@@ -117,17 +117,26 @@ class ColumnParallelLinear(torch.nn.Module):
         return output, (self.bias if self.skip_bias_add else None)
 
     # -- fused variants (no bias) ------------------------------------------
-    def forward_rotary(self, input_: torch.Tensor, positions: torch.Tensor, rotary_emb, rot_cols: int) -> torch.Tensor:
-        """qkv projection with ``rotary_emb`` applied to output columns [0, rot_cols)."""
+    def forward_rotary(self, input_: torch.Tensor, positions: torch.Tensor, rotary_emb, rot_cols: int,
+                       kv_append=None, num_kv_heads: int = 0) -> torch.Tensor:
+        """qkv projection with ``rotary_emb`` applied to output columns [0, rot_cols).  ``kv_append`` =
+        (paged_kv_cache, kv_slots): the k columns (the last ``num_kv_heads`` heads below rot_cols) and the v
+        columns are also stored into the paged KV cache."""
         assert self.bias is None and not self.gather_output
+        cache, slots = kv_append if kv_append is not None else (None, None)
         if dense_ops.fused_rotary_supported(input_, rotary_emb.head_size, rotary_emb.rotary_dim):
             return dense_ops.linear_rotary(input_, self.weight, positions, rotary_emb.cos_sin_cache,
                                            rotary_emb.head_size, rot_cols, rotary_emb.is_neox_style,
-                                           tile_n=self._cfg("rotary", input_))
+                                           tile_n=self._cfg("rotary", input_), kv_cache=cache, kv_slots=slots,
+                                           num_kv_heads=num_kv_heads)
         qkv = dense_ops.linear(input_, self.weight)
         n_rot_heads = rot_cols // rotary_emb.head_size
         # one call over q|k as a single strided "query" view; no separate key tensor
         rotary_emb.rotate_inplace(positions, qkv[:, :rot_cols], n_rot_heads)
+        if cache is not None:  # fp32 (or an unsupported head size): the append runs as its own kernel
+            from . import kv_cache_ops
+            kvc = num_kv_heads * rotary_emb.head_size
+            kv_cache_ops.append_rows(cache, qkv[:, rot_cols - kvc:rot_cols], qkv[:, rot_cols:rot_cols + kvc], slots)
         return qkv
 
     def forward_silu_mul(self, input_: torch.Tensor) -> torch.Tensor:
@@ -226,11 +235,13 @@ class RowParallelLinear(torch.nn.Module):
             # Nothing to exchange: the plain GEMM followed by the one-pass add (+ RMSNorm) kernel is faster
             # than the in-kernel tail, whose rows have to wait for every column tile of the GEMM.
             from . import layernorm_ops
-            prod = dense_ops.linear(input_, self.weight, add_bias,
-                                    tile_n=dense_ops.tuned_cfg("store", input_.shape[0], self.weight.shape[0],
-                                                               self.weight.shape[1], input_.dtype))
+            cfg = dense_ops.tuned_cfg("store", input_.shape[0], self.weight.shape[0], self.weight.shape[1], input_.dtype)
             if norm_weight is None:
-                return torch.add(residual, prod, out=out), None
+                if input_.dtype == torch.float32:
+                    return torch.add(residual, dense_ops.linear(input_, self.weight, add_bias), out=out), None
+                # the residual add rides in the GEMM epilogue
+                return dense_ops.linear(input_, self.weight, add_bias, out=out, tile_n=cfg, residual=residual), None
+            prod = dense_ops.linear(input_, self.weight, add_bias, tile_n=cfg)
             y = out if out is not None else torch.empty_like(prod)
             z = resid_out if resid_out is not None else torch.empty_like(prod)
             layernorm_ops.fused_add_rms_norm(y, z, prod, residual, norm_weight, eps)

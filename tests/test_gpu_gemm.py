@@ -82,6 +82,30 @@ def test_linear(dtype, tile_n, T, N, K):
 
 
 @pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("tile_n", [0, 128, 3256, 203128, 2064])
+@pytest.mark.parametrize("T,N,K", [(512, 4096, 512), (65, 200, 264), (300, 1000, 1000), (1, 256, 512)])
+def test_linear_with_residual_in_the_epilogue(dtype, tile_n, T, N, K):
+    """out = residual + round(x w^T + b): the reference's `hidden_states = residual + hidden_states` after a
+    row-parallel projection (models/llama.py:248,254) fused into the plain GEMM (what runs at TP = 1)."""
+    from oracle import tp_layer_oracle as O
+    from sarathi_serve_b200 import dense_ops
+    if tile_n // 100000 > (K + 63) // 64:
+        pytest.skip("more splits than k-blocks")
+    x, w = _rand((T, K), dtype, T + N + K), _rand((N, K), dtype, 7 * N + K, 0.05)
+    b, r = _rand((N,), dtype, 3), _rand((T, N), dtype, 4)
+    ref = r + O.linear(x.float(), w.float(), b.float()).to(dtype)
+    out = dense_ops.linear(x.cuda(), w.cuda(), b.cuda(), tile_n=tile_n, residual=r.cuda())
+    _check_status()
+    assert rel_err(out.float(), ref.float()) <= GEMM_TOL[dtype]
+    # strided residual view and a caller-provided output
+    big = torch.zeros(T, N + 64, dtype=dtype, device="cuda")
+    big[:, 32:32 + N] = r.cuda()
+    out2 = torch.empty(T, N, dtype=dtype, device="cuda")
+    dense_ops.linear(x.cuda(), w.cuda(), b.cuda(), out=out2, tile_n=tile_n, residual=big[:, 32:32 + N])
+    assert torch.equal(out2, out)
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
 def test_linear_strided_operands(dtype):
     """A and the output may be row-strided views (q view of the fused qkv buffer feeding o_proj)."""
     from sarathi_serve_b200 import dense_ops
@@ -106,7 +130,10 @@ def test_linear_rejects_misaligned_stride():
 
 @pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
 @pytest.mark.parametrize("neox", [True, False])
-@pytest.mark.parametrize("tile_n", [0, 256, 2256, 401256, 302256, 3256, 303256, 4256, 204128])
+@pytest.mark.parametrize("tile_n", [0, 256, 2256, 401256, 302256, 3256, 303256, 4256, 204128,
+                                    # 64-column tiles: for NeoX heads wider than 64 a tile holds 32 + 32 columns of
+                                    # the two halves of a head, so that every rotation pair sits in one accumulator
+                                    64, 2064, 3064, 4064, 303064, 600064])
 @pytest.mark.parametrize("T,nq,nkv,hd,K", [(512, 4, 1, 128, 4096), (288, 8, 2, 64, 1024), (65, 2, 2, 128, 512),
                                            (7, 1, 1, 256, 256)])
 def test_linear_rotary(dtype, neox, tile_n, T, nq, nkv, hd, K):
@@ -116,7 +143,8 @@ def test_linear_rotary(dtype, neox, tile_n, T, nq, nkv, hd, K):
     g = torch.Generator().manual_seed(5)
     pos = torch.randint(0, 2048, (T,), generator=g, dtype=torch.int64)
     cache = O.cos_sin_cache(hd, hd, 2048, 10000.0, dtype)
-    if tile_n // 100000 > (K + 63) // 64 or (tile_n and (tile_n % 1000) % hd):
+    split_head = neox and tile_n % 1000 == 64 and hd > 64
+    if tile_n // 100000 > (K + 63) // 64 or (tile_n and (tile_n % 1000) % hd and not split_head):
         pytest.skip("tile configuration does not fit this case")
     out = dense_ops.linear_rotary(x.cuda(), w.cuda(), pos.cuda(), cache.cuda(), hd, (nq + nkv) * hd, neox,
                                   tile_n=tile_n)
@@ -155,3 +183,16 @@ def test_gemm_linearity_full_size():
     y2 = dense_ops.linear(x * 4, w)
     _check_status()
     assert torch.equal(y1 * 4, y2)
+
+
+def test_mma_rate_diagnostic_runs_and_orders_the_two_modes():
+    """The planner's two constants, re-measured: a CTA pair completes a 256-row MMA of N = 128 in fewer clocks than
+    one CTA needs for its 128-row MMA, and N = 256 on a pair takes about twice as long as N = 128."""
+    from sarathi_serve_b200 import mma_rate
+    one = mma_rate.measure(False, 128, iters=256)
+    pair128 = mma_rate.measure(True, 128, iters=256)
+    pair256 = mma_rate.measure(True, 256, iters=256)
+    for r in (one, pair128, pair256):
+        assert 8 < r["clk_per_mma_complete"] < 2000, r
+    assert pair128["clk_per_mma_complete"] < one["clk_per_mma_complete"]
+    assert 1.5 < pair256["clk_per_mma_complete"] / pair128["clk_per_mma_complete"] < 2.5

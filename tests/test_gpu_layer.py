@@ -179,3 +179,86 @@ def test_model_stack_embedding_layers_norm_logits(tp1):
     assert rel_err(hidden, ref_hidden) <= TOL[case.dtype] * 1.5
     assert logits.shape == (case.num_tokens, 1000)
     assert rel_err(logits, O.linear(ref_hidden, head)[:, :1000]) <= TOL[case.dtype] * 1.5
+
+
+def test_model_graph_runner_whole_stack_per_batch_size_bucket(tp1):
+    """prepare_inputs lays a mixed batch out as the reference does (prefill chunks, then decodes, zero padding to
+    a multiple of 8); ModelGraphRunner captures the whole stack (embedding, two layers, final norm) once per
+    padded size and its replays equal the eager model on the same padded batch."""
+    from sarathi_serve_b200.decoder_layer import LlamaModel
+    from sarathi_serve_b200.model_runner import ModelGraphRunner, prepare_inputs
+
+    class Q:
+        def forward(self, q, k, v, layer_cache_idx, softmax_scale=1.0, layer_id=None):
+            return q
+
+    case = S.CASES["mini_bf16"]
+    cfg = case.hf_config()
+    cfg.num_hidden_layers, cfg.vocab_size = 2, 1000
+    old = torch.get_default_dtype()
+    torch.set_default_dtype(case.dtype)
+    try:
+        model = LlamaModel(cfg)
+    finally:
+        torch.set_default_dtype(old)
+    t = S.generate(case)
+    for layer in model.layers:
+        S.load_layer(layer, S.shard(t, 0, 1))
+    g = torch.Generator().manual_seed(3)
+    model.embed_tokens.weight.data.copy_(torch.randn(1024, case.hidden_size, generator=g).to(case.dtype))
+    tok, pos, n = prepare_inputs([([5, 6, 7, 8, 9], 0), ([11, 12, 13], 40)], [(21, 100), (22, 7)], "cuda")
+    assert n == 10 and tok.tolist() == [5, 6, 7, 8, 9, 11, 12, 13, 21, 22, 0, 0, 0, 0, 0, 0]
+    assert pos.tolist() == [0, 1, 2, 3, 4, 40, 41, 42, 99, 6, 0, 0, 0, 0, 0, 0]
+    runner = ModelGraphRunner(model, Q(), buckets=(16, 32, 64))
+    assert runner.bucket_for(1) == 16 and runner.bucket_for(17) == 32
+    for n_tok in (10, 16, 29, 64, 10):
+        ids = torch.randint(0, 1000, (n_tok,), generator=g).cuda()
+        p_ = torch.randint(0, 1000, (n_tok,), generator=g).cuda()
+        out = runner.run(ids, p_).clone()
+        size = runner.bucket_for(n_tok)
+        ids_p = torch.zeros(size, dtype=torch.long, device="cuda"); ids_p[:n_tok] = ids
+        pos_p = torch.zeros(size, dtype=torch.long, device="cuda"); pos_p[:n_tok] = p_
+        with torch.inference_mode():
+            eager = model(ids_p, pos_p, Q())[:n_tok]
+        assert out.shape == (n_tok, case.hidden_size) and torch.equal(out, eager), n_tok
+    assert sorted(runner._graphs) == [16, 32, 64]
+    tp1.get_tensor_model_parallel_comm().check_status()
+    with pytest.raises(RuntimeError, match="largest bucket"):
+        runner.run(torch.zeros(65, dtype=torch.long, device="cuda"), torch.zeros(65, dtype=torch.long, device="cuda"))
+
+
+@pytest.mark.parametrize("case_name", ["mini_bf16", "mini_f32"])
+def test_layer_appends_to_the_paged_kv_cache_through_the_wrapper_hook(tp1, case_name):
+    """An attention wrapper that offers fused_kv_append gets this step's rotated keys and values stored into its
+    paged cache by the qkv GEMM's epilogue (bf16) or by the append kernel (fp32): the cache then holds exactly
+    the k / v the wrapper's forward receives."""
+    from sarathi_serve_b200 import kv_cache_ops
+    case = S.CASES[case_name]
+    layer, t = build_layer(case)
+    T, page = case.num_tokens, 16
+    nkv, hd = case.num_kv_heads, case.head_dim
+    pages = -(-T // page) + 3
+    perm = torch.randperm(pages, generator=torch.Generator().manual_seed(1)).to(torch.int32)
+    # one request whose tokens 0..T-1 are this step's tokens
+    bi = torch.zeros(T, dtype=torch.int32, device="cuda")
+    pos = torch.arange(T, dtype=torch.int32, device="cuda")
+    ki, kp = perm[: -(-T // page)].cuda(), torch.tensor([0, -(-T // page)], dtype=torch.int32, device="cuda")
+
+    class Wrapper(QAttention):
+        def __init__(self):
+            super().__init__()
+            self.cache = torch.zeros(pages, 2, page, nkv, hd, dtype=case.dtype, device="cuda")
+            self.slots = kv_cache_ops.slots(bi, pos, ki, kp, page)   # what begin_forward would compute
+
+        def fused_kv_append(self, layer_cache_idx):
+            return self.cache, self.slots
+
+    w = Wrapper()
+    with torch.inference_mode():
+        layer(t.positions.cuda(), t.x.to(case.dtype).cuda(), 0, w)
+    want = torch.zeros_like(w.cache)
+    kv_cache_ops.append_rows(want, w.seen["k_rot"], w.seen["v"], w.slots)
+    assert torch.equal(w.cache, want) and float(w.cache.abs().sum()) > 0
+    ref = torch.zeros(pages, 2, page, nkv, hd, dtype=case.dtype)
+    O.append_paged_kv_cache(w.seen["k_rot"].cpu(), w.seen["v"].cpu(), bi.cpu(), pos.cpu(), ref, ki.cpu(), kp.cpu())
+    assert torch.equal(w.cache.cpu(), ref)

@@ -40,9 +40,14 @@ def _entry(rank, world, port, fn_name, ret, nvls):
         os.environ["MASTER_PORT"] = str(port)
         os.environ["NCCL_NVLS_ENABLE"] = "0"
         os.environ["SB200_NVLS"] = "1" if nvls else "0"  # heaps bound to an NVSwitch multicast range, or plain peer mappings
+        # a wait on a peer that cannot succeed ends after about a second (the library's default is ten): a protocol
+        # error then fails the test quickly instead of stalling every following collective for long
+        os.environ.setdefault("SB200_WAIT_LIMIT_CYCLES", "3000000000")
         import torch.distributed as dist
         torch.cuda.set_device(rank)
-        dist.init_process_group("gloo", rank=rank, world_size=world)
+        import datetime
+        # a rank that fails leaves the others in a host barrier: it gives up after a minute and a half
+        dist.init_process_group("gloo", rank=rank, world_size=world, timeout=datetime.timedelta(seconds=90))
         from sarathi_serve_b200 import parallel_state as ps
         ps.initialize_model_parallel(world)
         try:
@@ -66,7 +71,9 @@ def _run(fn_name, port, world, nvls=True):
     ret = mgr.dict()
     procs = [ctx.Process(target=_entry, args=(r, world, port, fn_name, ret, nvls)) for r in range(world)]
     [p.start() for p in procs]
-    [p.join(timeout=300) for p in procs]
+    import time
+    deadline = time.time() + 240
+    [p.join(timeout=max(1.0, deadline - time.time())) for p in procs]
     for p in procs:
         if p.is_alive():
             p.terminate()
@@ -361,6 +368,71 @@ def _body_graph_odd(rank, world):
     comm.check_status()
 
 
+def _body_all_gather(rank, world):
+    """All-gather of row blocks: every rank contributes its rows, every rank ends up with all of them --
+    exact copies -- also for batches with fewer rows than ranks and for ragged last blocks."""
+    from sarathi_serve_b200 import parallel_state as ps
+    comm = ps.get_tensor_model_parallel_comm(16 << 20)
+    for dtype in (torch.bfloat16, torch.float32):
+        for T, H in ((512, 4096), (65, 1024), (7, 256), (1, 64), (world, 128)):
+            g = torch.Generator().manual_seed(T + H)
+            full = torch.randn(T, H, generator=g).to(dtype)
+            rpr = -(-T // world)
+            lo, hi = min(T, rank * rpr), min(T, rank * rpr + rpr)
+            rows = full[lo:hi].contiguous().cuda()
+            _host_barrier()
+            y = comm.all_gather_rows(rows, T)
+            assert torch.equal(y.cpu(), full), ("heap view", dtype, T, H)
+            out = torch.empty(T, H, dtype=dtype, device="cuda")
+            y2 = comm.all_gather_rows(rows, T, out=out)
+            assert y2 is out and torch.equal(out.cpu(), full), ("caller tensor", dtype, T, H)
+            # interleaved with a sum: the two kinds of collective share the flags and the call counter
+            s_, _ = comm.all_reduce(out)
+            assert _rel(s_, full.float() * world) <= 1e-2
+    comm.check_status()
+
+
+def _body_graph_io(rank, world):
+    """LayerGraph with host buffers sharded by token rows: upload this rank's rows, all-gather inside the graph,
+    the layer, download this rank's rows of the result; replayed with fresh inputs."""
+    from oracle import tp_layer_oracle as O
+    from sarathi_serve_b200 import parallel_state as ps, synthetic as S
+    from sarathi_serve_b200.decoder_layer import LlamaDecoderLayer
+    from sarathi_serve_b200.graph_runner import LayerGraph
+    from helpers import TOL
+
+    class QAttention:
+        def forward(self, q, k, v, idx, scale=1.0, layer_id=None):
+            return q
+
+    case = S.CASES["mini_bf16"]
+    old = torch.get_default_dtype()
+    torch.set_default_dtype(case.dtype)
+    try:
+        layer = LlamaDecoderLayer(case.hf_config(), layer_id=0)
+    finally:
+        torch.set_default_dtype(old)
+    t = S.generate(case)
+    S.load_layer(layer, S.shard(t, rank, world))
+    _host_barrier()
+    runner = LayerGraph(layer, case.num_tokens, QAttention(), host_io=True, shard_host_io=True)
+    lo, hi = runner.row_range
+    cache = O.cos_sin_cache(case.head_dim, case.head_dim, case.max_position, case.rope_theta, case.dtype)
+    shards = [S.shard(t, r, world) for r in range(world)]
+    for rep in range(3):
+        x = (t.x * (1.0 + 0.25 * rep)).to(case.dtype)
+        runner.host_positions.copy_(t.positions)
+        runner.host_hidden_states.copy_(x[lo:hi])
+        _host_barrier()
+        out = runner.replay_host_io()
+        torch.cuda.current_stream().synchronize()
+        ref = O.decoder_layer(shards, x, t.positions, num_heads=case.num_heads, num_kv_heads=case.num_kv_heads,
+                              head_dim=case.head_dim, eps=case.rms_norm_eps, cache=cache)["out"]
+        err = float((out.double() - ref[lo:hi].double()).abs().max()) / float(ref.double().abs().max())
+        assert err <= TOL[case.dtype], (rep, err)
+    ps.get_tensor_model_parallel_comm().check_status()
+
+
 # -------------------------------------------------------------------- tests
 SCHEMES = pytest.mark.parametrize("nvls", (False, True), ids=("peer-loads", "nvls"))
 
@@ -393,6 +465,18 @@ def test_layer_stack_with_sharded_residual_multi_gpu(world, nvls):
 @pytest.mark.parametrize("world", (2, 4))
 def test_graph_with_an_odd_number_of_collectives_replays(world, nvls):
     _run("_body_graph_odd", 29808, world, nvls)
+
+
+@SCHEMES
+@pytest.mark.parametrize("world", WORLDS)
+def test_all_gather_rows_multi_gpu(world, nvls):
+    _run("_body_all_gather", 29809, world, nvls)
+
+
+@SCHEMES
+@pytest.mark.parametrize("world", (2, 8))
+def test_layer_graph_with_row_sharded_host_buffers(world, nvls):
+    _run("_body_graph_io", 29810, world, nvls)
 
 
 @pytest.mark.parametrize("world", WORLDS)

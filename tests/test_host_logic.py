@@ -412,3 +412,17 @@ def test_model_stack_api_surface_on_cpu():
         assert lm.lm_head.weight.shape == (1024, 128) and lm.lm_head.bias is None
     finally:
         ps.destroy_model_parallel()
+
+
+def test_prepare_inputs_lays_a_mixed_batch_out_like_the_reference():
+    """Prefill chunks first (positions continue where the prompt stopped), then one token per decoding request at
+    position context_len - 1, then zeros up to a multiple of 8 (sarathi/model_executor/model_runner.py:67-117)."""
+    from sarathi_serve_b200.model_runner import pad_to_alignment, prepare_inputs
+    tok, pos, n = prepare_inputs([([5, 6, 7], 0), ([9], 4)], [(21, 100)], "cpu")
+    assert n == 5 and tok.dtype == torch.long and pos.dtype == torch.long
+    assert tok.tolist() == [5, 6, 7, 9, 21, 0, 0, 0] and pos.tolist() == [0, 1, 2, 4, 99, 0, 0, 0]
+    tok, pos, n = prepare_inputs([], [(1, 1)] * 8, "cpu")
+    assert n == 8 and tok.numel() == 8 and pos.tolist() == [0] * 8
+    assert pad_to_alignment([], 8) == [] and len(pad_to_alignment([1] * 9, 8)) == 16
+    tok, pos, n = prepare_inputs([], [], "cpu")
+    assert n == 0 and tok.numel() == 0

@@ -45,7 +45,7 @@ def _child(body: str, timeout: int = 600) -> str:
 
 
 # What the reference needs around it to import and build a layer outside its engine: stub modules for the
-# plotting / sketch packages its metrics code imports, a disabled MetricsStore, a one-rank process group with
+# plotting / sketch packages its metrics code imports (and for its protobuf module when that is missing), a disabled MetricsStore, a one-rank process group with
 # its parallel state initialised, and -- without a GPU -- its device choices mapped to the CPU.
 _PRELUDE = r'''
 import os, sys, types
@@ -59,6 +59,16 @@ for name, attrs in (("plotly", {}), ("plotly.express", {}), ("plotly_express", {
         __import__(name)
     except Exception:
         m = types.ModuleType(name); m.__dict__.update(attrs); sys.modules[name] = m
+if not os.path.isfile(os.path.join(os.environ["SB200_TEST_REFERENCE"], "sarathi", "core", "proto", "datatypes_pb2.py")):
+    # a pip-installed copy of the reference lacks its protobuf module (the directory has no __init__.py, so the
+    # reference's own setup.py leaves it out); only the engine's wire format uses it
+    class _AnyAttr(types.ModuleType):
+        def __getattr__(self, name):
+            if name.startswith("__"):
+                raise AttributeError(name)
+            return object
+    sys.modules["sarathi.core.proto"] = _AnyAttr("sarathi.core.proto")
+    sys.modules["sarathi.core.proto.datatypes_pb2"] = sys.modules["sarathi.core.proto"].datatypes_pb2 = _AnyAttr("sarathi.core.proto.datatypes_pb2")
 HAVE_GPU = torch.cuda.is_available()
 if not HAVE_GPU:
     torch.cuda.current_device = lambda: "cpu"

@@ -106,3 +106,23 @@ def test_vocab_parallel_embedding_equals_the_full_table_lookup():
     for tp in (1, 2, 4, 8):
         shards = list(table.chunk(tp, dim=0))
         assert torch.equal(O.vocab_parallel_embedding(ids, shards), table[ids])
+
+
+def test_kv_cache_append_oracle_on_a_hand_worked_batch():
+    """Two requests, pages of 4 slots: request 0 holds 3 tokens and appends 3 (positions 3, 4, 5: the last
+    slot of its first page, then two slots of its second page), request 1 appends its first token."""
+    page = 4
+    kv_indices = [7, 2, 5]       # request 0 owns pages 7 and 2, request 1 page 5
+    kv_indptr = [0, 2, 3]
+    batch_indices = [0, 0, 0, 1, -1]
+    positions = [3, 4, 5, 0, 0]
+    s = O.kv_cache_slots(batch_indices, positions, kv_indices, kv_indptr, page)
+    assert s.tolist() == [7 * 8 + 3, 2 * 8 + 0, 2 * 8 + 1, 5 * 8 + 0, -1]
+    cache = torch.zeros(8, 2, page, 1, 2)
+    k = torch.arange(10, dtype=torch.float32).view(5, 1, 2) + 1
+    v = -k
+    O.append_paged_kv_cache(k, v, batch_indices, positions, cache, kv_indices, kv_indptr)
+    assert torch.equal(cache[7, 0, 3], k[0]) and torch.equal(cache[7, 1, 3], v[0])
+    assert torch.equal(cache[2, 0, 0], k[1]) and torch.equal(cache[2, 1, 1], v[2])
+    assert torch.equal(cache[5, 0, 0], k[3]) and torch.equal(cache[5, 1, 0], v[3])
+    assert float(cache.abs().sum()) == float(k[:4].abs().sum() * 2)  # the padding entry stored nothing
