@@ -892,17 +892,18 @@ def run_parts(a):
             return
         ar_bytes = 2.0 * (world - 1) / world * T * H * es  # per direction, per GPU
         gemm_entry("qkv_gemm+rotary", graph_us(lambda i: layers[i % nl].self_attn.qkv_rotary(pos, normed)), 2.0 * T * H * qkv_n)
-        us = graph_us(lambda i: layers[i % nl].self_attn.o_proj.forward_fused(q, x, nw, 1e-5))
+        # (as on the layer path: the new residual stays with the owner of each row -- resid_everywhere=False)
+        us = graph_us(lambda i: layers[i % nl].self_attn.o_proj.forward_fused(q, x, nw, 1e-5, resid_everywhere=False))
         gemm_entry("o_proj_gemm+allreduce+add+rmsnorm", us, 2.0 * T * H * nq * hd / world,
                    {"nvlink_gbs_per_direction": ar_bytes / us / 1e3 if world > 1 else None})
         gemm_entry("gate_up_gemm+silu_mul", graph_us(lambda i: layers[i % nl].mlp.gate_up_proj.forward_silu_mul(h)), 2.0 * T * H * 2 * d)
-        us = graph_us(lambda i: layers[i % nl].mlp.down_proj.forward_fused(act, resid, nw, 1e-5))
+        us = graph_us(lambda i: layers[i % nl].mlp.down_proj.forward_fused(act, resid, nw, 1e-5, resid_everywhere=False))
         gemm_entry("down_gemm+allreduce+add+rmsnorm", us, 2.0 * T * H * d,
                    {"nvlink_gbs_per_direction": ar_bytes / us / 1e3 if world > 1 else None})
         gemm_entry("o_proj_gemm_alone", graph_us(lambda i: dense_ops.linear(q, layers[i % nl].self_attn.o_proj.weight)), 2.0 * T * H * nq * hd / world)
         gemm_entry("down_gemm_alone", graph_us(lambda i: dense_ops.linear(act, layers[i % nl].mlp.down_proj.weight)), 2.0 * T * H * d)
         if world > 1:
-            us = graph_us(lambda i: comm.all_reduce(h, residual=x, norm_weight=nw, eps=1e-5))
+            us = graph_us(lambda i: comm.all_reduce(h, residual=x, norm_weight=nw, eps=1e-5, resid_everywhere=False))
             out["allreduce+add+rmsnorm_alone"] = {"us": us, "nvlink_bytes_per_direction": ar_bytes,
                                                    "nvlink_gbs_per_direction": ar_bytes / us / 1e3,
                                                    "frac_of_nvlink": ar_bytes / us / 1e3 / NVLINK_GBS}

@@ -184,7 +184,9 @@ typedef struct sb200_rotary_args {
  *   with 1|2 accumulators of 128 rows; MODE = 3|4: CTA pairs (tcgen05 cta_group::2) with
  *   1|2 accumulators of 256 rows; S >= 2 spreads the k-blocks of the tiles that do not fill
  *   a last round over about S units per tile, in equal ranges; a bare BN means MODE = 1,
- *   whole tiles per CTA).
+ *   whole tiles per CTA; MODE = 5: CTA pairs, every tile computed by a cluster of S = 2 or 4 pairs
+ *   that split its k-blocks and combine their fp32 accumulators through distributed shared memory --
+ *   accepted when the problem has at most #SMs / (2 S) tiles).
  * workspace: optional device buffer (zero-filled once by the caller, at least 64 KiB +
  *   room for the fp32 partial tiles) that allows tiles to be cut along K;
  *   the library leaves its first 64 KiB zero again after every launch.  NULL / 0: whole
@@ -217,10 +219,11 @@ int sb200_kv_cache_append(void* cache, const void* k, int64_t ldk, const void* v
                           int64_t n, int num_kv_heads, int head_dim, int page_size, int dtype, sb200_stream_t stream);
 
 /* The tile shape and schedule the two GEMM entry points would pick (epilogue 3 = the
- * row-parallel kernel): out[0..10] = cta_pairs, accumulators, BN, scheduling units,
+ * row-parallel kernel): out[0..11] = cta_pairs, accumulators, BN, scheduling units,
  * tiles handed out whole, S of the configuration, units that share the k-blocks of the
  * remaining tiles (= their number when nothing is cut), pipeline stages, M tiles, N tiles,
- * k-blocks.  Host-only; no counterpart in the reference. */
+ * k-blocks, CTA pairs per tile (> 1: MODE 5, the tile's k-blocks are split inside a cluster).
+ * Host-only; no counterpart in the reference. */
 int sb200_gemm_plan(int epilogue, int64_t T, int64_t N, int64_t K, int head_size, int tile_cfg,
                     int64_t workspace_bytes, int* out);
 

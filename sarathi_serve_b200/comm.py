@@ -74,6 +74,45 @@ class TPComm:
         heap_bytes = int(lib.sb200_comm_heap_bytes(self.region_bytes))
         self._heap = torch.as_tensor(_DeviceMemory(heap_ptr, heap_bytes), device=self.device)
         self._heap_ptr = heap_ptr
+        if self.multicast:
+            with torch.cuda.device(self.device):
+                self._self_test_multicast()
+
+    def _self_test_multicast(self) -> None:
+        """One small all-reduce through the switch against the same all-reduce over peer loads, once, at
+        construction.  If any rank sees a difference or a wait that ran out, every rank drops the multicast
+        alias (the heaps stay, the collectives use peer loads) -- a box whose NVSwitch multicast does not behave
+        costs speed, not results."""
+        import torch.distributed as dist
+        lib = N.lib()
+        T, H = 4 * self.world + 3, 512
+        x = ((torch.arange(T * H, device=self.device, dtype=torch.float32).view(T, H) % 61) * 0.125
+             - 3.0 + 0.25 * self.rank).to(torch.bfloat16)
+        default_wait = int(os.environ.get("SB200_WAIT_LIMIT_CYCLES", "0")) or 20_000_000_000
+        default_one_shot = int(os.environ.get("SB200_ONE_SHOT_BYTES", str(4 << 20)))
+        mc_ptr = ctypes.c_void_p(self._mc_ptr)
+        ok = 1
+        try:
+            self.set_wait_limit_cycles(3_000_000_000)   # about a second and a half
+            self.set_one_shot_bytes(0)                  # the owner-reduce schemes, whatever the size
+            y_mc = self.all_reduce(x)[0].float().clone()
+            N.check(lib.sb200_comm_set_multicast(self._h, None), "comm_set_multicast")
+            y_pl = self.all_reduce(x)[0].float().clone()
+            N.check(lib.sb200_comm_set_multicast(self._h, mc_ptr), "comm_set_multicast")
+            torch.cuda.synchronize(self.device)
+            if self.status_code() != 0 or float((y_mc - y_pl).abs().max()) > 0.26:  # sums up to ~40: 2 units in the last place
+                ok = 0
+        except RuntimeError:
+            ok = 0
+        verdict = [None] * self.world
+        dist.all_gather_object(verdict, ok, group=self.group)
+        self.set_wait_limit_cycles(default_wait)
+        self.set_one_shot_bytes(default_one_shot)
+        if not all(verdict):
+            N.check(lib.sb200_comm_set_multicast(self._h, None), "comm_set_multicast")
+            self.multicast = False
+            self._poisoned = False
+            self.reset()
 
     def _create_on_symmetric_memory(self, lib, region_bytes: int) -> bool:
         """Heaps from torch's symmetric-memory allocator, bound to an NVSwitch multicast range.  Every rank
@@ -107,6 +146,7 @@ class TPComm:
                 "comm_create_external")
         N.check(lib.sb200_comm_set_multicast(self._h, ctypes.c_void_p(mc_ptr)), "comm_set_multicast")
         self._symm = (tensor, handle)
+        self._mc_ptr = mc_ptr
         self.multicast = True
         return True
 

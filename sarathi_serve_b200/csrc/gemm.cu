@@ -80,6 +80,25 @@ GemmPlan plan_gemm(int epi, int64_t M, int64_t N, int64_t K, int head_size, int 
     if (f_mode == 0) f_mode = 1;
     if (f_s == 0) f_s = 1;
   }
+  if (f_mode == 5) {
+    // cluster K-split: explicit configurations only (the autotuner times them against the others)
+    GemmPlan p = {};
+    const int bn = f_bn, sp = f_s;
+    const bool rot_ok = epi != EPI_ROTARY || bn % head_size == 0 || (neox && bn < head_size && bn == 64 && head_size % bn == 0);
+    const bool shape_ok = bn >= 32 && bn <= 256 && bn % 64 == 0 && (sp == 2 || sp == 4) && rot_ok;
+    if (!shape_ok) return p;
+    const int m_tiles = (int)((M + 255) / 256);
+    const int cols_per_tile = (epi == EPI_SILU_MUL) ? bn / 2 : bn;
+    const int n_tiles = (int)((out_cols + cols_per_tile - 1) / cols_per_tile);
+    const int64_t tiles = (int64_t)m_tiles * n_tiles;
+    const int stages = gemm_max_stages(1, bn, 1);
+    const size_t exchange = (size_t)(sp - 1) * bn * 128 * sizeof(float);  // partial accumulators parked in one CTA
+    if (tiles * 2 * sp > sms || k_blocks < sp || stages < 2 || exchange > (size_t)stages * gemm_stage_bytes(1, bn, 1)) return p;
+    p.cta2 = 1; p.mi = 1; p.bn = bn; p.units = (int)tiles; p.tiles_full = (int)tiles; p.rem_splits = 1; p.rem_units = 0;
+    p.stages = stages; p.m_tiles = m_tiles; p.n_tiles = n_tiles; p.k_blocks = k_blocks; p.cluster_split = sp;
+    p.est_clocks = 9000.0 + (double)((k_blocks + sp - 1) / sp) * (2.0 * bn > 260.0 ? 2.0 * bn : 260.0) + exchange / 32.0;
+    return p;
+  }
   double best_cost = 1e30;
   for (int mode = 1; mode <= 4; ++mode) {
     if (f_mode && mode != f_mode) continue;
@@ -102,11 +121,13 @@ GemmPlan plan_gemm(int epi, int64_t M, int64_t N, int64_t K, int head_size, int 
       if (!f_mode && bm > 128 && M <= bm / 2) continue;  // half of the tile would be empty
       const int units_max = cta2 ? sms / 2 : sms;     // CTAs or CTA pairs that run at once
       const int64_t total = tiles * k_blocks;
-      // per-k-block clocks of one SM (constants fitted to measurements on B200):
-      //   one CTA: a tcgen05.mma of K=16 (M=128) occupies the tensor pipe ~154 clocks whatever N <= 256;
-      //   a CTA pair (M=256) runs at the nominal rate, N/2 clocks per MMA with a floor of ~65;
-      //   the stage also has to cross L2 -> shared memory (~50 B/clk/SM with every SM pulling, which
-      //   is what bounds 256x256 pair tiles) and shared memory itself (fill + operand reads).
+      // per-k-block clocks of one SM (constants fitted to the measured times of the full kernels on B200):
+      //   one CTA: about 616 clocks per k-block whatever N <= 256 -- not the tensor pipe (the MMA-rate probe of
+      //   diag.cu shows N/2 clocks per MMA for one CTA as for a pair) but the operand feed: a single-CTA stage
+      //   of 128 + N rows crosses L2 -> shared memory at ~50 B/clk/SM with every SM pulling;
+      //   a CTA pair loads half of the B tile per SM and reaches the nominal N/2 clocks per MMA down to a
+      //   floor of ~65; its 256x256 tiles are again bound by the feed (64 B/clk needed), and shared memory
+      //   itself (fill + operand reads) is modelled too.
       const double stage = gemm_stage_bytes(mi, bn, cta2);
       const double mma_nominal = cta2 ? 2.0 * mi * bn : 616.0 * mi;
       const double mma_floor = cta2 ? 260.0 * mi : 616.0 * mi;
@@ -155,6 +176,7 @@ GemmPlan plan_gemm(int epi, int64_t M, int64_t N, int64_t K, int head_size, int 
           best.tiles_full = (tiles >= units_max) ? (int)tiles_full : 0;
           best.rem_splits = sp; best.rem_units = (int)gs;
           best.stages = stages; best.m_tiles = m_tiles; best.n_tiles = n_tiles; best.k_blocks = k_blocks;
+          best.cluster_split = 1;
           best.est_clocks = cost;
         }
       }
@@ -231,14 +253,15 @@ static int launch_sm100(const CUtensorMap& ta, const CUtensorMap& tb, const Gemm
   const int smem = g.stages * gemm_stage_bytes(g.mi, g.bn, CTA2 ? 1 : 0) + kBarrierBytes + 1024;
   int grid = g.units;
   if (grid < 1) grid = 1;
+  const int pairs_per_unit = (CTA2 && g.cluster_split > 1) ? g.cluster_split : 1;
   cudaLaunchConfig_t cfg = {};
-  cfg.gridDim = dim3(CTA2 ? 2 * grid : grid);
+  cfg.gridDim = dim3(CTA2 ? 2 * pairs_per_unit * grid : grid);
   cfg.blockDim = dim3(kGemmThreads);
   cfg.dynamicSmemBytes = smem;
   cfg.stream = s;
   cudaLaunchAttribute attr[2];
   attr[0].id = cudaLaunchAttributeClusterDimension;
-  attr[0].val.clusterDim.x = CTA2 ? 2 : 1;
+  attr[0].val.clusterDim.x = CTA2 ? 2 * pairs_per_unit : 1;
   attr[0].val.clusterDim.y = 1;
   attr[0].val.clusterDim.z = 1;
   // programmatic dependent launch: the prologue (barriers, TMEM, tensor maps) may run while the previous
@@ -279,6 +302,7 @@ int run_gemm_sm100(int dtype, int epi, const GemmPlan& plan, const void* x, int6
   g.cta2 = plan.cta2;
   g.mi = plan.mi; g.bn = plan.bn; g.units = plan.units; g.tiles_full = plan.tiles_full;
   g.rem_units = plan.rem_units;
+  g.cluster_split = plan.cluster_split > 1 ? plan.cluster_split : 1;
   g.l2_prefetch = l2_prefetch_distance();
   g.stages = plan.stages; g.m_tiles = plan.m_tiles; g.n_tiles = plan.n_tiles; g.k_blocks = plan.k_blocks;
   if (plan.rem_units > (int)((int64_t)plan.m_tiles * plan.n_tiles - plan.tiles_full)) {
@@ -407,16 +431,16 @@ extern "C" int sb200_gemm_colpar(void* out, int64_t ldo, const void* x, int64_t 
 }
 
 // The tile shape and schedule sb200_gemm_colpar / sb200_gemm_rowpar would use (for tuning and tests).
-// out[0..10] = cta2, mi, bn, units, tiles_full, rem_splits, rem_units, stages, m_tiles, n_tiles, k_blocks.
+// out[0..11] = cta2, mi, bn, units, tiles_full, rem_splits, rem_units, stages, m_tiles, n_tiles, k_blocks, cluster_split.
 extern "C" int sb200_gemm_plan(int epilogue, int64_t T, int64_t N, int64_t K, int head_size, int tile_cfg,
                                int64_t workspace_bytes, int* out) {
   SB_CHECK_ARG(out != nullptr && T > 0 && N > 0 && K > 0, "gemm_plan: bad arguments");
   const int epi = epilogue == SB200_EPI_ROTARY ? EPI_ROTARY : epilogue == SB200_EPI_SILU_MUL ? EPI_SILU_MUL
                   : epilogue == 3 ? EPI_PUSH : EPI_STORE;
   const GemmPlan p = plan_gemm(epi, T, N, K, head_size ? head_size : 128, tile_cfg, (size_t)workspace_bytes);
-  const int v[11] = {p.cta2, p.mi, p.bn, p.units, p.tiles_full, p.rem_splits, p.rem_units, p.stages, p.m_tiles,
-                     p.n_tiles, p.k_blocks};
-  for (int i = 0; i < 11; ++i) out[i] = v[i];
+  const int v[12] = {p.cta2, p.mi, p.bn, p.units, p.tiles_full, p.rem_splits, p.rem_units, p.stages, p.m_tiles,
+                     p.n_tiles, p.k_blocks, p.cluster_split > 1 ? p.cluster_split : 1};
+  for (int i = 0; i < 12; ++i) out[i] = v[i];
   return p.bn ? SB200_OK : SB200_ERR_UNSUPPORTED;
 }
 

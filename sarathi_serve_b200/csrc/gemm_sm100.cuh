@@ -94,6 +94,9 @@ struct GemmArgs {
   float* ws;               // partial-tile workspace: [cut tiles * S][BM][bn] fp32
   uint32_t* ws_counters;   // [cut tiles][arrived[16], done[16]], zero between launches
   int cta2;                // 1: tiles of 256 rows computed by CTA pairs (cta_group::2)
+  int cluster_split;       // > 1 (CTA pairs, one accumulator, one tile per unit): a cluster of that many CTA pairs
+                           // computes ONE tile, pair p the p-th share of its k-blocks; the fp32 accumulators of pairs
+                           // 1.. travel to pair 0 through distributed shared memory and pair 0 runs the epilogue
   uint32_t* status;        // device word: first error of this launch (0 = none); may be null
 };
 
@@ -158,6 +161,27 @@ struct TmemSource {
     ptx::tmem_ld_32x32(row_addr + (uint32_t)col, r);
 #pragma unroll
     for (int j = 0; j < 32; ++j) f[j] = __uint_as_float(r[j]);
+  }
+};
+// Cluster K-split: the accumulator chunk of pair 0 (TMEM) plus the partial accumulators the other pairs of the
+// cluster left in this CTA's shared memory, laid out [part][column][128 rows] so that the 32 lanes of a warp
+// (32 consecutive rows) read one 128-byte line per column.  Parts are added in order: the result does not
+// depend on timing.
+struct TmemPlusSmemSource {
+  uint32_t row_addr;
+  const float* sm;  // this thread's row in the first partial: element (part, col) at ((part * bn + col) * 128)
+  int parts;        // partials in shared memory (cluster_split - 1)
+  int bn;
+  __device__ __forceinline__ void load32(int col, float* f) const {
+    uint32_t r[32];
+    ptx::tmem_ld_32x32(row_addr + (uint32_t)col, r);
+#pragma unroll
+    for (int j = 0; j < 32; ++j) f[j] = __uint_as_float(r[j]);
+    for (int p = 0; p < parts; ++p) {
+      const float* base = sm + (size_t)(p * bn + col) * 128;
+#pragma unroll
+      for (int j = 0; j < 32; ++j) f[j] += base[(size_t)j * 128];
+    }
   }
 };
 // Scheduling.  Tiles are numbered M-fastest.  With G scheduling units (CTAs or CTA pairs):
@@ -507,10 +531,19 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
   const int kStages = g.stages;
   const bool dbuf = (MI * BN * 2) <= (int)kTmemCols;  // room for two sets of accumulators
   const uint32_t idesc = ptx::make_idesc(DT<T>::id == SB200_BF16 ? 1 : 0, BN, CTA2 ? 256 : 128);
-  const uint32_t cta_rank = CTA2 ? ptx::cluster_ctarank() : 0u;
+  const uint32_t crank = CTA2 ? ptx::cluster_ctarank() : 0u;  // rank in the cluster: pair p = ranks (2p, 2p+1)
+  const uint32_t cta_rank = crank & 1u;                        // rank inside the pair
+  const uint32_t pair_base = crank & ~1u;                      // cluster rank of this pair's leader
   const bool leader = cta_rank == 0;
-  const int unit_id = CTA2 ? (int)(blockIdx.x >> 1) : (int)blockIdx.x;     // CTA or CTA pair
-  const int num_units_grid = CTA2 ? (int)(gridDim.x >> 1) : (int)gridDim.x;
+  const int ks = (CTA2 && g.cluster_split > 1) ? g.cluster_split : 1;  // CTA pairs per tile (cluster K-split)
+  const int kpart = (int)(crank >> 1);                                 // which share of the k-blocks this pair computes
+  const int ctas_per_unit = CTA2 ? 2 * ks : 1;
+  const int unit_id = (int)blockIdx.x / ctas_per_unit;                 // CTA, CTA pair or cluster of pairs
+  const int num_units_grid = (int)gridDim.x / ctas_per_unit;
+  const uint16_t pair_mask = (uint16_t)(3u << pair_base);
+  // the k-blocks of a work item this pair runs (all of them unless the cluster splits K)
+  auto kb_lo = [&](const Segment& sg) { return ks > 1 ? sg.kb0 + (int)((long long)(sg.kb1 - sg.kb0) * kpart / ks) : sg.kb0; };
+  auto kb_hi = [&](const Segment& sg) { return ks > 1 ? sg.kb0 + (int)((long long)(sg.kb1 - sg.kb0) * (kpart + 1) / ks) : sg.kb1; };
 
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -580,14 +613,15 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
           if (mt * BM >= rows_in_use) continue;  // row block beyond the padded slots: every role skips it
           b_row0 = g.expert_ids[mt] * g.rows_per_expert;
         }
-        for (int kb = sg.kb0; kb < sg.kb1; ++kb) {
+        const int p_kb1 = kb_hi(sg);
+        for (int kb = kb_lo(sg); kb < p_kb1; ++kb) {
           if (!ptx::mbar_wait(&empty_bar[stage], phase ^ 1u, abort_flag)) { ok = false; break; }
           uint8_t* sa = stage_base + (size_t)stage * stage_bytes;
           uint8_t* sb = sa + a_bytes;
           const bool halves = (EPI == EPI_SILU_MUL) || (EPI == EPI_ROTARY && g.rot_split);  // B tile = two row blocks
           const int b_first = tile_first_col<EPI>(g, nt);                                  // first row of the first block
           const int b_second = b_first + (EPI == EPI_SILU_MUL ? g.N / 2 : g.head_size / 2);  // ... of the second
-          if (g.l2_prefetch > 0 && kb + g.l2_prefetch < sg.kb1 && !(EPI == EPI_ROTARY && g.rot_split)) {
+          if (g.l2_prefetch > 0 && kb + g.l2_prefetch < p_kb1 && !(EPI == EPI_ROTARY && g.rot_split)) {
             // weights are read once: start their trip from HBM to L2 a few stages early
             const int pk = (kb + g.l2_prefetch) * kBK;
             if (CTA2) {
@@ -600,7 +634,7 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
           }
           if constexpr (CTA2) {
             // both CTAs' bytes are counted on the leader's barrier; only the leader announces them
-            const uint32_t bar = ptx::map_to_cta(ptx::smem_u32(&full_bar[stage]), 0);
+            const uint32_t bar = ptx::map_to_cta(ptx::smem_u32(&full_bar[stage]), pair_base);
             if (leader) ptx::mbar_expect_tx(&full_bar[stage], (uint32_t)(2 * stage_bytes));
 #pragma unroll
             for (int a = 0; a < MI; ++a)  // accumulator a covers tile rows [256a, 256a+256): this CTA's half of them
@@ -639,7 +673,7 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
         if (!sg.valid) break;
         if (g.expert_ids && (sg.tile % g.m_tiles) * BM >= rows_in_use) continue;
         const int local = used++;
-        const int kb0 = sg.kb0, kb1 = sg.kb1;
+        const int kb0 = kb_lo(sg), kb1 = kb_hi(sg);
         const int buf = dbuf ? (local & 1) : 0;
         const uint32_t use = (uint32_t)(dbuf ? (local >> 1) : local);  // earlier uses of this buffer
         if (!ptx::mbar_wait(&tmem_empty[buf], (use & 1u) ^ 1u, abort_flag)) { ok = false; break; }
@@ -662,11 +696,11 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
             }
           }
           // frees the smem stage (in both CTAs of a pair) once these MMAs have read it
-          if (CTA2) ptx::umma_commit_pair(&empty_bar[stage]); else ptx::umma_commit(&empty_bar[stage]);
+          if (CTA2) ptx::umma_commit_pair_mask(&empty_bar[stage], pair_mask); else ptx::umma_commit(&empty_bar[stage]);
           if (++stage == kStages) { stage = 0; phase ^= 1u; }
         }
         if (ok) {  // accumulators complete
-          if (CTA2) ptx::umma_commit_pair(&tmem_full[buf]); else ptx::umma_commit(&tmem_full[buf]);
+          if (CTA2) ptx::umma_commit_pair_mask(&tmem_full[buf], pair_mask); else ptx::umma_commit(&tmem_full[buf]);
         }
       }
     }
@@ -679,10 +713,10 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
     const int a0 = (MI == 2) ? hsel : 0;                   // accumulator this warp drains
     const int row_in_tile = (CTA2 ? a0 * 256 + (int)cta_rank * 128 : a0 * 128) + q * 32 + lane;
     const int u_first = (MI == 2) ? 0 : hsel, u_step = (MI == 2) ? 1 : 2;
-    const uint32_t empty_remote = CTA2 ? ptx::map_to_cta(ptx::smem_u32(&tmem_empty[0]), 0) : 0u;
+    const uint32_t empty_remote = CTA2 ? ptx::map_to_cta(ptx::smem_u32(&tmem_empty[0]), pair_base) : 0u;
     int used = 0;
     bool ok = true;
-    for (int it = 0; ok; ++it) {
+    for (int it = 0; ok && ks == 1; ++it) {  // (a cluster K-split finishes its one tile after the role branches)
       const Segment sg = segment_of(sc, unit_id, it);
       if (!sg.valid) break;
       const int tile = sg.tile, S = sg.parts;
@@ -734,7 +768,7 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
     // Second pass over the cut tiles this unit has a part of: once every part of a tile has left its
     // share for these 32 rows, finish 1/S of the tile's units -- all S parts work on the fix-up at
     // once instead of one of them doing it alone.
-    for (int it = sc.tiles_full / sc.G; ok; ++it) {
+    for (int it = sc.tiles_full / sc.G; ok && ks == 1; ++it) {
       const Segment sg = segment_of(sc, unit_id, it);
       if (!sg.valid) break;
       const int S = sg.parts;
@@ -771,6 +805,53 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
       }
       // every part reports its share of these rows: S arrivals per (cut tile, 32-row slot)
       if constexpr (EPI == EPI_PUSH) push_rows_done(comm, red, g, mt * BM + row_in_tile - lane);
+    }
+  }
+
+  // ------------------------------------------------- cluster K-split: exchange + epilogue
+  // Every thread of every CTA of the cluster joins the two cluster barriers, whatever happened before (a wait
+  // that ran out only makes its warp skip the work in between).
+  if constexpr (CTA2 && MI == 1) {
+    if (ks > 1) {
+      const Segment sg = segment_of(sc, unit_id, 0);  // the unit's one tile
+      const int mt = sg.tile % g.m_tiles, nt = sg.tile / g.m_tiles;
+      const int q = warp & 3, hsel = (warp - 2) >> 2;
+      const int U = num_units<EPI>(g);
+      const int row_in_cta = q * 32 + lane;
+      bool ok = sg.valid;
+      if (warp >= 2 && ok) {
+        ok = __all_sync(0xffffffffu, ptx::mbar_wait(&tmem_full[0], 0u, abort_flag) ? 1 : 0) != 0;
+        ptx::tc_fence_after();
+      }
+      ptx::tc_fence_before();
+      __syncthreads();          // (the warps re-converge here: the producer and the MMA issuer ran on one lane)
+      ptx::cluster_sync_all();  // every pair's MMAs are complete: the stage buffers of all CTAs are free
+      ptx::tc_fence_after();
+      const uint32_t tmem_row = tmem_base + ((uint32_t)(q * 32) << 16);
+      if (warp >= 2 && ok && kpart > 0) {
+        // this pair's partial accumulator rows go to the CTA of pair 0 that holds the same 128 rows
+        const uint32_t dst = ptx::map_to_cta(ptx::smem_u32(stage_base), cta_rank) +
+                             (uint32_t)(((size_t)(kpart - 1) * BN * 128 + row_in_cta) * sizeof(float));
+        for (int c = hsel * 32; c < BN; c += 64) {  // the two warps of a lane quarter alternate 32-column chunks
+          uint32_t r[32];
+          ptx::tmem_ld_32x32(tmem_row + (uint32_t)c, r);
+#pragma unroll
+          for (int j = 0; j < 32; ++j)
+            ptx::st_shared_cluster_f32(dst + (uint32_t)((c + j) * 128 * sizeof(float)), __uint_as_float(r[j]));
+        }
+      }
+      ptx::tc_fence_before();
+      __syncthreads();
+      ptx::cluster_sync_all();  // the partials are in pair 0's shared memory
+      ptx::tc_fence_after();
+      if (warp >= 2 && ok && kpart == 0) {
+        const int n0 = tile_first_col<EPI>(g, nt);
+        const int row_in_tile = (int)cta_rank * 128 + row_in_cta;
+        const RowCtx<T> rc = make_row_ctx<T, EPI>(g, comm, red, mt * BM + row_in_tile, n0);
+        const TmemPlusSmemSource src{tmem_row, reinterpret_cast<const float*>(stage_base) + row_in_cta, ks - 1, BN};
+        for (int u = hsel; u < U; u += 2) finish_unit<T, EPI>(g, rc, src, u);
+        if constexpr (EPI == EPI_PUSH) push_rows_done(comm, red, g, mt * BM + row_in_tile - lane);
+      }
     }
   }
 

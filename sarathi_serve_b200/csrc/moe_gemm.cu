@@ -78,16 +78,23 @@ static int moe_gemm(int epi, void* out, int64_t ldo, const void* a, const void* 
   SB_CHECK_ARG(rows_cap > 0 && rows_cap % kMoeBlockRows == 0, "moe GEMM: the row capacity must be a multiple of %d",
                kMoeBlockRows);
   SB_CHECK_ARG(out && a && w && expert_ids && num_post_pad && E > 0 && N > 0 && K > 0, "moe GEMM: bad arguments");
-  // one accumulator of 128 rows per tile (row blocks of different experts never share a tile), whole tiles only
+  // One accumulator per tile and whole tiles only; a tile is one row block of one expert: 128 rows on a single
+  // CTA (configurations 1xxx) or 256 rows on a CTA pair (3xxx; each CTA of a pair loads half of the weight tile,
+  // and the L2 -> shared-memory feed is what bounds these GEMMs), so the caller aligns the expert blocks to the
+  // tile's rows.
   int cfg = tile_cfg;
   if (cfg == 0) {
     const GemmPlan p0 = plan_gemm(epi == EPI_MOE_SCATTER ? EPI_STORE : epi, rows_cap, N, K, 128, 0, 0);
     int bn = p0.bn ? p0.bn : 128;
     cfg = bn + 1000;
   }
-  SB_CHECK_ARG((cfg / 1000) % 100 == 1 && cfg < 100000, "moe GEMM: only single-CTA, whole-tile configurations (1xxx)");
+  const int mode = (cfg / 1000) % 100;
+  SB_CHECK_ARG((mode == 1 || mode == 3) && cfg < 100000,
+               "moe GEMM: only whole-tile configurations with one accumulator (1xxx: one CTA, 3xxx: CTA pairs)");
+  const int block = mode == 3 ? 2 * kMoeBlockRows : kMoeBlockRows;
+  SB_CHECK_ARG(rows_cap % block == 0, "moe GEMM: the row capacity must be a multiple of the %d-row expert blocks", block);
   const GemmPlan plan = plan_gemm(epi == EPI_MOE_SCATTER ? EPI_STORE : epi, rows_cap, N, K, 128, cfg, 0);
-  SB_CHECK_ARG(plan.bn != 0 && plan.mi == 1 && !plan.cta2, "moe GEMM: no tile shape for configuration %d", cfg);
+  SB_CHECK_ARG(plan.bn != 0 && plan.mi == 1 && plan.cta2 == (mode == 3 ? 1 : 0), "moe GEMM: no tile shape for configuration %d", cfg);
   GemmArgs g = {};
   g.M = (int)rows_cap; g.N = (int)N; g.K = (int)K;
   g.out = out; g.ldo = ldo; g.status = status; g.head_size = 128;

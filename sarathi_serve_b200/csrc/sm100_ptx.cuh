@@ -205,6 +205,22 @@ __device__ __forceinline__ void umma_commit_pair(uint64_t* bar) {
                ::"r"(smem_u32(bar)), "h"(mask) : "memory");
 }
 
+// The same for a pair that sits at ranks (2i, 2i+1) of a larger cluster: `mask` has the two bits of those ranks.
+__device__ __forceinline__ void umma_commit_pair_mask(uint64_t* bar, uint16_t mask) {
+  asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
+               ::"r"(smem_u32(bar)), "h"(mask) : "memory");
+}
+__device__ __forceinline__ uint32_t cluster_nctarank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_nctarank;" : "=r"(r));
+  return r;
+}
+// Store into the shared memory of another CTA of the cluster (distributed shared memory); the address comes
+// from map_to_cta.  Ordered for the target CTA by the next barrier.cluster (release on arrive, acquire on wait).
+__device__ __forceinline__ void st_shared_cluster_f32(uint32_t cluster_addr, float v) {
+  asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(cluster_addr), "f"(v) : "memory");
+}
+
 // Instruction descriptor for kind::f16 / kind::tf32, fp32 accumulate, both operands K-major, M = 128.
 // ab_format: 0 = fp16, 1 = bf16, 2 = tf32.
 __host__ __device__ constexpr uint32_t make_idesc(int ab_format, int n, int m = 128) {

@@ -183,10 +183,10 @@ def linear_silu_mul(x: torch.Tensor, weight: torch.Tensor, out: Optional[torch.T
 def gemm_plan(epilogue: int, T: int, Nn: int, K: int, head_size: int = 128, tile_cfg: int = 0,
               workspace_bytes: int = WORKSPACE_BYTES) -> dict:
     """The tile shape / schedule the library would use for a [T, K] x [Nn, K]^T projection."""
-    out = (ctypes.c_int * 11)()
+    out = (ctypes.c_int * 12)()
     N.check(N.lib().sb200_gemm_plan(epilogue, T, Nn, K, head_size, tile_cfg, workspace_bytes, out), "gemm_plan")
     keys = ("cta_pairs", "accumulators", "bn", "units", "tiles_full", "k_parts", "rem_units", "stages", "m_tiles",
-            "n_tiles", "k_blocks")
+            "n_tiles", "k_blocks", "cluster_split")
     return dict(zip(keys, out))
 
 
@@ -222,9 +222,9 @@ def tuned_cfg(kind: str, T: int, Nn: int, K: int, dtype: torch.dtype) -> int:
 def _candidates(kind: str, T: int, Nn: int, K: int, head_size: int):
     epi = {"store": EPI_NONE, "rotary": EPI_ROTARY, "silu": EPI_SILU_MUL, "push": 3}[kind]
     seen, out = set(), []
-    for mode in (1, 3, 4):
+    for mode in (1, 3, 4, 5):
         for bn in (64, 96, 128, 160, 192, 224, 256):
-            for s in (1, 2, 3, 4, 6, 8):
+            for s in ((2, 4) if mode == 5 else (1, 2, 3, 4, 6, 8)):
                 cfg = bn + 1000 * mode + 100000 * s
                 try:
                     p = gemm_plan(epi, T, Nn, K, head_size, cfg)
@@ -235,6 +235,9 @@ def _candidates(kind: str, T: int, Nn: int, K: int, head_size: int):
                     continue
                 seen.add(key)
                 # encode what the planner actually accepted, so that the key reproduces the plan
+                if p["cluster_split"] > 1:
+                    out.append(p["bn"] + 5000 + 100000 * p["cluster_split"])
+                    continue
                 mode_eff = (2 + p["accumulators"]) if p["cta_pairs"] else p["accumulators"]
                 out.append(p["bn"] + 1000 * mode_eff + 100000 * p["k_parts"])
     return sorted(set(out))

@@ -22,9 +22,17 @@ from . import dense_ops, moe_ops
 from . import parallel_state as ps
 
 
-def block_rows() -> int:
-    """Rows per expert block the grouped GEMMs work with (one tile row block = one expert)."""
-    return int(N.lib().sb200_moe_block_rows())
+def block_rows(pairs: bool = False) -> int:
+    """Rows per expert block the grouped GEMMs work with (one tile row block = one expert): 128 for single-CTA
+    tiles, 256 for CTA-pair tiles."""
+    return int(N.lib().sb200_moe_block_rows()) * (2 if pairs else 1)
+
+
+def use_pair_tiles(num_slots: int, num_experts: int) -> bool:
+    """CTA-pair tiles (256-row expert blocks) once an expert sees 128 slots or more on average: a pair loads half of
+    the weight tile per SM, and the operand feed is what bounds these GEMMs, which outweighs the extra padding;
+    small batches keep 128-row blocks."""
+    return num_slots >= 128 * num_experts
 
 
 def fused_topk(hidden_states: torch.Tensor, gating_output: torch.Tensor, topk: int, renormalize: bool):
@@ -51,7 +59,7 @@ def moe_align_block_size(topk_ids: torch.Tensor, block_size: int, num_experts: i
     return sorted_ids, expert_ids, num_tokens_post_pad
 
 
-def _expert_slots(hidden_states, w1, w2, topk_weights, topk_ids, ids_in_range: bool = False):
+def _expert_slots(hidden_states, w1, w2, topk_weights, topk_ids, ids_in_range: bool = False, pairs: Optional[bool] = None):
     """Common part of fused_experts: returns out3 [T*k, H] (per-slot expert outputs, already scaled by
     the routed weights) for bf16/fp16 inputs.  ``ids_in_range``: the caller guarantees 0 <= id < E for
     every slot (ids produced by ``fused_topk``); otherwise the slots are zeroed first, because a slot whose
@@ -62,7 +70,9 @@ def _expert_slots(hidden_states, w1, w2, topk_weights, topk_ids, ids_in_range: b
     if K != H or w2.shape[0] != E or w2.shape[2] * 2 != two_d:
         raise RuntimeError("fused_experts: weight shapes do not match")
     dev, dt = hidden_states.device, hidden_states.dtype
-    blk = block_rows()
+    pairs = use_pair_tiles(T * k, E) if pairs is None else bool(pairs)
+    blk = block_rows(pairs)
+    cfg = 3256 if pairs else 0
     # capacity of the sorted order, rounded up to whole blocks (the grouped GEMMs address whole row blocks)
     rows_cap = (T * k + E * (blk - 1) + blk - 1) // blk * blk
     sorted_ids = torch.empty(rows_cap, dtype=torch.int32, device=dev)
@@ -76,11 +86,11 @@ def _expert_slots(hidden_states, w1, w2, topk_weights, topk_ids, ids_in_range: b
                                       T, H, k, N.dtype_id(hidden_states), N.stream_ptr()), "moe_gather_rows")
     act = torch.empty(rows_cap, two_d // 2, dtype=dt, device=dev)
     N.check(lib.sb200_moe_gemm1(N.ptr(act), N.ptr(xs), N.ptr(w1), N.ptr(expert_ids), N.ptr(num_post_pad), rows_cap, E,
-                                two_d, K, N.dtype_id(hidden_states), st, 0, N.stream_ptr()), "moe_gemm1")
+                                two_d, K, N.dtype_id(hidden_states), st, cfg, N.stream_ptr()), "moe_gemm1")
     out3 = (torch.empty if ids_in_range else torch.zeros)(T * k, w2.shape[1], dtype=dt, device=dev)
     N.check(lib.sb200_moe_gemm2(N.ptr(out3), N.ptr(act), N.ptr(w2), N.ptr(expert_ids), N.ptr(num_post_pad),
                                 N.ptr(sorted_ids), N.ptr(topk_weights), rows_cap, T * k, E, w2.shape[1], w2.shape[2],
-                                N.dtype_id(hidden_states), st, 0, N.stream_ptr()), "moe_gemm2")
+                                N.dtype_id(hidden_states), st, cfg, N.stream_ptr()), "moe_gemm2")
     return out3
 
 

@@ -1,8 +1,7 @@
 """The tensor-parallel region mappings of the reference
 (sarathi/model_executor/parallel_utils/tensor_parallel/mappings.py:266-279) as
-plain inference-time functions.  The all-reduce runs this library's own kernels
-over the symmetric heaps (comm.py); the all-gather, which is not on the decoder
-layer path, goes through torch.distributed."""
+plain inference-time functions.  The all-reduce and the all-gather run this
+library's own kernels over the symmetric heaps (comm.py)."""
 from __future__ import annotations
 
 import torch
@@ -75,11 +74,27 @@ def scatter_to_tensor_model_parallel_region(input_: torch.Tensor) -> torch.Tenso
 
 
 def gather_from_tensor_model_parallel_region(input_: torch.Tensor) -> torch.Tensor:
-    """Concatenate the ranks' shards along the last dimension (mappings.py:71-92)."""
+    """Concatenate the ranks' shards along the last dimension (mappings.py:71-92), e.g. the vocabulary slices of
+    the logits (layers/sampler.py:89-97).  Every rank's shard travels as one block of this library's all-gather
+    (multicast stores or peer loads over NVLink, comm.py); the blocks are then interleaved locally.  Shards whose
+    size is not a multiple of 16 bytes go through torch.distributed."""
     world = ps.get_tensor_model_parallel_world_size()
     if world == 1:
         return input_
-    import torch.distributed as dist
-    parts = [torch.empty_like(input_) for _ in range(world)]
-    dist.all_gather(parts, input_.contiguous(), group=ps.get_tensor_model_parallel_group())
-    return torch.cat(parts, dim=-1).contiguous()
+    shard = input_.contiguous()
+    es = shard.element_size()
+    width = _regroup_width(shard.numel(), es)
+    if width == 0 or not shard.is_cuda:
+        import torch.distributed as dist
+        parts = [torch.empty_like(shard) for _ in range(world)]
+        dist.all_gather(parts, shard, group=ps.get_tensor_model_parallel_group())
+        return torch.cat(parts, dim=-1).contiguous()
+    rows = shard.numel() // width
+    need = world * shard.numel() * es
+    comm = ps.get_tensor_model_parallel_comm(max(need, ps.DEFAULT_COMM_REGION_BYTES) if ps._TP_COMM is None else None)
+    if need > comm.region_bytes:
+        raise RuntimeError(f"gather_from_tensor_model_parallel_region: {need} bytes exceed the communication context's "
+                           f"regions ({comm.region_bytes}); create the context with a larger size first")
+    full = comm.all_gather_rows(shard.view(rows, width), world * rows)     # [world * rows, width]: rank-major blocks
+    blocks = full.view(world, *shard.shape)                                # [world, ..., d]
+    return torch.cat(list(blocks.unbind(0)), dim=-1)                       # [..., world * d], a new tensor

@@ -58,7 +58,18 @@ def _check_status():
 
 # tile configuration = BN + 1000*MI + 100000*splitK (0 = chosen by the library)
 TILE_CFGS = [0, 64, 96, 128, 160, 224, 256, 2064, 2128, 2256, 301128, 402256, 1602128, 200032,
-             3064, 3128, 3192, 3256, 203256, 503128, 4064, 4128, 4256, 304256]  # 3xxx/4xxx = CTA pairs (cta_group::2)
+             3064, 3128, 3192, 3256, 203256, 503128, 4064, 4128, 4256, 304256,  # 3xxx/4xxx = CTA pairs (cta_group::2)
+             205256, 205128, 405128, 205064, 405064, 405192]  # 5xxx = a cluster of 2 / 4 CTA pairs splits the K of every tile
+
+
+def _skip_unless_planned(epi, T, N, K, cfg, head_size=128):
+    """Cluster K-split configurations are only accepted for problems with few tiles (one cluster per tile)."""
+    from sarathi_serve_b200 import dense_ops
+    if (cfg // 1000) % 100 == 5:
+        try:
+            dense_ops.gemm_plan(epi, T, N, K, head_size, cfg)
+        except RuntimeError:
+            pytest.skip("this problem does not fit the cluster K-split configuration")
 
 
 @pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16, torch.float32])
@@ -71,6 +82,7 @@ def test_linear(dtype, tile_n, T, N, K):
         pytest.skip("tile shape applies to the tensor-core path only")
     if tile_n // 100000 > (K + 63) // 64:
         pytest.skip("more splits than k-blocks")
+    _skip_unless_planned(0, T, N, K, tile_n)
     x, w = _rand((T, K), dtype, T + N + K), _rand((N, K), dtype, 7 * N + K, 0.05)
     b = _rand((N,), dtype, 3)
     ref = x.float().cuda() @ w.float().cuda().t()
@@ -82,7 +94,7 @@ def test_linear(dtype, tile_n, T, N, K):
 
 
 @pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
-@pytest.mark.parametrize("tile_n", [0, 128, 3256, 203128, 2064])
+@pytest.mark.parametrize("tile_n", [0, 128, 3256, 203128, 2064, 205256, 405128])
 @pytest.mark.parametrize("T,N,K", [(512, 4096, 512), (65, 200, 264), (300, 1000, 1000), (1, 256, 512)])
 def test_linear_with_residual_in_the_epilogue(dtype, tile_n, T, N, K):
     """out = residual + round(x w^T + b): the reference's `hidden_states = residual + hidden_states` after a
@@ -91,6 +103,7 @@ def test_linear_with_residual_in_the_epilogue(dtype, tile_n, T, N, K):
     from sarathi_serve_b200 import dense_ops
     if tile_n // 100000 > (K + 63) // 64:
         pytest.skip("more splits than k-blocks")
+    _skip_unless_planned(0, T, N, K, tile_n)
     x, w = _rand((T, K), dtype, T + N + K), _rand((N, K), dtype, 7 * N + K, 0.05)
     b, r = _rand((N,), dtype, 3), _rand((T, N), dtype, 4)
     ref = r + O.linear(x.float(), w.float(), b.float()).to(dtype)
@@ -133,7 +146,8 @@ def test_linear_rejects_misaligned_stride():
 @pytest.mark.parametrize("tile_n", [0, 256, 2256, 401256, 302256, 3256, 303256, 4256, 204128,
                                     # 64-column tiles: for NeoX heads wider than 64 a tile holds 32 + 32 columns of
                                     # the two halves of a head, so that every rotation pair sits in one accumulator
-                                    64, 2064, 3064, 4064, 303064, 600064])
+                                    64, 2064, 3064, 4064, 303064, 600064,
+                                    205128, 405128, 205064, 405256])
 @pytest.mark.parametrize("T,nq,nkv,hd,K", [(512, 4, 1, 128, 4096), (288, 8, 2, 64, 1024), (65, 2, 2, 128, 512),
                                            (7, 1, 1, 256, 256)])
 def test_linear_rotary(dtype, neox, tile_n, T, nq, nkv, hd, K):
@@ -146,6 +160,7 @@ def test_linear_rotary(dtype, neox, tile_n, T, nq, nkv, hd, K):
     split_head = neox and tile_n % 1000 == 64 and hd > 64
     if tile_n // 100000 > (K + 63) // 64 or (tile_n and (tile_n % 1000) % hd and not split_head):
         pytest.skip("tile configuration does not fit this case")
+    _skip_unless_planned(1, T, (nq + 2 * nkv) * hd, K, tile_n, hd)
     out = dense_ops.linear_rotary(x.cuda(), w.cuda(), pos.cuda(), cache.cuda(), hd, (nq + nkv) * hd, neox,
                                   tile_n=tile_n)
     _check_status()
@@ -159,12 +174,14 @@ def test_linear_rotary(dtype, neox, tile_n, T, nq, nkv, hd, K):
 
 
 @pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
-@pytest.mark.parametrize("tile_n", [0, 64, 128, 192, 256, 2128, 2256, 501256, 402128, 3064, 3128, 3256, 403256, 4128, 4256, 304256])
+@pytest.mark.parametrize("tile_n", [0, 64, 128, 192, 256, 2128, 2256, 501256, 402128, 3064, 3128, 3256, 403256, 4128, 4256, 304256,
+                                    205256, 405128, 205064])
 @pytest.mark.parametrize("T,d,K", [(512, 1792, 4096), (288, 1408, 1024), (65, 96, 512), (1, 64, 64)])
 def test_linear_silu_mul(dtype, tile_n, T, d, K):
     from sarathi_serve_b200 import dense_ops
     if tile_n // 100000 > (K + 63) // 64:
         pytest.skip("more splits than k-blocks")
+    _skip_unless_planned(2, T, 2 * d, K, tile_n)
     x, w = _rand((T, K), dtype, T + K), _rand((2 * d, K), dtype, d, 0.05)
     out = dense_ops.linear_silu_mul(x.cuda(), w.cuda(), tile_n=tile_n)
     _check_status()

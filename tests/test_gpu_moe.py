@@ -63,6 +63,30 @@ def test_fused_experts_token_counts(T):
     assert rel_err(out, O.fused_experts(x, w13, w2, ow, oids.long())) <= 2e-2
 
 
+@pytest.mark.parametrize("T", [1, 129, 300, 1024])
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+def test_expert_gemms_on_cta_pair_tiles_equal_single_cta_tiles(T, dtype):
+    """The grouped GEMMs on CTA-pair tiles (256-row expert blocks) against the single-CTA tiles (128-row blocks) and
+    the oracle: the alignment differs, the per-slot results must not."""
+    from sarathi_serve_b200 import fused_moe as FM
+    g = torch.Generator().manual_seed(T + 1)
+    H, I, E, k = 256, 384, 8, 2
+    x = torch.randn(T, H, generator=g).to(dtype).cuda()
+    w13 = (torch.randn(E, 2 * I, H, generator=g) * 0.05).to(dtype).cuda()
+    w2 = (torch.randn(E, H, I, generator=g) * 0.05).to(dtype).cuda()
+    logits = torch.randn(T, E, generator=g)
+    logits[:, 5] = -30.0
+    wts, ids = FM.fused_topk(x, logits.cuda(), k, True)
+    single = FM._expert_slots(x, w13, w2, wts, ids, True, pairs=False)
+    pair = FM._expert_slots(x, w13, w2, wts, ids, True, pairs=True)
+    _check_status()
+    assert torch.equal(pair, single)
+    ow, oids, _ = O.topk_softmax(logits, k, renormalize=True)
+    ref = O.fused_experts(x.cpu(), w13.cpu(), w2.cpu(), ow, oids.long())
+    assert rel_err(pair.view(T, k, H).float().sum(1), ref.float()) <= 2e-2
+    assert FM.use_pair_tiles(2048, 8) and not FM.use_pair_tiles(154, 8)
+
+
 def test_mixtral_moe_block_tp1():
     """MixtralMoE module (gate + FusedMoE) at tensor-parallel size 1 against the oracle's MoE layer."""
     from sarathi_serve_b200 import parallel_state as ps

@@ -122,7 +122,10 @@ def _body_all_reduce(rank, world):
             zref = (resid.float() + (total.to(dtype).float() + bias.float()).to(dtype).float()).to(dtype)
             zf = zref.float()
             yref = ((zf * torch.rsqrt(zf.pow(2).mean(-1, keepdim=True) + 1e-5)).to(dtype) * w)
-            assert _rel(z2, zref) <= tol, ("z", dtype, T, H)
+            # (the in-switch reduction of the multicast scheme rounds the fp32 sum to the 16-bit type with its own
+            #  tie rule: about 5e-5 of the sums differ from round-to-nearest-even by one unit in the last place,
+            #  which the bias and residual adds can carry to two units -- the bound is twice the plain sum's)
+            assert _rel(z2, zref) <= max(tol, 1e-4) * 2, ("z", dtype, T, H)
             assert _rel(y2, yref) <= max(tol, 1e-4) * 2, ("y", dtype, T, H)
             # heap views of the same call agree with the copies
             y3, z3 = comm.all_reduce(x, bias=bias.cuda(), residual=resid.cuda(), norm_weight=w.cuda(), eps=1e-5)
@@ -137,13 +140,19 @@ def _body_rowpar(rank, world):
                                  (torch.float32, 2e-5, 4 << 20)):
         comm.set_one_shot_bytes(one_shot)  # the library's threshold / never one-shot / always one-shot
         for T, H, K in ((512, 4096, 1024), (288, 1024, 704), (65, 256, 64), (1, 128, 512), (130, 4096, 7168), (96, 8192, 256)):
-            for tile_n in (0, 128, 2256, 302128, 3256, 203128, 4256, 204128):
+            for tile_n in (0, 128, 2256, 302128, 3256, 203128, 4256, 204128, 205256, 405128):
                 if dtype == torch.float32 and tile_n != 0:
                     continue
-                if world > 2 and (dtype == torch.float16 or tile_n not in (0, 302128, 3256, 203128)):
+                if world > 2 and (dtype == torch.float16 or tile_n not in (0, 302128, 3256, 203128, 205256)):
                     continue  # larger groups: a reduced set keeps the multi-GPU run short
                 if tile_n // 100000 > (K + 63) // 64:
                     continue
+                if (tile_n // 1000) % 100 == 5:  # cluster K-split: only problems with one cluster per tile
+                    from sarathi_serve_b200 import dense_ops
+                    try:
+                        dense_ops.gemm_plan(3, T, H, K, 128, tile_n)
+                    except RuntimeError:
+                        continue
                 g = torch.Generator().manual_seed(T + H + K)
                 X = torch.randn(T, K * world, generator=g).to(dtype)
                 W = (torch.randn(H, K * world, generator=g) * 0.05).to(dtype)
@@ -389,6 +398,15 @@ def _body_all_gather(rank, world):
             # interleaved with a sum: the two kinds of collective share the flags and the call counter
             s_, _ = comm.all_reduce(out)
             assert _rel(s_, full.float() * world) <= 1e-2
+    # gather_from_tensor_model_parallel_region: shards concatenated along the LAST dimension (the logits gather of
+    # the sampler, layers/sampler.py:89-97), through the same kernel
+    from sarathi_serve_b200.mappings import gather_from_tensor_model_parallel_region
+    for shape in ((13, 16032), (5, 3, 64), (1, 8)):
+        g = torch.Generator().manual_seed(sum(shape))
+        shards = [torch.randn(*shape, generator=g).to(torch.bfloat16) for _ in range(world)]
+        _host_barrier()
+        got = gather_from_tensor_model_parallel_region(shards[rank].cuda())
+        assert torch.equal(got.cpu(), torch.cat(shards, dim=-1)), shape
     comm.check_status()
 
 
