@@ -12,7 +12,8 @@ from ctypes import c_char_p, c_float, c_int, c_int64, c_void_p
 import torch
 
 _PKG = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(_PKG, "libsarathi_b200.so")
+# SB200_LIBRARY: load another build of the library (e.g. the profiling variant of `build.py --trace`)
+LIB_PATH = os.environ.get("SB200_LIBRARY") or os.path.join(_PKG, "libsarathi_b200.so")
 
 F32, F16, BF16 = 0, 1, 2
 I32, I64, I16, I8, U8 = 0, 1, 2, 3, 4

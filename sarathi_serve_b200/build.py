@@ -47,21 +47,23 @@ def _headers_mtime() -> float:
     return max(os.path.getmtime(h) for h in hs)
 
 
-def build(force: bool = False, verbose: bool = False) -> str:
-    os.makedirs(OBJ, exist_ok=True)
+def build(force: bool = False, verbose: bool = False, defines=(), lib: str = LIB, obj_dir: str = OBJ) -> str:
+    """``defines``: extra -D macros, e.g. ("SB200_TRACE",) for a profiling build whose collective kernels record
+    per-phase time stamps (give such a build its own ``lib`` / ``obj_dir``; ``SB200_LIBRARY`` makes the package load it)."""
+    os.makedirs(obj_dir, exist_ok=True)
     nvcc = _nvcc()
     hm = _headers_mtime()
     todo, objs = [], []
     for f in sources():
         src = os.path.join(CSRC, f)
-        obj = os.path.join(OBJ, f[:-3] + ".o")
+        obj = os.path.join(obj_dir, f[:-3] + ".o")
         objs.append(obj)
         if force or not os.path.exists(obj) or os.path.getmtime(obj) < max(os.path.getmtime(src), hm):
             todo.append((src, obj))
 
     def compile_one(job):
         src, obj = job
-        cmd = [nvcc, *NVCC_FLAGS, "-c", src, "-o", obj]
+        cmd = [nvcc, *NVCC_FLAGS, *[f"-D{d}" for d in defines], "-c", src, "-o", obj]
         r = subprocess.run(cmd, capture_output=True, text=True)
         log = obj[:-2] + ".ptxas.log"
         with open(log, "w") as fh:
@@ -75,18 +77,24 @@ def build(force: bool = False, verbose: bool = False) -> str:
     if todo:
         with ThreadPoolExecutor(min(len(todo), os.cpu_count() or 1)) as ex:
             list(ex.map(compile_one, todo))
-    if todo or not os.path.exists(LIB):
-        cmd = [nvcc, "-shared", "-o", LIB, *objs, "-gencode", "arch=compute_100a,code=sm_100a", "-lcudart"]
+    if todo or not os.path.exists(lib):
+        cmd = [nvcc, "-shared", "-o", lib, *objs, "-gencode", "arch=compute_100a,code=sm_100a", "-lcudart"]
         r = subprocess.run(cmd, capture_output=True, text=True)
         if r.returncode != 0:
             raise RuntimeError(f"link failed:\n{r.stdout}\n{r.stderr}")
-    return LIB
+    return lib
 
 
 if __name__ == "__main__":
     ap = argparse.ArgumentParser()
     ap.add_argument("--force", action="store_true")
     ap.add_argument("--verbose", action="store_true")
+    ap.add_argument("--trace", metavar="DIR", default=None,
+                    help="build a profiling variant (-DSB200_TRACE) into DIR/libsarathi_b200_trace.so instead")
     a = ap.parse_args()
-    print(build(a.force, a.verbose))
+    if a.trace:
+        print(build(a.force, a.verbose, defines=("SB200_TRACE",), lib=os.path.join(a.trace, "libsarathi_b200_trace.so"),
+                    obj_dir=os.path.join(a.trace, "obj")))
+    else:
+        print(build(a.force, a.verbose))
     sys.exit(0)

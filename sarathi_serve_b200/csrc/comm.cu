@@ -20,6 +20,7 @@ struct sb200_comm {
   bool own_heap;
   bool ipc_opened[sb200::kMaxRanks];
   void* mc;          // multicast alias of all ranks' heaps (NVSwitch), or null
+  int mc_pull;       // multicast scheme: finished rows are pulled by the peers instead of multicast-stored
   uint64_t seq;
   long long wait_cycles;
   unsigned long long* trace;
@@ -178,6 +179,7 @@ static int plan_call(sb200_comm* c, int64_t T_, int64_t H, int dtype, const void
   a.one_shot = (c->world == 1 || (size_t)(c->world - 1) * T_ * H * es <= c->one_shot_bytes) ? 1 : 0;
   // larger ones go through the NVSwitch multicast alias when the heaps are bound to one
   a.use_mc = (!a.one_shot && c->mc != nullptr) ? 1 : 0;
+  a.mc_pull = c->mc_pull;
   a.bias = bias; a.residual = residual; a.norm_w = norm_w; a.eps = eps;
   a.write_resid_all = write_resid_all;
   a.out_copy = out_copy; a.resid_copy = resid_copy;
@@ -239,6 +241,7 @@ static int comm_new(sb200_comm** out, int rank, int world, int64_t region_bytes)
   c->wait_cycles = 5 * ptx::kWaitLimitCycles;  // ~10 s: ranks of a serving engine can be seconds apart on the host (first steps, GC)
   c->one_shot_bytes = 4u << 20;
   if (const char* e = getenv("SB200_ONE_SHOT_BYTES")) c->one_shot_bytes = (size_t)atoll(e);
+  if (const char* e = getenv("SB200_MC_PULL")) c->mc_pull = atoi(e) != 0 ? 1 : 0;
   if (const char* e = getenv("SB200_WAIT_LIMIT_CYCLES")) { const long long v = atoll(e); if (v > 0) c->wait_cycles = v; }
   if (cudaGetDevice(&c->device) != cudaSuccess) { delete c; set_error("comm_create: no current CUDA device"); return SB200_ERR_CUDA; }
   *out = c;

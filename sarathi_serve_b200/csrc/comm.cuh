@@ -181,6 +181,8 @@ struct ReduceArgs {
                           // trip over the links instead of two; pays off while (world-1)*T*H bytes is small); 0: rows
                           // are reduced by their owners and gathered afterwards
   int use_mc;             // 1 (only with one_shot = 0): owners reduce and publish through the NVSwitch multicast alias
+  int mc_pull;            // with use_mc: owners keep their finished rows in their own heap and the peers pull them (peer
+                          // loads), instead of multicast stores followed by a system-scope fence in every CTA
   uint32_t push_expected[kMaxRanks];  // arrivals this rank's own kernel reports per destination owner
                                       // (epilogue warp-tiles of the GEMM, or CTAs of the all-reduce); one-shot and
                                       // multicast calls count all arrivals in [0]
@@ -193,7 +195,7 @@ struct ReduceArgs {
   void* resid_copy;       // optional local [T, H] tensor that receives z when norm_w != null
   long long wait_cycles;
 #ifdef SB200_TRACE
-  unsigned long long* trace;  // [gridDim.x][8] nanosecond time stamps of the phases (profiling builds only)
+  unsigned long long* trace;  // [gridDim.x][16] nanosecond time stamps of the phases (profiling builds only)
 #endif
 };
 
@@ -205,7 +207,7 @@ __device__ __forceinline__ unsigned long long global_ns() {
 }
 // Thread 0 of every CTA records when it passed phase boundary `slot`.
 __device__ __forceinline__ void trace_mark(const ReduceArgs& a, int slot) {
-  if (a.trace && threadIdx.x == 0) a.trace[(size_t)blockIdx.x * 8 + slot] = global_ns();
+  if (a.trace && threadIdx.x == 0) a.trace[(size_t)blockIdx.x * 16 + slot] = global_ns();
 }
 #else
 __device__ __forceinline__ void trace_mark(const ReduceArgs&, int) {}
@@ -539,6 +541,7 @@ __device__ __forceinline__ void mc_reduce_rows(const CommView& c, const ReduceAr
   T* mc_out = (T*)(c.mc + c.out_off[a.set]);
   T* mc_res = (T*)(c.mc + c.resid_off[a.set]);
   T* my_res = (T*)(c.heap[c.rank] + c.resid_off[a.set]);
+  T* my_out = (T*)(c.heap[c.rank] + c.out_off[a.set]);
   Vec16<T> x[VPL];
   auto load_row = [&](size_t row_off) {
 #pragma unroll
@@ -565,13 +568,18 @@ __device__ __forceinline__ void mc_reduce_rows(const CommView& c, const ReduceAr
       for (int j = 0; j < N; ++j) acc[j] = DT<T>::to_f(x[b].v[j]);
       ss += finish_vec<T>(acc, bias ? &bv : nullptr, resid ? &rv : nullptr, &z[b]);
     }
+    trace_mark(a, 7);  // the row's sum has arrived from the switch
     if (lr + num_ctas < nrows) load_row((size_t)(row0 + lr + num_ctas) * a.H);
 #pragma unroll
     for (int b = 0; b < VPL; ++b) {
       const int v = vbase + vstep * b;
       if (v >= nvec) continue;
       const size_t e = row_off + (size_t)v * N;
-      if (!nw) {
+      if (a.mc_pull && (!nw || a.write_resid_all)) {
+        st16((nw ? my_res : my_out) + e, z[b]);            // kept here; the peers pull it
+        T* zc = (T*)(nw ? a.resid_copy : a.out_copy);
+        if (zc) st16(zc + e, z[b]);
+      } else if (!nw) {
         mc_st16(mc_out + e, z[b].raw);                     // z is the primary result: every rank gets it
       } else if (a.write_resid_all) {
         mc_st16(mc_res + e, z[b].raw);
@@ -602,9 +610,15 @@ __device__ __forceinline__ void mc_reduce_rows(const CommView& c, const ReduceAr
 #pragma unroll
         for (int j = 0; j < N; ++j)
           y.v[j] = DT<T>::from_f(rt<T>(DT<T>::to_f(z[b].v[j]) * inv) * DT<T>::to_f(w[b].v[j]));
-        mc_st16(mc_out + row_off + (size_t)v * N, y.raw);
+        if (a.mc_pull) {
+          st16(my_out + row_off + (size_t)v * N, y);
+          if (a.out_copy) st16((T*)a.out_copy + row_off + (size_t)v * N, y);
+        } else {
+          mc_st16(mc_out + row_off + (size_t)v * N, y.raw);
+        }
       }
     }
+    trace_mark(a, 8);  // the finished row has been issued to the switch
   }
 }
 
@@ -676,13 +690,15 @@ __device__ void mc_reduce_gather_phase(const CommView& c, const ReduceArgs& a, i
     // multicast store.
     team_barrier(15, 32 * kReduceWarps);
     if (threadIdx.x == 0) {
-      fence_sys();
+      if (!a.mc_pull) fence_sys();  // (local stores are covered by the flag's release)
+      trace_mark(a, 9);  // this CTA's multicast stores are performed
       if (arrive_acq_rel(comm_counter(c, c.rank, CC_LOCAL_DONE)) + 1u == (uint32_t)ctas_with_rows)
         mc_st_release_u32(comm_counter_mc(c, done_flag_index(n, c.rank)), n);
     }
     trace_mark(a, 4);
   }
-  mc_wait_all_done<T>(c, a, n, cta, num_ctas);
+  if (a.mc_pull) gather_phase<T>(c, a, cta, num_ctas);  // own rows: already in place, with the caller's copies
+  else mc_wait_all_done<T>(c, a, n, cta, num_ctas);
 }
 
 // The phases after the partial rows have been produced, for whichever scheme the call uses.

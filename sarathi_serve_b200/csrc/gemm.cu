@@ -92,11 +92,14 @@ GemmPlan plan_gemm(int epi, int64_t M, int64_t N, int64_t K, int head_size, int 
     const int n_tiles = (int)((out_cols + cols_per_tile - 1) / cols_per_tile);
     const int64_t tiles = (int64_t)m_tiles * n_tiles;
     const int stages = gemm_max_stages(1, bn, 1);
-    const size_t exchange = (size_t)(sp - 1) * bn * 128 * sizeof(float);  // partial accumulators parked in one CTA
+    // room in every CTA's stage ring for the chunks it sends and the chunks it receives
+    const bool split_tile = epi == EPI_ROTARY && bn < head_size;
+    const int units_of_tile = (epi == EPI_SILU_MUL || split_tile) ? bn / 64 : bn / 32;
+    const size_t exchange = 2 * (size_t)(sp - 1) * xchg_area_bytes(units_of_tile, sp, (epi == EPI_SILU_MUL || epi == EPI_ROTARY) ? 2 : 1);
     if (tiles * 2 * sp > sms || k_blocks < sp || stages < 2 || exchange > (size_t)stages * gemm_stage_bytes(1, bn, 1)) return p;
     p.cta2 = 1; p.mi = 1; p.bn = bn; p.units = (int)tiles; p.tiles_full = (int)tiles; p.rem_splits = 1; p.rem_units = 0;
     p.stages = stages; p.m_tiles = m_tiles; p.n_tiles = n_tiles; p.k_blocks = k_blocks; p.cluster_split = sp;
-    p.est_clocks = 9000.0 + (double)((k_blocks + sp - 1) / sp) * (2.0 * bn > 260.0 ? 2.0 * bn : 260.0) + exchange / 32.0;
+    p.est_clocks = 9000.0 + (double)((k_blocks + sp - 1) / sp) * (2.0 * bn > 260.0 ? 2.0 * bn : 260.0) + exchange / 2.0 / 64.0;
     return p;
   }
   double best_cost = 1e30;
@@ -159,6 +162,7 @@ GemmPlan plan_gemm(int epi, int64_t M, int64_t N, int64_t K, int head_size, int 
           gs = rem_t * sp < units_max ? rem_t * sp : units_max;
           if (gs > W / 2) gs = W / 2;          // at least two k-blocks per unit
           if (gs <= rem_t) continue;           // degenerates to whole tiles
+          if (!sk_fits_32bit(k_blocks, rem_t, gs)) continue;  // the kernel's scheduling arithmetic is 32-bit
           if (tiles < units_max) units = gs;
           const size_t need = kWsCounterBytes + (size_t)(gs + rem_t) * bm * bn * sizeof(float);
           if (need > ws_bytes || (size_t)rem_t * 32 * sizeof(uint32_t) > kWsCounterBytes) continue;
@@ -189,7 +193,8 @@ GemmPlan plan_gemm(int epi, int64_t M, int64_t N, int64_t K, int head_size, int 
 
 // Arrivals the row-parallel kernel of a rank counts for the rank that owns
 // rows [lo, hi): one per (tile, epilogue slot whose 32 rows overlap the range), times the number of
-// K-parts for tiles that are cut (every part finishes a share of such a tile and reports it).
+// K-parts for tiles that are cut or split inside a cluster (every part finishes a share of such a tile and
+// reports it).
 uint32_t gemm_push_increments(const GemmPlan& p, int64_t M, int64_t lo, int64_t hi) {
   if (hi <= lo) return 0;
   const int bm = (p.cta2 ? 256 : 128) * p.mi;
@@ -209,6 +214,7 @@ uint32_t gemm_push_increments(const GemmPlan& p, int64_t M, int64_t lo, int64_t 
     for (int64_t t = mt; t < tiles; t += p.m_tiles) {
       int first = 0, parts = 1;
       if (t >= p.tiles_full) sk_tile_parts(p.k_blocks, (int)(tiles - p.tiles_full), p.rem_units, (int)(t - p.tiles_full), &first, &parts);
+      if (p.cluster_split > 1) parts = p.cluster_split;  // every pair of the cluster finishes a share of the tile
       weight += (uint64_t)parts;
     }
     total += (uint64_t)groups * slots_per_group * weight;
@@ -250,7 +256,7 @@ static int launch_sm100(const CUtensorMap& ta, const CUtensorMap& tb, const Gemm
     SB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBudget));
     configured_dev = dev;
   }
-  const int smem = g.stages * gemm_stage_bytes(g.mi, g.bn, CTA2 ? 1 : 0) + kBarrierBytes + 1024;
+  const int smem = g.stages * gemm_stage_bytes(g.mi, g.bn, CTA2 ? 1 : 0) + kBarrierBytes + kEpiStageBytes + 1024;
   int grid = g.units;
   if (grid < 1) grid = 1;
   const int pairs_per_unit = (CTA2 && g.cluster_split > 1) ? g.cluster_split : 1;
@@ -429,6 +435,16 @@ extern "C" int sb200_gemm_colpar(void* out, int64_t ldo, const void* x, int64_t 
                                   epi == EPI_ROTARY ? g.is_neox : 1);
   return run_gemm_sm100(dtype, epi, plan, x, ldx, w, ldw, g, workspace, cv, ra, s);
 }
+
+#ifdef SB200_TRACE
+// profiling builds only: the phase time stamps (ns) CTA 0 of the last 64 GEMM launches recorded, and the launch count
+extern "C" int sb200_debug_gemm_trace(unsigned long long* host_out /*[64][16]*/, unsigned int* launches) {
+  SB_CUDA(cudaDeviceSynchronize());
+  SB_CUDA(cudaMemcpyFromSymbol(host_out, g_gemm_trace, sizeof(unsigned long long) * 64 * 16));
+  SB_CUDA(cudaMemcpyFromSymbol(launches, g_gemm_trace_launch, sizeof(unsigned int)));
+  return SB200_OK;
+}
+#endif
 
 // The tile shape and schedule sb200_gemm_colpar / sb200_gemm_rowpar would use (for tuning and tests).
 // out[0..11] = cta2, mi, bn, units, tiles_full, rem_splits, rem_units, stages, m_tiles, n_tiles, k_blocks, cluster_split.

@@ -46,6 +46,23 @@
 
 namespace sb200 {
 
+#ifdef SB200_TRACE
+// profiling builds: CTA 0 of every GEMM launch records %globaltimer at its phase boundaries, launch after launch
+// (slot = launch ordinal modulo 64); read back with sb200_debug_gemm_trace.
+__device__ unsigned long long g_gemm_trace[64][16];
+__device__ unsigned int g_gemm_trace_launch;
+#define SB_GEMM_MARK(slot)                                                                          \
+  do {                                                                                              \
+    if (blockIdx.x == 0) {                                                                          \
+      unsigned long long t__;                                                                       \
+      asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t__) :: "memory");                           \
+      g_gemm_trace[gemm_trace_row % 64][slot] = t__;                                                \
+    }                                                                                               \
+  } while (0)
+#else
+#define SB_GEMM_MARK(slot) do { } while (0)
+#endif
+
 enum GemmEpilogue { EPI_STORE = 0, EPI_ROTARY = 1, EPI_SILU_MUL = 2, EPI_PUSH = 3, EPI_MOE_SCATTER = 4 };
 
 constexpr int kBK = 64;            // K elements per stage: 128 bytes of bf16 = one swizzle row
@@ -53,6 +70,8 @@ constexpr int kGemmThreads = 320;  // 10 warps
 constexpr int kEpiWarps = 8;
 constexpr int kSmemBudget = 226 * 1024;  // dynamic shared memory requested (static use is a few bytes)
 constexpr int kBarrierBytes = 1024;
+constexpr int kEpiWarpStageBytes = 32 * 64;  // per epilogue warp: 32 rows x 32 sixteen-bit values, to transpose stores
+constexpr int kEpiStageBytes = 8 * kEpiWarpStageBytes;
 
 struct GemmArgs {
   int M, N, K;             // N counts B rows (for EPI_SILU_MUL: 2*d)
@@ -104,8 +123,13 @@ struct GemmArgs {
 __host__ __device__ inline int gemm_stage_bytes(int mi, int bn, int cta2 = 0) {
   return cta2 ? (mi * 128 + bn / 2) * kBK * 2 : (mi * 128 + bn) * kBK * 2;
 }
+// Cluster K-split: bytes of one pair's share of an accumulator (its units, `chunks_per_unit` 16 KiB chunks each);
+// a CTA needs 2 * (split - 1) such areas inside its stage ring (what it sends, what it receives).
+__host__ __device__ inline uint32_t xchg_area_bytes(int units, int split, int chunks_per_unit) {
+  return (uint32_t)((units + split - 1) / split * chunks_per_unit) * (uint32_t)(128 * 32 * sizeof(float));
+}
 __host__ __device__ inline int gemm_max_stages(int mi, int bn, int cta2 = 0) {
-  int s = (kSmemBudget - kBarrierBytes - 1024) / gemm_stage_bytes(mi, bn, cta2);
+  int s = (kSmemBudget - kBarrierBytes - kEpiStageBytes - 1024) / gemm_stage_bytes(mi, bn, cta2);
   return s > 8 ? 8 : s;
 }
 
@@ -143,6 +167,44 @@ __device__ __forceinline__ void store_row32(T* dst, const float* f, int valid_co
   }
 }
 
+// The same store done by the whole warp.  After a TMEM load a thread holds 32 values of ITS row, so a plain
+// per-thread store makes every 16-byte store instruction of the warp touch 32 different 128-byte lines (the
+// epilogue of a 128x128 tile then spends ~2000 clocks in the load/store unit).  Here the warp transposes the
+// 32 x 64-byte block through its private 2 KiB of shared memory (16-byte chunk c of row r kept at
+// c ^ ((r >> 1) & 3): conflict-free both ways) and stores it so that four lanes cover one row's 64 bytes.
+// Called by all 32 lanes; `row_ok` = this lane's row is to be stored, `dst` = its first element.
+template <typename T>
+__device__ __forceinline__ void warp_store_rows32(uint8_t* stage, T* dst, const float* f, int valid_cols, bool vec_ok,
+                                                  bool row_ok) {
+  const int lane = threadIdx.x & 31;
+  if (valid_cols >= 32 && vec_ok) {  // warp-uniform
+    const uint32_t sbase = ptx::smem_u32(stage);
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {
+      const uint32_t a = sbase + (uint32_t)(lane * 64 + ((q ^ ((lane >> 1) & 3)) << 4));
+      asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(a), "r"(Pack2<T>::pack(f[q * 8 + 0], f[q * 8 + 1])),
+                   "r"(Pack2<T>::pack(f[q * 8 + 2], f[q * 8 + 3])), "r"(Pack2<T>::pack(f[q * 8 + 4], f[q * 8 + 5])),
+                   "r"(Pack2<T>::pack(f[q * 8 + 6], f[q * 8 + 7]))
+                   : "memory");
+    }
+    const unsigned ok_mask = __ballot_sync(0xffffffffu, row_ok);  // (also orders the shared-memory stores above)
+    __syncwarp();
+    const int chunk = lane & 3;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const int row = i * 8 + (lane >> 2);
+      uint4 v;
+      const uint32_t a = sbase + (uint32_t)(row * 64 + ((chunk ^ ((row >> 1) & 3)) << 4));
+      asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(a) : "memory");
+      T* p = reinterpret_cast<T*>(__shfl_sync(0xffffffffu, reinterpret_cast<unsigned long long>(dst), row));
+      if ((ok_mask >> row) & 1u) *reinterpret_cast<uint4*>(p + chunk * 8) = v;
+    }
+    __syncwarp();  // the block is read before the warp's next unit overwrites it
+  } else if (row_ok) {
+    store_row32<T>(dst, f, valid_cols, false);
+  }
+}
+
 template <typename T>
 __device__ __forceinline__ void load_row32(const T* src, float* f) {
 #pragma unroll
@@ -156,31 +218,37 @@ __device__ __forceinline__ void load_row32(const T* src, float* f) {
 // Where an epilogue warp gets the fp32 accumulator chunk (32 columns of its row) from.
 struct TmemSource {
   uint32_t row_addr;  // TMEM address of (lane quarter, first column of the accumulator)
-  __device__ __forceinline__ void load32(int col, float* f) const {
+  __device__ __forceinline__ void load32(int col, float* f, int /*chunk_of_unit*/ = 0) const {
     uint32_t r[32];
     ptx::tmem_ld_32x32(row_addr + (uint32_t)col, r);
 #pragma unroll
     for (int j = 0; j < 32; ++j) f[j] = __uint_as_float(r[j]);
   }
 };
-// Cluster K-split: the accumulator chunk of pair 0 (TMEM) plus the partial accumulators the other pairs of the
-// cluster left in this CTA's shared memory, laid out [part][column][128 rows] so that the 32 lanes of a warp
-// (32 consecutive rows) read one 128-byte line per column.  Parts are added in order: the result does not
-// depend on timing.
+// Cluster K-split: this pair's accumulator chunk (TMEM) plus the partial accumulators the other pairs of the
+// cluster copied into this CTA's shared memory.  An exchanged chunk is a block of [128 rows][32 fp32] = 16 KiB
+// (a warp's 32 rows: 4 KiB of it) with the 16-byte pieces of a row permuted (piece j of row r at j ^ (r & 7)):
+// the 32 lanes of a warp hold 32 consecutive rows, so its 16-byte accesses touch every bank once per quarter
+// warp.  Parts are added in the order of their pairs: the result does not depend on timing.
+constexpr uint32_t kXchgChunkBytes = 128 * 32 * sizeof(float);
 struct TmemPlusSmemSource {
   uint32_t row_addr;
-  const float* sm;  // this thread's row in the first partial: element (part, col) at ((part * bn + col) * 128)
-  int parts;        // partials in shared memory (cluster_split - 1)
-  int bn;
-  __device__ __forceinline__ void load32(int col, float* f) const {
+  const uint8_t* sm;   // this thread's row in the first chunk of the unit, first source pair
+  int parts;           // partials in shared memory (cluster_split - 1)
+  uint32_t part_bytes; // distance between the source pairs' areas
+  __device__ __forceinline__ void load32(int col, float* f, int chunk_of_unit) const {
     uint32_t r[32];
     ptx::tmem_ld_32x32(row_addr + (uint32_t)col, r);
 #pragma unroll
     for (int j = 0; j < 32; ++j) f[j] = __uint_as_float(r[j]);
+    const int sw = (int)(threadIdx.x & 7);
     for (int p = 0; p < parts; ++p) {
-      const float* base = sm + (size_t)(p * bn + col) * 128;
+      const uint8_t* rowp = sm + (size_t)p * part_bytes + (size_t)chunk_of_unit * kXchgChunkBytes;
 #pragma unroll
-      for (int j = 0; j < 32; ++j) f[j] += base[(size_t)j * 128];
+      for (int j = 0; j < 8; ++j) {
+        const float4 v = *reinterpret_cast<const float4*>(rowp + ((j ^ sw) << 4));
+        f[4 * j] += v.x; f[4 * j + 1] += v.y; f[4 * j + 2] += v.z; f[4 * j + 3] += v.w;
+      }
     }
   }
 };
@@ -198,6 +266,7 @@ struct TmemPlusSmemSource {
 // cannot form a cycle.
 struct Sched {
   int G, tiles_full, rem_tiles, Gs, k_blocks;
+  int rounds;  // tiles_full / G: whole-tile work items of every unit
 };
 struct Segment {
   int tile, kb0, kb1;
@@ -219,37 +288,51 @@ __host__ __device__ inline void sk_tile_parts(int k_blocks, int rem_tiles, int G
   *first_unit = pf;
   *parts = pl - pf + 1;
 }
+// True when the device-side scheduling arithmetic below, which runs in 32 bits (a 64-bit division costs
+// the one thread that feeds the pipeline about 0.1 us, and there were six of them on the way to the
+// first load), cannot overflow for this plan.
+__host__ __device__ inline bool sk_fits_32bit(long long k_blocks, long long rem_tiles, long long Gs) {
+  return (rem_tiles + 1) * k_blocks * (Gs + 1) < (1ll << 31);
+}
 // it-th work item of unit p.
 __device__ __forceinline__ Segment segment_of(const Sched& sc, int p, int it) {
   Segment sg;
   sg.valid = true;
-  const int nA = sc.tiles_full / sc.G;
-  if (it < nA) {
+  sg.kb0 = 0; sg.kb1 = sc.k_blocks; sg.parts = 1; sg.part_slot = 0; sg.first_slot = 0; sg.rem_index = 0;
+  if (it < sc.rounds) {
     sg.tile = p + it * sc.G;
-    sg.kb0 = 0; sg.kb1 = sc.k_blocks; sg.parts = 1; sg.part_slot = 0; sg.first_slot = 0; sg.rem_index = 0;
     return sg;
   }
   sg.valid = false;
   if (p >= sc.Gs || sc.rem_tiles == 0) return sg;
-  const long long W = (long long)sc.rem_tiles * sc.k_blocks;
-  const long long b0 = (long long)p * W / sc.Gs, b1 = (long long)(p + 1) * W / sc.Gs;
-  const int rt = (int)(b0 / sc.k_blocks) + (it - nA);
-  if (rt >= sc.rem_tiles) return sg;
-  const long long t0 = (long long)rt * sc.k_blocks;
-  const long long lo = b0 > t0 ? b0 : t0, hi = b1 < t0 + sc.k_blocks ? b1 : t0 + sc.k_blocks;
+  if (sc.Gs == sc.rem_tiles) {  // nothing is cut: unit p has the whole remaining tile p
+    if (it > sc.rounds) return sg;
+    sg.valid = true;
+    sg.tile = sc.tiles_full + p;
+    sg.rem_index = p; sg.first_slot = sg.part_slot = 2 * p;
+    return sg;
+  }
+  const unsigned kbs = (unsigned)sc.k_blocks, Gs = (unsigned)sc.Gs;
+  const unsigned W = (unsigned)sc.rem_tiles * kbs;
+  const unsigned b0 = (unsigned)p * W / Gs, b1 = (unsigned)(p + 1) * W / Gs;
+  const unsigned rt = b0 / kbs + (unsigned)(it - sc.rounds);
+  if (rt >= (unsigned)sc.rem_tiles) return sg;
+  const unsigned t0 = rt * kbs;
+  const unsigned lo = b0 > t0 ? b0 : t0, hi = b1 < t0 + kbs ? b1 : t0 + kbs;
   if (lo >= hi) return sg;
-  int pf, S;
-  sk_tile_parts(sc.k_blocks, sc.rem_tiles, sc.Gs, rt, &pf, &S);
+  const unsigned pf = ((t0 + 1u) * Gs - 1u) / W, pl = ((t0 + kbs) * Gs - 1u) / W;  // sk_tile_parts in 32 bits
   sg.valid = true;
-  sg.tile = sc.tiles_full + rt;
+  sg.tile = sc.tiles_full + (int)rt;
   sg.kb0 = (int)(lo - t0);
   sg.kb1 = (int)(hi - t0);
-  sg.parts = S;
-  sg.first_slot = pf + rt;
-  sg.part_slot = p + rt;
-  sg.rem_index = rt;
+  sg.parts = (int)(pl - pf + 1u);
+  sg.first_slot = (int)(pf + rt);
+  sg.part_slot = p + (int)rt;
+  sg.rem_index = (int)rt;
   return sg;
 }
+// True when some tile of this launch is cut along K (its parts meet in the workspace).
+__device__ __forceinline__ bool has_cut_tiles(const Sched& sc) { return sc.Gs > sc.rem_tiles; }
 
 // Partial tiles are kept column-major in the workspace ([BN columns][BM rows] fp32): the 32 lanes
 // of an epilogue warp hold 32 consecutive rows, so every load / store instruction of a warp moves
@@ -259,7 +342,7 @@ struct WorkspaceSource {
   size_t slot_stride;    // floats per slot (BM * BN)
   int bm;                // rows of the tile = stride between columns
   int parts;
-  __device__ __forceinline__ void load32(int col, float* f) const {
+  __device__ __forceinline__ void load32(int col, float* f, int /*chunk_of_unit*/ = 0) const {
 #pragma unroll
     for (int j = 0; j < 32; ++j) f[j] = 0.f;
     int i = 0;
@@ -291,6 +374,7 @@ template <typename T> struct RowCtx {
   T* kv_row;       // EPI_ROTARY: this token's key row in the paged KV cache, or null
   bool vec_ok;
   float scale;     // EPI_MOE_SCATTER: routed weight of this row's slot
+  uint8_t* stage;  // this warp's block of shared memory for warp_store_rows32
 };
 
 // Work units of a tile: the chunks an epilogue warp fetches together.
@@ -350,39 +434,40 @@ __device__ __forceinline__ int unit_chunks(const GemmArgs& g, int n0, int u, int
 // straddles the k / v boundary.
 template <typename T>
 __device__ __forceinline__ void store_kv32(const GemmArgs& g, const RowCtx<T>& rc, int gn, const float* f) {
-  if (!rc.kv_row || gn < g.q_cols || gn >= g.q_cols + 2 * g.kv_cols) return;
+  if (!g.kv_cache || gn < g.q_cols || gn >= g.q_cols + 2 * g.kv_cols) return;  // warp-uniform
   const int c = gn - g.q_cols;
-  T* dst = c < g.kv_cols ? rc.kv_row + c : rc.kv_row + (int64_t)g.kv_page_size * g.kv_cols + (c - g.kv_cols);
-  store_row32<T>(dst, f, 32, true);
+  T* dst = nullptr;
+  if (rc.kv_row) dst = c < g.kv_cols ? rc.kv_row + c : rc.kv_row + (int64_t)g.kv_page_size * g.kv_cols + (c - g.kv_cols);
+  warp_store_rows32<T>(rc.stage, dst, f, 32, true, rc.row_ok && dst != nullptr);
 }
 
-// Finish one unit: fetch its chunk(s) from `src`, apply the epilogue math, store.
+// Finish one unit: fetch its chunk(s) from `src`, apply the epilogue math, store.  Called by all lanes of a warp
+// (rows beyond M take part in the loads and in the cooperative store, and store nothing).
 template <typename T, int EPI, typename Source>
 __device__ __forceinline__ void finish_unit(const GemmArgs& g, const RowCtx<T>& rc, const Source& src, int u) {
   int cols[2];
   const int nch = unit_chunks<EPI>(g, rc.n0, u, cols);
   if (nch == 0) return;
   float a[32];
-  src.load32(cols[0], a);  // warp-uniform (TMEM loads are .sync.aligned)
+  src.load32(cols[0], a, 0);  // warp-uniform (TMEM loads are .sync.aligned)
+  const int gn = rc.n0 + cols[0];  // the unit's first output column: the same for all lanes
   if constexpr (EPI == EPI_MOE_SCATTER) {
     // Reference: the second fused_moe_kernel launch multiplies the fp32 accumulator by the routed
     // weight before rounding to T (layers/fused_moe/fused_moe.py:130-147, MUL_ROUTED_WEIGHT).
-    const int gn = rc.n0 + cols[0];
-    if (rc.row_ok && gn < g.N) {
+    if (gn < g.N) {
 #pragma unroll
       for (int j = 0; j < 32; ++j) a[j] *= rc.scale;
-      store_row32<T>(rc.out_row + gn, a, g.N - gn, rc.vec_ok);
+      warp_store_rows32<T>(rc.stage, rc.out_row + gn, a, g.N - gn, rc.vec_ok, rc.row_ok);
     }
   } else if constexpr (EPI == EPI_STORE || EPI == EPI_PUSH) {
-    const int gn = rc.n0 + cols[0];
-    if (rc.row_ok && gn < g.N) {
-      if (EPI == EPI_STORE && g.bias) {
+    if (gn < g.N) {
+      if (EPI == EPI_STORE && g.bias && rc.row_ok) {
         const T* bias = reinterpret_cast<const T*>(g.bias);
 #pragma unroll
         for (int j = 0; j < 32; ++j)
           if (gn + j < g.N) a[j] += DT<T>::to_f(bias[gn + j]);
       }
-      if (EPI == EPI_STORE && rc.res_row) {
+      if (EPI == EPI_STORE && rc.res_row) {  // (null for rows beyond M)
         // Reference: hidden_states = residual + hidden_states on the rounded projection output
         // (models/llama.py:248,254): one more operator result of the 16-bit type.
         if (g.N - gn >= 32 && rc.vec_ok && ((g.ldr & 7) == 0) && aligned16(g.residual)) {
@@ -396,35 +481,33 @@ __device__ __forceinline__ void finish_unit(const GemmArgs& g, const RowCtx<T>& 
             if (gn + j < g.N) a[j] = rt<T>(DT<T>::to_f(rc.res_row[gn + j]) + rt<T>(a[j]));
         }
       }
-      store_row32<T>(rc.out_row + gn, a, g.N - gn, rc.vec_ok);
+      warp_store_rows32<T>(rc.stage, rc.out_row + gn, a, g.N - gn, rc.vec_ok, rc.row_ok);
     }
   } else if constexpr (EPI == EPI_SILU_MUL) {
     // Reference: gate_up = F.linear(x) rounded to T, then silu_and_mul
     // (csrc/activation_kernels.cu:8-25): out = (T)(silu(gate)) * up.
     float b[32];
-    src.load32(cols[1], b);
+    src.load32(cols[1], b, 1);
     const int d = g.N / 2;
-    const int gn = rc.n0 + cols[0];
-    if (rc.row_ok && gn < d) {
+    if (gn < d) {
 #pragma unroll
       for (int j = 0; j < 32; ++j) {
         const float gte = rt<T>(a[j]), up = rt<T>(b[j]);
         const float sl = rt<T>(gte / (1.0f + expf(-gte)));
         a[j] = rt<T>(sl * up);
       }
-      store_row32<T>(rc.out_row + gn, a, d - gn, rc.vec_ok);
+      warp_store_rows32<T>(rc.stage, rc.out_row + gn, a, d - gn, rc.vec_ok, rc.row_ok);
     }
   } else {  // EPI_ROTARY
     // Reference: F.linear output rounded to T (tensor_parallel/layers.py:278-284), then
     // rotary_embedding in T arithmetic on the q and k heads (csrc/pos_encoding_kernels.cu:8-76).
-    const int gn = rc.n0 + cols[0];
     if (nch == 2) {  // NeoX pair of chunks: x = global columns gn.., y = x + head_size/2
       float b[32];
-      src.load32(cols[1], b);
-      if (rc.row_ok && gn < g.N) {
+      src.load32(cols[1], b, 1);
+      if (gn < g.N) {
         const int half = g.head_size / 2;
         const int in_head = gn % g.head_size;  // (whole-head tiles: = cols[0] % head_size)
-        if (gn - in_head < g.rot_cols) {  // a q or k head; the v heads of a split tile are stored as they are
+        if (gn - in_head < g.rot_cols && rc.row_ok) {  // a q or k head; the v heads of a split tile are stored as they are
           float co[32], si[32];
           load_row32<T>(rc.cs + in_head, co);
           load_row32<T>(rc.cs + half + in_head, si);
@@ -435,14 +518,14 @@ __device__ __forceinline__ void finish_unit(const GemmArgs& g, const RowCtx<T>& 
             b[j] = rt<T>(rt<T>(y * co[j]) + rt<T>(x * si[j]));
           }
         }
-        store_row32<T>(rc.out_row + gn, a, g.N - gn, rc.vec_ok);
-        store_row32<T>(rc.out_row + gn + half, b, g.N - gn - half, rc.vec_ok);
+        warp_store_rows32<T>(rc.stage, rc.out_row + gn, a, g.N - gn, rc.vec_ok, rc.row_ok);
+        warp_store_rows32<T>(rc.stage, rc.out_row + gn + half, b, g.N - gn - half, rc.vec_ok, rc.row_ok);
         store_kv32<T>(g, rc, gn, a);
         store_kv32<T>(g, rc, gn + half, b);
       }
-    } else if (rc.row_ok && gn < g.N) {
+    } else if (gn < g.N) {
       const int head0 = (cols[0] / g.head_size) * g.head_size;
-      if ((rc.n0 + head0) < g.rot_cols) {  // GPT-J style: pairs (2i, 2i+1), cos/sin index = column_in_head / 2
+      if ((rc.n0 + head0) < g.rot_cols && rc.row_ok) {  // GPT-J style: pairs (2i, 2i+1), cos/sin index = column_in_head / 2
         const int half = g.head_size / 2;
         const int in_head = cols[0] - head0;
 #pragma unroll
@@ -454,7 +537,7 @@ __device__ __forceinline__ void finish_unit(const GemmArgs& g, const RowCtx<T>& 
           a[j + 1] = rt<T>(rt<T>(y * co) + rt<T>(x * si));
         }
       }
-      store_row32<T>(rc.out_row + gn, a, g.N - gn, rc.vec_ok);
+      warp_store_rows32<T>(rc.stage, rc.out_row + gn, a, g.N - gn, rc.vec_ok, rc.row_ok);
       store_kv32<T>(g, rc, gn, a);
     }
   }
@@ -463,8 +546,9 @@ __device__ __forceinline__ void finish_unit(const GemmArgs& g, const RowCtx<T>& 
 // Per-thread context of the rows an epilogue warp finishes.
 template <typename T, int EPI>
 __device__ __forceinline__ RowCtx<T> make_row_ctx(const GemmArgs& g, const CommView& comm, const ReduceArgs& red,
-                                                  int gm, int n0) {
+                                                  int gm, int n0, uint8_t* stage) {
   RowCtx<T> rc;
+  rc.stage = stage;
   rc.gm = gm;
   rc.row_ok = gm < g.M;
   rc.n0 = n0;
@@ -552,10 +636,19 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
   uint64_t* empty_bar = full_bar + 8;
   uint64_t* tmem_full = empty_bar + 8;   // [2]
   uint64_t* tmem_empty = tmem_full + 2;  // [2]
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tmem_empty + 2);
+  uint64_t* xchg_bar = tmem_empty + 2;    // cluster K-split: bytes of the other pairs' partials landing here
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(xchg_bar + 1);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  // each epilogue warp's block for the transposing stores (warps 0 and 1 never use theirs)
+  uint8_t* epi_stage = smem + (size_t)kStages * stage_bytes + kBarrierBytes + (size_t)((threadIdx.x >> 5) >= 2 ? (threadIdx.x >> 5) - 2 : 0) * kEpiWarpStageBytes;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+#ifdef SB200_TRACE
+  __shared__ unsigned int gemm_trace_row_s;
+  if (blockIdx.x == 0 && threadIdx.x == 0) gemm_trace_row_s = atomicAdd(&g_gemm_trace_launch, 1u);
+  unsigned int gemm_trace_row = 0;
+  if (threadIdx.x == 0) { gemm_trace_row = gemm_trace_row_s; SB_GEMM_MARK(0); }
+#endif
   if constexpr (EPI == EPI_PUSH) trace_mark(red, 0);
   // this unit's work items
   Sched sc;
@@ -564,6 +657,7 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
   sc.rem_tiles = g.m_tiles * g.n_tiles - g.tiles_full;
   sc.Gs = g.rem_units;
   sc.k_blocks = g.k_blocks;
+  sc.rounds = g.tiles_full / num_units_grid;
   // Every CTA of this persistent grid is resident from the start, so the next kernel of the stream may be
   // scheduled onto SMs as they become free (its prologue then overlaps this kernel's tail).
   ptx::grid_launch_dependents();
@@ -577,6 +671,7 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
       ptx::mbar_init(&tmem_full[b], 1);
       ptx::mbar_init(&tmem_empty[b], CTA2 ? 2 * kEpiWarps : kEpiWarps);  // one arrival per epilogue warp (of both CTAs)
     }
+    ptx::mbar_init(xchg_bar, 1);
     *abort_flag = 0;
     ptx::mbar_fence_init();
   }
@@ -593,8 +688,13 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
   if (CTA2) ptx::cluster_sync_all();  // the peer's barriers are initialised before anything signals them
   ptx::tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
+#ifdef SB200_TRACE
+  gemm_trace_row = gemm_trace_row_s;
+  if (threadIdx.x == 0) SB_GEMM_MARK(1);  // prologue done
+#endif
   // Nothing above touched global memory: from here on the kernel reads what earlier kernels of the stream wrote.
   ptx::grid_dependency_wait();
+  if (threadIdx.x == 0) SB_GEMM_MARK(10);  // after the dependency wait
   // grouped mode: rows of A in use (a device value written by moe_align_block_size earlier in the stream)
   const int rows_in_use = g.expert_ids ? min(g.M, *g.num_post_pad) : g.M;
 
@@ -604,9 +704,11 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
+      SB_GEMM_MARK(14);  // producer entered
       for (int it = 0; ok; ++it) {
         const Segment sg = segment_of(sc, unit_id, it);
         if (!sg.valid) break;
+        if (it == 0) SB_GEMM_MARK(15);  // first segment known
         const int mt = sg.tile % g.m_tiles, nt = sg.tile / g.m_tiles;
         int b_row0 = 0;  // grouped mode: first B row of this row block's expert
         if (g.expert_ids) {
@@ -616,6 +718,7 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
         const int p_kb1 = kb_hi(sg);
         for (int kb = kb_lo(sg); kb < p_kb1; ++kb) {
           if (!ptx::mbar_wait(&empty_bar[stage], phase ^ 1u, abort_flag)) { ok = false; break; }
+          if (kb == kb_lo(sg) && it == 0) SB_GEMM_MARK(11);  // stage 0 free, about to request it
           uint8_t* sa = stage_base + (size_t)stage * stage_bytes;
           uint8_t* sb = sa + a_bytes;
           const bool halves = (EPI == EPI_SILU_MUL) || (EPI == EPI_ROTARY && g.rot_split);  // B tile = two row blocks
@@ -657,9 +760,11 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
               ptx::tma_load_2d(sb, &tmap_b, &full_bar[stage], kb * kBK, b_row0 + nt * BN);
             }
           }
+          if (kb == kb_lo(sg) && it == 0) SB_GEMM_MARK(2);  // first stage requested
           if (++stage == kStages) { stage = 0; phase ^= 1u; }
         }
       }
+      SB_GEMM_MARK(3);  // last stage requested
     }
   } else if (warp == 1) {
     // -------------------------------------------------------------- MMA issuer
@@ -682,6 +787,7 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
         for (int kb = kb0; kb < kb1; ++kb) {
           if (!ptx::mbar_wait(&full_bar[stage], phase, abort_flag)) { ok = false; break; }
           ptx::tc_fence_after();
+          if (kb == kb0 && it == 0) SB_GEMM_MARK(4);  // first stage arrived
           const uint32_t sa = ptx::smem_u32(stage_base + (size_t)stage * stage_bytes);
           const uint64_t db = ptx::make_smem_desc_sw128(sa + a_bytes);
 #pragma unroll
@@ -702,6 +808,7 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
         if (ok) {  // accumulators complete
           if (CTA2) ptx::umma_commit_pair_mask(&tmem_full[buf], pair_mask); else ptx::umma_commit(&tmem_full[buf]);
         }
+        SB_GEMM_MARK(5);  // last MMA issued
       }
     }
   } else {
@@ -728,9 +835,10 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
       ok = __all_sync(0xffffffffu, ptx::mbar_wait(&tmem_full[buf], use & 1u, abort_flag) ? 1 : 0) != 0;
       if (!ok) break;  // warp-uniform: no lane is left behind in an aligned tcgen05.ld
       ptx::tc_fence_after();
+      if (warp == 2 && lane == 0) SB_GEMM_MARK(6);  // accumulators complete (seen by the epilogue)
 
       const int n0 = tile_first_col<EPI>(g, nt);
-      const RowCtx<T> rc = make_row_ctx<T, EPI>(g, comm, red, mt * BM + row_in_tile, n0);
+      const RowCtx<T> rc = make_row_ctx<T, EPI>(g, comm, red, mt * BM + row_in_tile, n0, epi_stage);
       const TmemSource tsrc{tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)((buf * MI + a0) * BN)};
       if (S == 1) {
         for (int u = u_first; u < U; u += u_step) finish_unit<T, EPI>(g, rc, tsrc, u);
@@ -750,6 +858,8 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
         }
       }
 
+      if (warp == 2 && lane == 0) SB_GEMM_MARK(7);  // this warp's share of the tile stored
+      if (warp == 9 && lane == 0) SB_GEMM_MARK(13);
       // TMEM drained: hand the buffer back to the MMA warp (of the leader CTA).
       ptx::tc_fence_before();
       __syncwarp();
@@ -768,7 +878,7 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
     // Second pass over the cut tiles this unit has a part of: once every part of a tile has left its
     // share for these 32 rows, finish 1/S of the tile's units -- all S parts work on the fix-up at
     // once instead of one of them doing it alone.
-    for (int it = sc.tiles_full / sc.G; ok && ks == 1; ++it) {
+    for (int it = sc.rounds; ok && ks == 1 && has_cut_tiles(sc); ++it) {
       const Segment sg = segment_of(sc, unit_id, it);
       if (!sg.valid) break;
       const int S = sg.parts;
@@ -788,7 +898,7 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
       arrived = __shfl_sync(0xffffffffu, arrived, 0);
       if (!arrived) { ok = false; break; }
       const int n0 = tile_first_col<EPI>(g, nt);
-      const RowCtx<T> rc = make_row_ctx<T, EPI>(g, comm, red, mt * BM + row_in_tile, n0);
+      const RowCtx<T> rc = make_row_ctx<T, EPI>(g, comm, red, mt * BM + row_in_tile, n0, epi_stage);
       {
         const int my_part = sg.part_slot - sg.first_slot;
         const WorkspaceSource wsrc{g.ws + (size_t)sg.first_slot * BM * BN + row_in_tile, (size_t)BM * BN, BM, S};
@@ -809,16 +919,37 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
   }
 
   // ------------------------------------------------- cluster K-split: exchange + epilogue
-  // Every thread of every CTA of the cluster joins the two cluster barriers, whatever happened before (a wait
-  // that ran out only makes its warp skip the work in between).
+  // The pairs of the cluster hold partial accumulators of the same tile.  The tile's epilogue units are dealt
+  // out to the pairs (unit u belongs to pair u % ks).  A pair parks the chunks of the other pairs' units in its
+  // own shared memory (the stage ring is free by then) and hands each warp's 4 KiB block to the copy engine,
+  // which moves it into the owner's shared memory and counts the bytes on the owner's barrier; a pair finishes
+  // its own units from TMEM plus what it received.  The exchange so moves (ks-1)/ks of an accumulator per CTA,
+  // in all directions at once, and the epilogue work is split ks ways.
+  // Every thread of every CTA of the cluster joins the cluster barrier, whatever happened before (a wait that
+  // ran out only makes its warp skip the work after it).
   if constexpr (CTA2 && MI == 1) {
     if (ks > 1) {
+      constexpr int kChunksPerUnit = (EPI == EPI_SILU_MUL || EPI == EPI_ROTARY) ? 2 : 1;
       const Segment sg = segment_of(sc, unit_id, 0);  // the unit's one tile
       const int mt = sg.tile % g.m_tiles, nt = sg.tile / g.m_tiles;
       const int q = warp & 3, hsel = (warp - 2) >> 2;
       const int U = num_units<EPI>(g);
       const int row_in_cta = q * 32 + lane;
+      const int n0 = tile_first_col<EPI>(g, nt);
+      const uint32_t area_bytes = xchg_area_bytes(U, ks, kChunksPerUnit);  // one pair's units of an accumulator
+      uint8_t* out_area = stage_base;                                 // [other pair][unit of it][chunk]: what this CTA sends
+      uint8_t* in_area = stage_base + (size_t)(ks - 1) * area_bytes;   // [other pair][own unit][chunk]: what it receives
       bool ok = sg.valid;
+      if (warp == 2 && lane == 0) {
+        // announce the bytes the other pairs will send for this pair's units (before the cluster barrier below,
+        // so before any of them can arrive)
+        uint32_t chunks = 0;
+        for (int u = (int)kpart; u < U; u += ks) {
+          int cols[2];
+          chunks += (uint32_t)unit_chunks<EPI>(g, n0, u, cols);
+        }
+        ptx::mbar_expect_tx(xchg_bar, chunks * (uint32_t)(ks - 1) * kXchgChunkBytes);
+      }
       if (warp >= 2 && ok) {
         ok = __all_sync(0xffffffffu, ptx::mbar_wait(&tmem_full[0], 0u, abort_flag) ? 1 : 0) != 0;
         ptx::tc_fence_after();
@@ -827,42 +958,68 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
       __syncthreads();          // (the warps re-converge here: the producer and the MMA issuer ran on one lane)
       ptx::cluster_sync_all();  // every pair's MMAs are complete: the stage buffers of all CTAs are free
       ptx::tc_fence_after();
+      if (warp == 2 && lane == 0) SB_GEMM_MARK(6);
       const uint32_t tmem_row = tmem_base + ((uint32_t)(q * 32) << 16);
-      if (warp >= 2 && ok && kpart > 0) {
-        // this pair's partial accumulator rows go to the CTA of pair 0 that holds the same 128 rows
-        const uint32_t dst = ptx::map_to_cta(ptx::smem_u32(stage_base), cta_rank) +
-                             (uint32_t)(((size_t)(kpart - 1) * BN * 128 + row_in_cta) * sizeof(float));
-        for (int c = hsel * 32; c < BN; c += 64) {  // the two warps of a lane quarter alternate 32-column chunks
-          uint32_t r[32];
-          ptx::tmem_ld_32x32(tmem_row + (uint32_t)c, r);
+      // the k-th unit of a pair (u = k * ks + pair) is sent, and later finished, by warp k % 2 of the lane quarter
+      if (warp >= 2 && ok) {
+        for (int u = 0; u < U; ++u) {
+          const int owner = u % ks, k = u / ks;
+          if (owner == (int)kpart || (k & 1) != hsel) continue;
+          int cols[2];
+          const int nch = unit_chunks<EPI>(g, n0, u, cols);
+          const int slot_out = owner < (int)kpart ? owner : owner - 1;
+          const int slot_in = (int)kpart < owner ? (int)kpart : (int)kpart - 1;  // the owner keeps its sources in pair order
+          const uint32_t dst_cta = (uint32_t)(2 * owner) + cta_rank;
+          for (int c = 0; c < nch; ++c) {
+            const size_t blk = (size_t)(k * kChunksPerUnit + c) * kXchgChunkBytes + (size_t)q * (kXchgChunkBytes / 4);
+            uint8_t* mine = out_area + (size_t)slot_out * area_bytes + blk;
+            uint32_t r[32];
+            ptx::tmem_ld_32x32(tmem_row + (uint32_t)cols[c], r);
+            const uint32_t rowp = ptx::smem_u32(mine) + (uint32_t)(lane * 128);
 #pragma unroll
-          for (int j = 0; j < 32; ++j)
-            ptx::st_shared_cluster_f32(dst + (uint32_t)((c + j) * 128 * sizeof(float)), __uint_as_float(r[j]));
+            for (int j = 0; j < 8; ++j)
+              asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(rowp + (uint32_t)((j ^ (lane & 7)) << 4)), "r"(r[4 * j]),
+                           "r"(r[4 * j + 1]), "r"(r[4 * j + 2]), "r"(r[4 * j + 3])
+                           : "memory");
+            ptx::fence_proxy_async_smem();
+            __syncwarp();
+            if (lane == 0)
+              ptx::bulk_copy_to_cta(ptx::map_to_cta(ptx::smem_u32(in_area + (size_t)slot_in * area_bytes + blk), dst_cta),
+                                    ptx::smem_u32(mine), kXchgChunkBytes / 4, ptx::map_to_cta(ptx::smem_u32(xchg_bar), dst_cta));
+          }
         }
       }
-      ptx::tc_fence_before();
-      __syncthreads();
-      ptx::cluster_sync_all();  // the partials are in pair 0's shared memory
-      ptx::tc_fence_after();
-      if (warp >= 2 && ok && kpart == 0) {
-        const int n0 = tile_first_col<EPI>(g, nt);
-        const int row_in_tile = (int)cta_rank * 128 + row_in_cta;
-        const RowCtx<T> rc = make_row_ctx<T, EPI>(g, comm, red, mt * BM + row_in_tile, n0);
-        const TmemPlusSmemSource src{tmem_row, reinterpret_cast<const float*>(stage_base) + row_in_cta, ks - 1, BN};
-        for (int u = hsel; u < U; u += 2) finish_unit<T, EPI>(g, rc, src, u);
-        if constexpr (EPI == EPI_PUSH) push_rows_done(comm, red, g, mt * BM + row_in_tile - lane);
+      if (warp == 2 && lane == 0) SB_GEMM_MARK(7);
+      if (warp >= 2 && ok) {
+        ok = __all_sync(0xffffffffu, ptx::mbar_wait(xchg_bar, 0u, abort_flag) ? 1 : 0) != 0;  // the partials have landed
+        if (warp == 2 && lane == 0) SB_GEMM_MARK(13);
+        if (ok) {
+          const int row_in_tile = (int)cta_rank * 128 + row_in_cta;
+          const RowCtx<T> rc = make_row_ctx<T, EPI>(g, comm, red, mt * BM + row_in_tile, n0, epi_stage);
+          for (int u = (int)kpart + hsel * ks; u < U; u += 2 * ks) {
+            const TmemPlusSmemSource src{tmem_row, in_area + (size_t)((u / ks) * kChunksPerUnit) * kXchgChunkBytes +
+                                                       (size_t)row_in_cta * 128, ks - 1, area_bytes};
+            finish_unit<T, EPI>(g, rc, src, u);
+          }
+          // every warp of every pair reports its share of these 32 rows (also one that had no unit to finish)
+          if constexpr (EPI == EPI_PUSH) push_rows_done(comm, red, g, mt * BM + row_in_tile - lane);
+        }
       }
     }
   }
 
   // -------------------------------------------------------------- common exit
+  __syncwarp();  // the producer / MMA lanes re-join their warps before the block-wide barrier
   ptx::tc_fence_before();
   __syncthreads();
+  if (threadIdx.x == 0) SB_GEMM_MARK(8);  // all roles done
   if (CTA2) ptx::cluster_sync_all();  // the peer no longer signals our barriers / writes our TMEM
+  if (threadIdx.x == 32) SB_GEMM_MARK(12);  // before the TMEM release
   if (warp == 1) {
     ptx::tc_fence_after();
     if (CTA2) ptx::tmem_dealloc_pair(tmem_base, kTmemCols); else ptx::tmem_dealloc(tmem_base, kTmemCols);
   }
+  if (threadIdx.x == 32) SB_GEMM_MARK(9);  // TMEM released
   if (*abort_flag) {
     if (threadIdx.x == 0) {
       if (g.status) atomicCAS(g.status, 0u, (uint32_t)CS_TIMEOUT_MBARRIER);

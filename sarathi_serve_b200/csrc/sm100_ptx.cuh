@@ -220,6 +220,16 @@ __device__ __forceinline__ uint32_t cluster_nctarank() {
 __device__ __forceinline__ void st_shared_cluster_f32(uint32_t cluster_addr, float v) {
   asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(cluster_addr), "f"(v) : "memory");
 }
+// Bulk copy from this CTA's shared memory into the shared memory of a CTA of the cluster (both addresses and
+// the size multiples of 16 bytes; destination and barrier are cluster addresses from map_to_cta).  The copy
+// engine counts the bytes on the destination CTA's mbarrier as they land.  Writes made by ordinary stores must
+// be handed to the copy engine with fence_proxy_async_smem first.
+__device__ __forceinline__ void bulk_copy_to_cta(uint32_t cluster_dst, uint32_t local_src, uint32_t bytes, uint32_t cluster_bar) {
+  asm volatile("cp.async.bulk.shared::cluster.shared::cta.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(cluster_dst),
+               "r"(local_src), "r"(bytes), "r"(cluster_bar)
+               : "memory");
+}
+__device__ __forceinline__ void fence_proxy_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 
 // Instruction descriptor for kind::f16 / kind::tf32, fp32 accumulate, both operands K-major, M = 128.
 // ab_format: 0 = fp16, 1 = bf16, 2 = tf32.

@@ -68,6 +68,9 @@ CASES: Dict[str, LayerCase] = {
                            norm_weight_noise=0.02),
     "mini_f16": LayerCase("mini_f16", 512, 8, 2, 64, 768, 1e-6, 10000.0, 1024, 130, 0, 6, 130, 1024, torch.float16,
                           norm_weight_noise=0.02),
+    # eight kv heads: shards over up to 8 tensor-parallel ranks (the reference splits whole kv heads)
+    "mini8_bf16": LayerCase("mini8_bf16", 1024, 8, 8, 128, 2048, 1e-5, 500000.0, 1024, 57, 5, 12, 64, 1024, torch.bfloat16,
+                            norm_weight_noise=0.02),
 }
 
 

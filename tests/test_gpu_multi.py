@@ -225,7 +225,7 @@ def _body_carry(rank, world):
         def forward(self, q, k, v, idx, scale=1.0, layer_id=None):
             return q
 
-    case = S.CASES["mini_bf16"]
+    case = S.CASES["mini_bf16" if world <= 2 else "mini8_bf16"]  # (kv heads must divide over the ranks)
     old = torch.get_default_dtype()
     torch.set_default_dtype(case.dtype)
     try:
@@ -423,7 +423,7 @@ def _body_graph_io(rank, world):
         def forward(self, q, k, v, idx, scale=1.0, layer_id=None):
             return q
 
-    case = S.CASES["mini_bf16"]
+    case = S.CASES["mini_bf16" if world <= 2 else "mini8_bf16"]  # (kv heads must divide over the ranks)
     old = torch.get_default_dtype()
     torch.set_default_dtype(case.dtype)
     try:
