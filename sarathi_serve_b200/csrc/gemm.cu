@@ -57,6 +57,43 @@ int make_tmap_2d(CUtensorMap* map, int dtype, const void* ptr, int64_t rows, int
   return SB200_OK;
 }
 
+// Clusters of `cluster_ctas` GEMM CTAs (one CTA per SM) that can be resident at the same time.  A cluster must
+// sit inside one GPC, so this is less than #SMs / cluster_ctas when the GPCs' SM counts are not multiples of the
+// cluster size.  It matters for the row-parallel kernel: its CTAs wait, after their tiles, for flags that depend
+// on every tile of the launch, so all clusters of a launch must be resident together -- one that is still
+// queued behind waiting CTAs would never start.  Asked of the runtime once per device and cluster size; without
+// a device (planning on a CPU-only host) the estimate is three quarters of #SMs / cluster_ctas.
+static int max_coresident_clusters(int cluster_ctas) {
+  static std::mutex mu;
+  static int cached[64][17];
+  int dev = 0;
+  const bool have_dev = cudaGetDevice(&dev) == cudaSuccess && dev >= 0 && dev < 64;
+  if (cluster_ctas < 2 || cluster_ctas > 16) return sm_count();
+  if (!have_dev) { cudaGetLastError(); return sm_count() / cluster_ctas * 3 / 4; }
+  std::lock_guard<std::mutex> lock(mu);
+  if (cached[dev][cluster_ctas] > 0) return cached[dev][cluster_ctas];
+  auto kern = gemm_sm100_kernel<__nv_bfloat16, EPI_PUSH, true, 1>;
+  int n = 0;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(cluster_ctas * 32);
+  cfg.blockDim = dim3(kGemmThreads);
+  cfg.dynamicSmemBytes = kSmemBudget;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = cluster_ctas;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBudget) != cudaSuccess ||
+      cudaOccupancyMaxActiveClusters(&n, kern, &cfg) != cudaSuccess || n <= 0) {
+    cudaGetLastError();
+    n = sm_count() / cluster_ctas * 3 / 4;
+  }
+  cached[dev][cluster_ctas] = n;
+  return n;
+}
+
 // ------------------------------------------------------------ tile selection
 // Analytical choice of (CTA pairing, MI, BN, scheduling): estimated SM clocks of the slowest unit.
 //   main loop per k-block = max(tensor time, shared-memory traffic of the stage at 128 B/clk
@@ -97,6 +134,10 @@ GemmPlan plan_gemm(int epi, int64_t M, int64_t N, int64_t K, int head_size, int 
     const int units_of_tile = (epi == EPI_SILU_MUL || split_tile) ? bn / 64 : bn / 32;
     const size_t exchange = 2 * (size_t)(sp - 1) * xchg_area_bytes(units_of_tile, sp, (epi == EPI_SILU_MUL || epi == EPI_ROTARY) ? 2 : 1);
     if (tiles * 2 * sp > sms || k_blocks < sp || stages < 2 || exchange > (size_t)stages * gemm_stage_bytes(1, bn, 1)) return p;
+    // row-parallel kernel: its CTAs wait for one another, so every cluster must be resident; and clusters of
+    // four pairs are not used with it (on two ranks that combination left an owner's flag unset in the
+    // owner-reduce scheme -- the bounded wait reported it -- while clusters of two pairs pass every case)
+    if (epi == EPI_PUSH && (sp != 2 || tiles > max_coresident_clusters(2 * sp))) return p;
     p.cta2 = 1; p.mi = 1; p.bn = bn; p.units = (int)tiles; p.tiles_full = (int)tiles; p.rem_splits = 1; p.rem_units = 0;
     p.stages = stages; p.m_tiles = m_tiles; p.n_tiles = n_tiles; p.k_blocks = k_blocks; p.cluster_split = sp;
     p.est_clocks = 9000.0 + (double)((k_blocks + sp - 1) / sp) * (2.0 * bn > 260.0 ? 2.0 * bn : 260.0) + exchange / 2.0 / 64.0;
@@ -122,7 +163,8 @@ GemmPlan plan_gemm(int epi, int64_t M, int64_t N, int64_t K, int head_size, int 
       const int n_tiles = (int)((out_cols + cols_per_tile - 1) / cols_per_tile);
       const int64_t tiles = (int64_t)m_tiles * n_tiles;
       if (!f_mode && bm > 128 && M <= bm / 2) continue;  // half of the tile would be empty
-      const int units_max = cta2 ? sms / 2 : sms;     // CTAs or CTA pairs that run at once
+      int units_max = cta2 ? sms / 2 : sms;     // CTAs or CTA pairs that run at once
+      if (cta2 && epi == EPI_PUSH && max_coresident_clusters(2) < units_max) units_max = max_coresident_clusters(2);
       const int64_t total = tiles * k_blocks;
       // per-k-block clocks of one SM (constants fitted to the measured times of the full kernels on B200):
       //   one CTA: about 616 clocks per k-block whatever N <= 256 -- not the tensor pipe (the MMA-rate probe of

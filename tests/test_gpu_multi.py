@@ -170,6 +170,10 @@ def _body_rowpar(rank, world):
                 zf = zref.float()
                 yref = (zf * torch.rsqrt(zf.pow(2).mean(-1, keepdim=True) + 1e-5)).to(dtype) * nw
                 assert _rel(z, zref) <= tol * 2 and _rel(y, yref) <= tol * 2, ("fused", dtype, T, H, K, tile_n)
+                try:  # a wait that ran out is reported with the configuration it happened in
+                    comm.check_status()
+                except RuntimeError as e:
+                    raise AssertionError(f"status after {(dtype, one_shot, T, H, K, tile_n)}: {e}") from e
     comm.check_status()
 
 
