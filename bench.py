@@ -17,11 +17,13 @@ the path).  Inputs are seeded synthetic tensors (sarathi_serve_b200.synthetic).
             in one CUDA graph, CUDA-event timed, max over ranks.
 `gpu_comparison`: the same step as the reference runs it on a GPU (cuBLAS GEMMs, separate rotary /
             SiLU*mul / add+RMSNorm kernels, NCCL all-reduce), same graph timing.
-`e2e`     : tokens/s through the public layer API with HOST buffers: pinned H2D of the
-            hidden states and positions, LlamaDecoderLayer.forward and the D2H of the result, all captured
-            once per layer in a CUDA graph (graph_runner.LayerGraph with host_io) and replayed, then a host
-            sync, every step.  At N > 1 every rank moves its T/N token rows over PCIe and the full input is
-            assembled over NVLink inside the graph (shard_host_io).
+`e2e`     : tokens/s through the public layer API with HOST buffers: every step uploads its hidden states
+            and positions from pinned host memory, runs LlamaDecoderLayer.forward (captured once per layer in a
+            CUDA graph, graph_runner.LayerGraph) and brings its result back to pinned host memory, where the
+            host waits for it.  graph_runner.HostPipeline keeps three steps in flight: the upload of step i+1
+            and the download of step i-1 run on copy streams under the kernels of step i.  At N > 1 every rank
+            moves its T/N token rows over PCIe and the full input is assembled over NVLink inside the graph
+            (shard_host_io).
 `roofline`: the dominant kernel (gate_up GEMM + SiLU*mul), timed alone with CUDA events.
 Weights of several distinct layers are cycled so that each step's operands exceed the L2.
 One JSON line is printed by rank 0.
@@ -226,7 +228,7 @@ def run_reference_arm(a):
 PARITY_TOL = 2e-2  # bf16: max|a - b| / max|ref| per tensor
 
 
-def check_parity(case, t, world, rank, dev, step_resident, runner0, layers, max_over_ranks) -> dict:
+def check_parity(case, t, world, rank, dev, step_resident, runner0, layers, max_over_ranks, pipelined_out=None) -> dict:
     import torch
     from oracle import tp_layer_oracle as O
     from sarathi_serve_b200 import synthetic as S
@@ -251,7 +253,13 @@ def check_parity(case, t, world, rank, dev, step_resident, runner0, layers, max_
     p = {"max_rel_err_out": max_over_ranks(err_out), "max_rel_err_residual_rows": max_over_ranks(err_res),
          "max_rel_err_e2e": max_over_ranks(err_e2e), "tol": PARITY_TOL,
          "against": f"CPU oracle of the layer over all {world} shards; every rank checks its outputs, max over ranks"}
-    p["ok"] = all(p[k] <= PARITY_TOL for k in ("max_rel_err_out", "max_rel_err_residual_rows", "max_rel_err_e2e"))
+    keys = ["max_rel_err_out", "max_rel_err_residual_rows", "max_rel_err_e2e"]
+    if pipelined_out is not None:
+        # what the TIMED end-to-end steps left in the host buffer of the first layer's slot (three steps in flight)
+        err_pipe = float((pipelined_out.double() - ref["out"][io_lo:io_hi].double()).abs().max()) / float(ref["out"].double().abs().max())
+        p["max_rel_err_e2e_pipelined"] = max_over_ranks(err_pipe)
+        keys.append("max_rel_err_e2e_pipelined")
+    p["ok"] = all(p[k] <= PARITY_TOL for k in keys)
     return p
 
 
@@ -367,23 +375,27 @@ def run_native(a):
         x_host = t.x.to(case.dtype).pin_memory()
         pos_host = t.positions.pin_memory()
 
-        # the public call for a fixed batch shape: a captured layer (LayerGraph) fed from host buffers
-        from sarathi_serve_b200.graph_runner import LayerGraph
-        # (host_io: the H2D copies of the step's inputs and the D2H copy of its result are nodes of the graph,
-        #  so a step is one launch and one host synchronisation)
+        # the public call for a fixed batch shape: captured layers (LayerGraph) fed from pinned host buffers
+        # through HostPipeline -- the upload of step i+1 and the download of step i-1 run on copy streams while
+        # the kernels of step i do; every step's input crosses PCIe and every step's result is read on the host.
         #  At N > 1 the host buffers are sharded by token rows: each rank uploads T/N rows, the full input is
         #  assembled over NVLink by an all-gather inside the graph, and each rank downloads its T/N rows of the
         #  result -- the step's hidden states cross PCIe once per node, not once per rank.)
-        runners = [LayerGraph(l, T, attn, host_io=True, shard_host_io=world > 1) for l in layers]
+        from sarathi_serve_b200.graph_runner import HostPipeline, LayerGraph
+        n_slots = max(3, n_layers)
+        runners = [LayerGraph(layers[j % n_layers], T, attn, host_io=True, shard_host_io=world > 1, copies_in_graph=False)
+                   for j in range(n_slots)]
         io_lo, io_hi = runners[0].row_range
         for r_ in runners:
             r_.host_positions.copy_(pos_host)
             r_.host_hidden_states.copy_(x_host[io_lo:io_hi])
+        pipe = HostPipeline(runners)
         barrier()
 
         def step_e2e(i):
-            runners[i % n_layers].replay_host_io()
-            torch.cuda.current_stream().synchronize()
+            pipe.submit()
+            if pipe.in_flight >= 3:
+                pipe.collect()  # waits for the oldest step's result to be in host memory
 
         e2e_steps = max(50, a.steps)
         # untimed lead-in: at least `warmup` steps and at least 0.3 s of them, so that the clocks have settled under
@@ -396,18 +408,21 @@ def run_native(a):
         extra = int(max_over_ranks(max(0.0, 0.3 - n_warm * per) / per))
         for i in range(extra):
             step_e2e(i)
+        pipe.drain()
         barrier()
         t0 = time.perf_counter()
         for i in range(e2e_steps):
             step_e2e(i)
+        pipe.drain()  # the last results are on the host before the clock stops
         barrier()
         ms_e2e = max_over_ranks((time.perf_counter() - t0) * 1e3 / e2e_steps)
+        pipelined_out = runners[0].host_output.clone()  # checked against the oracle below
         comm.check_status()
 
         # ---- parity of what was just timed, outside the timed regions: one resident step (normed output on
         # every rank, the rows of the new residual this rank owns) and one end-to-end step (host buffers in,
         # host buffer out) against the CPU oracle of the layer over all `world` shards
-        parity = check_parity(case, t, world, rank, dev, step_resident, runners[0], layers, max_over_ranks)
+        parity = check_parity(case, t, world, rank, dev, step_resident, runners[0], layers, max_over_ranks, pipelined_out)
 
         def graph_ms(fn, n, reps=5, lead_in=True):
             """Mean device time of one fn(i) call: n calls captured in a CUDA graph, replayed reps times;
@@ -513,7 +528,9 @@ def run_native(a):
                         "h2d_bytes_per_step": (io_hi - io_lo) * H * es + T * 8, "d2h_bytes_per_step": (io_hi - io_lo) * H * es,
                         "io": (f"per rank: token rows [{io_lo}, {io_hi}) of the {T} x {H} hidden states up and down, all "
                                f"{T} positions up; whole job: {T * H * es} B up and down plus {world} x {T * 8} B of positions"
-                               if world > 1 else "the full batch up and down")},
+                               if world > 1 else "the full batch up and down"),
+                        "pipeline": "3 steps in flight: upload of step i+1 and download of step i-1 on copy streams "
+                                    "under the kernels of step i; the host waits for every step's result"},
                 "gpu_launches": (4 if world > 1 else 6) * a.steps, "launch_mode": "one CUDA graph of all timed steps",
                 "tile_cfgs": {k[0] + f"[{k[2]}x{k[3]}]": v for k, v in dense_ops._tuned.items()},
                 "roofline": {"bound": "tensor", "kernel": "gemm_sm100_kernel<bf16, EPI_SILU_MUL> (gate_up + SiLU*mul)",

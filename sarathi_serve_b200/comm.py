@@ -10,9 +10,10 @@ from cudaMalloc with the 64-byte CUDA IPC handles exchanged once at
 construction; either way a host barrier follows.  The data path is this
 library's own kernels over NVLink; NCCL is not called on it.
 
-``SB200_NVLS=1`` in the environment (or ``multicast=True``) asks for the
-multicast heaps; without it the heaps stay on plain peer mappings.  Every rank
-of a group has to make the same choice."""
+The multicast heaps are the default; ``SB200_NVLS=0`` in the environment (or
+``multicast=False``) keeps the heaps on plain peer mappings (so does a node
+without NVSwitch multicast, or a start-up self-test of the multicast path that
+fails on any rank).  Every rank of a group has to make the same choice."""
 from __future__ import annotations
 
 import ctypes
@@ -54,7 +55,7 @@ class TPComm:
         self.multicast = False
         lib = N.lib()
         if multicast is None:
-            multicast = os.environ.get("SB200_NVLS", "0") == "1"
+            multicast = os.environ.get("SB200_NVLS", "1") != "0"
         with torch.cuda.device(self.device):
             if world > 1 and multicast and self._create_on_symmetric_memory(lib, int(region_bytes)):
                 pass

@@ -138,6 +138,47 @@ def test_layer_graph_replay_equals_eager(tp1):
     tp1.get_tensor_model_parallel_comm().check_status()
 
 
+def test_host_pipeline_returns_every_steps_result_in_order(tp1):
+    """graph_runner.HostPipeline (uploads and downloads on copy streams under the neighbouring steps' kernels):
+    with three steps in flight every collected result equals the eager layer on that step's input."""
+    from sarathi_serve_b200.graph_runner import HostPipeline, LayerGraph
+
+    class Q:
+        def forward(self, q, k, v, layer_cache_idx, softmax_scale=1.0, layer_id=None):
+            return q
+
+    case = S.CASES["mini_bf16"]
+    layer, t = build_layer(case)
+    slots = [LayerGraph(layer, case.num_tokens, Q(), host_io=True, copies_in_graph=False) for _ in range(3)]
+    with pytest.raises(RuntimeError, match="copies_in_graph"):
+        HostPipeline([LayerGraph(layer, case.num_tokens, Q(), host_io=True)] * 2)
+    pipe = HostPipeline(slots)
+    scales = [1.0, -0.5, 0.25, 2.0, -1.5, 0.75, 1.25]
+    with torch.inference_mode():
+        eager = [layer(t.positions.cuda(), (t.x * sc).to(case.dtype).cuda(), 0, Q()).cpu() for sc in scales]
+    got = []
+    for sc in scales:
+        g = pipe.next_slot()
+        g.host_positions.copy_(t.positions)
+        g.host_hidden_states.copy_((t.x * sc).to(case.dtype))
+        pipe.submit()
+        if pipe.in_flight >= 3:
+            got.append(pipe.collect().clone())
+    while pipe.in_flight:
+        got.append(pipe.collect().clone())
+    assert len(got) == len(scales)
+    for i, (a, b) in enumerate(zip(got, eager)):
+        assert torch.equal(a, b), i
+    with pytest.raises(RuntimeError, match="nothing in flight"):
+        pipe.collect()
+    # the serial call of such a graph (copies enqueued around the replay) gives the same
+    slots[0].host_hidden_states.copy_((t.x * scales[1]).to(case.dtype))
+    out = slots[0].replay_host_io()
+    torch.cuda.synchronize()
+    assert torch.equal(out, eager[1])
+    tp1.get_tensor_model_parallel_comm().check_status()
+
+
 def test_model_stack_embedding_layers_norm_logits(tp1):
     """Token ids -> VocabParallelEmbedding -> two decoder layers chained through forward_carry -> final norm
     (applied by the last layer's kernel) -> lm_head logits, against the oracle's op-by-op chain."""

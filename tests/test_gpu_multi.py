@@ -453,6 +453,29 @@ def _body_graph_io(rank, world):
         err = float((out.double() - ref[lo:hi].double()).abs().max()) / float(ref.double().abs().max())
         assert err <= TOL[case.dtype], (rep, err)
     ps.get_tensor_model_parallel_comm().check_status()
+    # the same through HostPipeline: three steps in flight, copies on their own streams, kernels on one
+    from sarathi_serve_b200.graph_runner import HostPipeline
+    slots = [LayerGraph(layer, case.num_tokens, QAttention(), host_io=True, shard_host_io=True, copies_in_graph=False)
+             for _ in range(3)]
+    pipe = HostPipeline(slots)
+    xs = [(t.x * (1.0 - 0.2 * rep)).to(case.dtype) for rep in range(5)]
+    got = []
+    _host_barrier()
+    for x in xs:
+        g = pipe.next_slot()
+        g.host_positions.copy_(t.positions)
+        g.host_hidden_states.copy_(x[lo:hi])
+        pipe.submit()
+        if pipe.in_flight >= 3:
+            got.append(pipe.collect().clone())
+    while pipe.in_flight:
+        got.append(pipe.collect().clone())
+    for rep, (x, out) in enumerate(zip(xs, got)):
+        ref = O.decoder_layer(shards, x, t.positions, num_heads=case.num_heads, num_kv_heads=case.num_kv_heads,
+                              head_dim=case.head_dim, eps=case.rms_norm_eps, cache=cache)["out"]
+        err = float((out.double() - ref[lo:hi].double()).abs().max()) / float(ref.double().abs().max())
+        assert err <= TOL[case.dtype], ("pipelined", rep, err)
+    ps.get_tensor_model_parallel_comm().check_status()
 
 
 # -------------------------------------------------------------------- tests
