@@ -255,10 +255,10 @@ def check_parity(case, t, world, rank, dev, step_resident, runner0, layers, max_
          "against": f"CPU oracle of the layer over all {world} shards; every rank checks its outputs, max over ranks"}
     keys = ["max_rel_err_out", "max_rel_err_residual_rows", "max_rel_err_e2e"]
     if pipelined_out is not None:
-        # what the TIMED end-to-end steps left in the host buffer of the first layer's slot (three steps in flight)
+        # what the TIMED pipelined end-to-end steps left in the host buffer of the first layer's slot (three steps
+        # in flight); the caller reports the pipelined figure only if this passes, the serial one otherwise
         err_pipe = float((pipelined_out.double() - ref["out"][io_lo:io_hi].double()).abs().max()) / float(ref["out"].double().abs().max())
         p["max_rel_err_e2e_pipelined"] = max_over_ranks(err_pipe)
-        keys.append("max_rel_err_e2e_pipelined")
     p["ok"] = all(p[k] <= PARITY_TOL for k in keys)
     return p
 
@@ -389,40 +389,76 @@ def run_native(a):
         for r_ in runners:
             r_.host_positions.copy_(pos_host)
             r_.host_hidden_states.copy_(x_host[io_lo:io_hi])
-        pipe = HostPipeline(runners)
         barrier()
 
-        def step_e2e(i):
+        def time_e2e(step, finish):
+            """ms per step of `step(i)`; `finish()` brings the last results to the host before the clock stops.
+            Untimed lead-in: at least `warmup` steps and at least 0.3 s of them, so that the clocks have settled
+            under this leg's duty cycle (the GPU idled while the graphs were built); the same count on every rank."""
+            n_warm = max(10, a.warmup)
+            t_w = time.perf_counter()
+            for i in range(n_warm):
+                step(i)
+            per = max(1e-5, (time.perf_counter() - t_w) / n_warm)
+            extra = int(max_over_ranks(max(0.0, 0.3 - n_warm * per) / per))
+            for i in range(extra):
+                step(i)
+            finish()
+            barrier()
+            t0 = time.perf_counter()
+            for i in range(e2e_steps):
+                step(i)
+            finish()
+            barrier()
+            return max_over_ranks((time.perf_counter() - t0) * 1e3 / e2e_steps)
+
+        e2e_steps = max(50, a.steps)
+
+        # (1) one step at a time: upload, layer, download, host synchronisation
+        def step_serial(i):
+            runners[i % n_slots].replay_host_io()
+            torch.cuda.current_stream().synchronize()
+
+        ms_e2e_serial = time_e2e(step_serial, lambda: None)
+        comm.check_status()
+
+        # (2) three steps in flight.  This is the figure reported when the result it leaves in the host buffer
+        # passes the parity check below on every rank; otherwise the serial figure stands.
+        pipe = HostPipeline(runners)
+
+        def step_pipelined(i):
             pipe.submit()
             if pipe.in_flight >= 3:
                 pipe.collect()  # waits for the oldest step's result to be in host memory
 
-        e2e_steps = max(50, a.steps)
-        # untimed lead-in: at least `warmup` steps and at least 0.3 s of them, so that the clocks have settled under
-        # this leg's duty cycle (the GPU idled while the graphs were built); the same count on every rank
-        n_warm = max(10, a.warmup)
-        t_w = time.perf_counter()
-        for i in range(n_warm):
-            step_e2e(i)
-        per = max(1e-5, (time.perf_counter() - t_w) / n_warm)
-        extra = int(max_over_ranks(max(0.0, 0.3 - n_warm * per) / per))
-        for i in range(extra):
-            step_e2e(i)
-        pipe.drain()
-        barrier()
-        t0 = time.perf_counter()
-        for i in range(e2e_steps):
-            step_e2e(i)
-        pipe.drain()  # the last results are on the host before the clock stops
-        barrier()
-        ms_e2e = max_over_ranks((time.perf_counter() - t0) * 1e3 / e2e_steps)
-        pipelined_out = runners[0].host_output.clone()  # checked against the oracle below
-        comm.check_status()
+        ms_e2e_pipelined, pipelined_out, pipeline_note = None, None, ""
+        failed = 0
+        try:
+            ms_local = time_e2e(step_pipelined, pipe.drain)
+            pipelined_out = runners[0].host_output.clone()
+            comm.check_status()
+        except RuntimeError as e:  # (a bounded wait that ran out, or a stream / graph error)
+            failed, pipeline_note = 1, f"pipelined leg failed on rank {rank}: {str(e)[:200]}"
+        if max_over_ranks(float(failed)) > 0:
+            torch.cuda.synchronize()
+            if world > 1:
+                comm.reset()  # every rank: the contexts' call counters and flags are back in step
+            pipelined_out = None
+            pipeline_note = pipeline_note or "pipelined leg failed on another rank"
+        else:
+            ms_e2e_pipelined = ms_local
 
         # ---- parity of what was just timed, outside the timed regions: one resident step (normed output on
         # every rank, the rows of the new residual this rank owns) and one end-to-end step (host buffers in,
         # host buffer out) against the CPU oracle of the layer over all `world` shards
         parity = check_parity(case, t, world, rank, dev, step_resident, runners[0], layers, max_over_ranks, pipelined_out)
+        if ms_e2e_pipelined is not None and parity.get("max_rel_err_e2e_pipelined", 1.0) <= PARITY_TOL:
+            ms_e2e, e2e_mode = ms_e2e_pipelined, ("3 steps in flight: upload of step i+1 and download of step i-1 on copy "
+                                                  "streams under the kernels of step i; the host waits for every step's result")
+        else:
+            ms_e2e, e2e_mode = ms_e2e_serial, ("one step at a time (upload, layer, download, host synchronisation)"
+                                               + (": " + pipeline_note if pipeline_note else ": the pipelined leg's result "
+                                                  "did not pass the parity check"))
 
         def graph_ms(fn, n, reps=5, lead_in=True):
             """Mean device time of one fn(i) call: n calls captured in a CUDA graph, replayed reps times;
@@ -529,8 +565,8 @@ def run_native(a):
                         "io": (f"per rank: token rows [{io_lo}, {io_hi}) of the {T} x {H} hidden states up and down, all "
                                f"{T} positions up; whole job: {T * H * es} B up and down plus {world} x {T * 8} B of positions"
                                if world > 1 else "the full batch up and down"),
-                        "pipeline": "3 steps in flight: upload of step i+1 and download of step i-1 on copy streams "
-                                    "under the kernels of step i; the host waits for every step's result"},
+                        "pipeline": e2e_mode, "ms_per_step_serial": ms_e2e_serial,
+                        "ms_per_step_pipelined": ms_e2e_pipelined},
                 "gpu_launches": (4 if world > 1 else 6) * a.steps, "launch_mode": "one CUDA graph of all timed steps",
                 "tile_cfgs": {k[0] + f"[{k[2]}x{k[3]}]": v for k, v in dense_ops._tuned.items()},
                 "roofline": {"bound": "tensor", "kernel": "gemm_sm100_kernel<bf16, EPI_SILU_MUL> (gate_up + SiLU*mul)",
