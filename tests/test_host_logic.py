@@ -133,6 +133,57 @@ def test_two_rank_gloo_groups_and_distributed_oracle():
     mp.spawn(_gloo_worker, args=(2, 29731, None), nprocs=2)
 
 
+def _pipeline_worker(rank, world, port, tp, pp):
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    import torch.distributed as dist
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    torch.set_num_threads(1)
+    from sarathi_serve_b200 import parallel_state as ps
+    from sarathi_serve_b200.pipeline_mappings import recv, send
+    ps.initialize_model_parallel(tp, pp)
+    # the reference's layout (parallel_state.py:147-178): tensor-parallel groups are consecutive ranks, the stages
+    # of a pipeline are world / pp apart
+    assert ps.get_tensor_model_parallel_world_size() == tp and ps.get_tensor_model_parallel_rank() == rank % tp
+    assert ps.get_pipeline_model_parallel_world_size() == pp
+    stage = rank // (world // pp)
+    assert ps.get_pipeline_model_parallel_rank() == stage
+    assert ps.is_pipeline_first_stage() == (stage == 0) and ps.is_pipeline_last_stage() == (stage == pp - 1)
+    assert ps.get_pipeline_model_parallel_next_rank() == (rank + world // pp) % world
+    assert ps.get_pipeline_model_parallel_prev_rank() == (rank - world // pp) % world
+    # hidden states travel down the pipeline, every stage adds its mark (models/llama.py:347-359)
+    h = torch.zeros(5, 8)
+    if not ps.is_pipeline_first_stage():
+        h = recv(h)
+        assert torch.equal(h, torch.full((5, 8), float(sum(range(1, stage + 1)))) + (rank % (world // pp)))
+    else:
+        h = h + (rank % (world // pp))  # pipelines carry different data
+    if not ps.is_pipeline_last_stage():
+        send(h + (stage + 1))
+    ps.destroy_model_parallel()
+    assert ps.get_pipeline_model_parallel_world_size() == 1
+    dist.destroy_process_group()
+
+
+def test_pipeline_parallel_groups_and_stage_hand_off_two_stages():
+    mp.spawn(_pipeline_worker, args=(2, 29741, 1, 2), nprocs=2)
+
+
+def test_pipeline_parallel_groups_with_tensor_parallel_pairs():
+    mp.spawn(_pipeline_worker, args=(4, 29743, 2, 2), nprocs=4)
+
+
+def test_single_stage_hand_off_is_a_no_op():
+    from sarathi_serve_b200 import parallel_state as ps
+    from sarathi_serve_b200.pipeline_mappings import recv, send
+    ps.destroy_model_parallel()
+    ps.initialize_model_parallel(1)
+    x = torch.ones(2, 3)
+    assert send(x) is x and recv(x) is x
+    assert ps.is_pipeline_first_stage() and ps.is_pipeline_last_stage()
+    ps.destroy_model_parallel()
+
+
 # --------------------------------------------- host model of the flag protocol
 class _Rank:
     """Control words of one rank's heap: per-source flags (written by peers) and local arrival counters."""
