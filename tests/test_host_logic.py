@@ -361,6 +361,26 @@ def test_planner_gives_valid_schedules_for_the_layer_shapes(tp):
             assert 2 <= p["stages"] <= 8
 
 
+def test_planner_rules_for_the_cluster_k_split():
+    """Tile mode 5 (a cluster of S CTA pairs per tile): one cluster per tile, at least S k-blocks, room for the
+    exchanged accumulator shares in the stage ring; with the row-parallel epilogue, whose CTAs wait for one another,
+    only two pairs per cluster and only as many clusters as can be resident together."""
+    from sarathi_serve_b200 import dense_ops as D
+    p = D.gemm_plan(0, 512, 768, 4096, tile_cfg=405128)
+    assert p["cluster_split"] == 4 and p["cta_pairs"] == 1 and p["units"] == p["tiles_full"] == 12 and p["rem_units"] == 0
+    p = D.gemm_plan(0, 288, 1024, 704, tile_cfg=205256)
+    assert p["cluster_split"] == 2 and p["units"] == 8
+    with pytest.raises(RuntimeError):
+        D.gemm_plan(0, 512, 4096, 64, tile_cfg=205256)      # one k-block cannot be split
+    with pytest.raises(RuntimeError):
+        D.gemm_plan(0, 2048, 4096, 4096, tile_cfg=205256)   # 128 tiles x 4 CTAs do not fit the GPU
+    with pytest.raises(RuntimeError):
+        D.gemm_plan(1, 512, 6144, 4096, 128, tile_cfg=205256)  # 48 tiles x 4 CTAs do not fit either
+    assert D.gemm_plan(3, 288, 1024, 704, tile_cfg=205256)["cluster_split"] == 2
+    with pytest.raises(RuntimeError):
+        D.gemm_plan(3, 288, 1024, 704, tile_cfg=405128)     # row-parallel epilogue: two pairs only
+
+
 def test_tuned_configuration_cache_round_trip(tmp_path):
     from sarathi_serve_b200 import dense_ops as D
     saved = dict(D._tuned)
