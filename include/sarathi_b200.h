@@ -186,7 +186,9 @@ typedef struct sb200_rotary_args {
  *   a last round over about S units per tile, in equal ranges; a bare BN means MODE = 1,
  *   whole tiles per CTA; MODE = 5: CTA pairs, every tile computed by a cluster of S = 2 or 4 pairs
  *   that split its k-blocks and combine their fp32 accumulators through distributed shared memory --
- *   accepted when the problem has at most #SMs / (2 S) tiles).
+ *   accepted when the problem has at most #SMs / (2 S) tiles and at least S k-blocks (with the
+ *   row-parallel epilogue of sb200_gemm_rowpar: S = 2 only, and only as many clusters as the
+ *   device reports co-resident, because that kernel's CTAs wait for one another).
  * workspace: optional device buffer (zero-filled once by the caller, at least 64 KiB +
  *   room for the fp32 partial tiles) that allows tiles to be cut along K;
  *   the library leaves its first 64 KiB zero again after every launch.  NULL / 0: whole
