@@ -54,7 +54,7 @@ def reduce_from_tensor_model_parallel_region(input_: torch.Tensor) -> torch.Tens
             return input_
     flat = input_.view(-1, width)
     es_total = flat.shape[0] * width * es
-    comm = ps.get_tensor_model_parallel_comm(max(es_total, ps.DEFAULT_COMM_REGION_BYTES)
+    comm = ps.get_tensor_model_parallel_comm(max(es_total, ps.default_comm_region_bytes())
                                              if ps._TP_COMM is None else None)
     rows_per_call = max(1, comm.region_bytes // (width * es) // comm.world * comm.world)
     for r0 in range(0, flat.shape[0], rows_per_call):  # batches larger than the context's regions go in slices
@@ -91,7 +91,7 @@ def gather_from_tensor_model_parallel_region(input_: torch.Tensor) -> torch.Tens
         return torch.cat(parts, dim=-1).contiguous()
     rows = shard.numel() // width
     need = world * shard.numel() * es
-    comm = ps.get_tensor_model_parallel_comm(max(need, ps.DEFAULT_COMM_REGION_BYTES) if ps._TP_COMM is None else None)
+    comm = ps.get_tensor_model_parallel_comm(max(need, ps.default_comm_region_bytes()) if ps._TP_COMM is None else None)
     if need > comm.region_bytes:
         raise RuntimeError(f"gather_from_tensor_model_parallel_region: {need} bytes exceed the communication context's "
                            f"regions ({comm.region_bytes}); create the context with a larger size first")

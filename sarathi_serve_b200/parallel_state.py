@@ -38,6 +38,14 @@ def _following() -> bool:
 DEFAULT_COMM_REGION_BYTES = 64 << 20
 
 
+def default_comm_region_bytes() -> int:
+    """``DEFAULT_COMM_REGION_BYTES``, or SB200_COMM_REGION_BYTES from the environment (a worker sets it to
+    max_num_batched_tokens * hidden_size * itemsize when that exceeds 64 MiB; every rank the same)."""
+    import os
+    v = os.environ.get("SB200_COMM_REGION_BYTES")
+    return max(int(v), 1 << 20) if v else DEFAULT_COMM_REGION_BYTES
+
+
 def initialize_model_parallel(tensor_model_parallel_size: int = 1, pipeline_model_parallel_size: int = 1,
                               virtual_pipeline_model_parallel_size=None,
                               pipeline_model_parallel_split_rank=None) -> None:
@@ -163,7 +171,7 @@ def get_tensor_model_parallel_comm(region_bytes: Optional[int] = None):
     if _TP_COMM is None:
         from .comm import TPComm
         _TP_COMM = TPComm(get_tensor_model_parallel_rank(), get_tensor_model_parallel_world_size(),
-                          region_bytes or DEFAULT_COMM_REGION_BYTES,
+                          region_bytes or default_comm_region_bytes(),
                           group=get_tensor_model_parallel_group() if model_parallel_is_initialized() else None)
     elif region_bytes is not None and region_bytes > _TP_COMM.region_bytes:
         raise RuntimeError(f"the tensor-parallel context was created with {_TP_COMM.region_bytes} byte regions; "

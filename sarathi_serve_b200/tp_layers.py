@@ -203,8 +203,16 @@ class RowParallelLinear(torch.nn.Module):
         es = torch.empty((), dtype=self.weight.dtype).element_size()
         rows = -(-T // self.world_size) * self.world_size
         need = rows * self.output_size * es
-        return ps.get_tensor_model_parallel_comm(max(need, ps.DEFAULT_COMM_REGION_BYTES)
-                                                 if ps._TP_COMM is None else None)
+        comm = ps._TP_COMM
+        if comm is None:
+            return ps.get_tensor_model_parallel_comm(max(need, ps.default_comm_region_bytes()))
+        if need > comm.region_bytes:
+            # the context is shared by every layer of the process and sized once, by its first user
+            raise RuntimeError(f"a [{rows}, {self.output_size}] batch needs {need} bytes per region of the tensor-parallel "
+                               f"context, which was created with {comm.region_bytes}: create it before the first forward "
+                               f"with parallel_state.get_tensor_model_parallel_comm(max_num_batched_tokens * hidden_size * "
+                               f"itemsize), or set SB200_COMM_REGION_BYTES")
+        return comm
 
     def forward(self, input_) -> Tuple[torch.Tensor, Optional[torch.Tensor]]:
         input_parallel = input_ if self.input_is_parallel else scatter_to_tensor_model_parallel_region(input_)
